@@ -1,0 +1,359 @@
+// MSDA backward for sm_100a. For every sample s of task (b, q, h) and corner c:
+//     grad_value[row_c, :] += w_c * attn * grad_out[b, q, h, :]        (scatter)
+//     S_c = sum_d value[row_c, d] * grad_out[b, q, h, d]               (gather)
+// and per sample
+//     grad_attn  = w1*S1 + w2*S2 + w3*S3 + w4*S4          (bilinear w, no attn)
+//     grad_loc_x = W * attn * (hh*(S2 - S1) + lh*(S4 - S3))
+//     grad_loc_y = H * attn * (hw*(S3 - S1) + lw*(S4 - S2))
+// all three zero for a dropped sample. Replaces the reference's backward
+// device kernel and tiling
+// (kernels/multi_scale_deformable_attn/op_kernel/multi_scale_deformable_attn_grad.cpp:151-249,
+//  op_host/multi_scale_deformable_attn_grad.cpp:35-86).
+//
+// Same decomposition as the forward kernel. In phase 2 each lane holds the
+// piece of grad_out that matches its 16-byte piece of the row, issues one
+// vector reduction into the accumulation row (red.global.add.v4.f32, or
+// .v4.bf16x2 / .v4.f16x2 when accumulating straight into a 16-bit grad_value)
+// and leaves its partial dot product in shared memory; when a row is spread
+// over more than 8 lanes, xor shuffles first fold it to 8 partials. In phase 3
+// lane = sample again: it sums the partials of its four corners, forms the
+// three gradients and stores them next to its neighbours' (coalesced).
+#include "msda_launch.h"
+#include "msda_tile.cuh"
+
+namespace msda {
+
+constexpr int kPartMax = 8;  // partial dot products kept per (sample, corner)
+
+template <typename T, typename TG, int LPR, int NV, bool SCALAR>
+__global__ void __launch_bounds__(kThreadsPerCta)
+msda_bwd_kernel(const __grid_constant__ Params p) {
+    constexpr int VEC = SCALAR ? 1 : Elem<T>::kVec;
+    constexpr int RPI = 32 / LPR;
+    constexpr int PART = (LPR < kPartMax) ? LPR : kPartMax;  // partials per slot
+    constexpr int SSTRIDE = 4 * PART + 1;                    // per-sample stride (bank spread)
+    constexpr int UNROLL = (RPI >= 16) ? 2 : 4;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int g = lane / LPR;
+    const int j = lane % LPR;
+
+    Stage<T> st = stage_init<T>(p, smem);
+    unsigned char* warp_base =
+        smem + (p.stage ? stage_smem_bytes(p.tasks_per_item, p.LP, sizeof(T)) : 0);
+    warp_base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(warp_base) + 15) & ~uintptr_t(15));
+    constexpr int kWarpWords = 2 * kSlots + kChunk * (4 * kPartMax + 1) + 3;
+    constexpr int kWarpWordsAligned = (kWarpWords + 3) & ~3;
+    int* s_rows = reinterpret_cast<int*>(warp_base) + warp * kWarpWordsAligned;
+    float* s_wts = reinterpret_cast<float*>(s_rows + kSlots);
+    float* s_part = s_wts + kSlots;
+
+    const LaneLevels lv = load_lane_levels(p, lane);
+    const T* __restrict__ value = static_cast<const T*>(p.value);
+    const T* __restrict__ gloc = static_cast<const T*>(p.loc);
+    const T* __restrict__ gattn = static_cast<const T*>(p.attn);
+    const T* __restrict__ gout = static_cast<const T*>(p.grad_out);
+    TG* __restrict__ gval = static_cast<TG*>(p.grad_value);
+    T* __restrict__ gl = static_cast<T*>(p.grad_loc);
+    T* __restrict__ ga = static_cast<T*>(p.grad_attn);
+
+    const int TPC = p.tasks_per_item;
+    const int LP = p.LP;
+    const int D = p.D;
+    const int nchunks = (TPC == 1) ? (LP + kChunk - 1) / kChunk : 1;
+    const int QH = p.Q * p.H;
+    const long long ntiles = (p.nitems + kWarpsPerCta - 1) / kWarpsPerCta;
+
+    bool stage_ok = st.enabled;
+    if (stage_ok && threadIdx.x == 0 && blockIdx.x < ntiles && st.full(blockIdx.x)) {
+        st.issue(p, blockIdx.x, 0);
+    }
+
+    int iter = 0;
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++iter) {
+        const int buf = iter & 1;
+        bool from_smem = false;
+        if (stage_ok) {
+            const long long next = tile + gridDim.x;
+            if (threadIdx.x == 0 && next < ntiles && st.full(next)) st.issue(p, next, buf ^ 1);
+            if (st.full(tile)) {
+                from_smem = mbar_wait(st.bar + buf, (iter >> 1) & 1);
+                if (!from_smem) {
+                    stage_ok = false;
+                    atomicOr(p.status, kStatusStageTimeout);
+                }
+            }
+        }
+
+        const T* sloc = st.loc(buf);
+        const T* sattn = st.attn(buf);
+        const long long item = tile * kWarpsPerCta + warp;
+        if (item < p.nitems) {
+            const int t0 = static_cast<int>(item) * TPC;
+            const int ntask_here = min(TPC, static_cast<int>(p.ntasks - t0));
+
+            for (int chunk = 0; chunk < nchunks; ++chunk) {
+                // ---- phase 1: lane = sample -------------------------------------
+                int tl, s;
+                lane_sample_index(p, chunk, lane, tl, s);
+                const bool active = (tl < ntask_here) && (s < LP);
+                int4 rows = make_int4(-1, -1, -1, -1);
+                float4 wts = make_float4(0.f, 0.f, 0.f, 0.f);
+                SampleGeom geom;
+                geom.lw = geom.lh = geom.a = geom.wf = geom.hf = 0.f;
+                geom.valid = false;
+                long long gi = 0;
+                if (active) {
+                    const int t = t0 + tl;
+                    gi = static_cast<long long>(t) * LP + s;
+                    float lx, ly, a;
+                    if (from_smem) {
+                        const int li = (warp * TPC + tl) * LP + s;
+                        lx = Elem<T>::to_f(sloc[2 * li]);
+                        ly = Elem<T>::to_f(sloc[2 * li + 1]);
+                        a = Elem<T>::to_f(sattn[li]);
+                    } else {
+                        lx = Elem<T>::to_f(gloc[2 * gi]);
+                        ly = Elem<T>::to_f(gloc[2 * gi + 1]);
+                        a = Elem<T>::to_f(gattn[gi]);
+                    }
+                    const int b = t / QH;
+                    const int h = t % p.H;
+                    const int c = (TPC == 1) ? chunk : 0;
+                    const int row_base = (b * p.K + lv.start(c)) * p.H + h;
+                    sample_setup(lx, ly, a, lv.w(c), lv.h(c), row_base, p.H, rows, wts, geom);
+                }
+                reinterpret_cast<int4*>(s_rows)[lane] = rows;
+                reinterpret_cast<float4*>(s_wts)[lane] = wts;
+                __syncwarp();
+
+                // ---- phase 2: lane = (row slot, piece of row) -------------------
+                for (int tl2 = 0; tl2 < ntask_here; ++tl2) {
+                    int slot_begin, slot_end;
+                    if (TPC == 1) {
+                        slot_begin = 0;
+                        slot_end = 4 * min(kChunk, LP - chunk * kChunk);
+                    } else {
+                        slot_begin = tl2 * 4 * LP;
+                        slot_end = slot_begin + 4 * LP;
+                    }
+                    // this lane's piece of grad_out[b, q, h, :]
+                    float go[NV][VEC];
+                    const size_t obase = static_cast<size_t>(t0 + tl2) * D;
+#pragma unroll
+                    for (int k = 0; k < NV; ++k) {
+                        if constexpr (!SCALAR) {
+                            const uint4 raw =
+                                *reinterpret_cast<const uint4*>(gout + obase + (j + k * LPR) * VEC);
+                            unpack16<T>(raw, go[k]);
+                        } else {
+                            const int c = j + k * 32;
+                            go[k][0] = (c < D) ? Elem<T>::to_f(gout[obase + c]) : 0.f;
+                        }
+                    }
+#pragma unroll 1
+                    for (int base = slot_begin; base < slot_end; base += RPI * UNROLL) {
+                        int r[UNROLL];
+                        float w[UNROLL];
+                        float part[UNROLL];
+#pragma unroll
+                        for (int u = 0; u < UNROLL; ++u) {
+                            const int slot = base + u * RPI + g;
+                            const bool in = slot < slot_end;
+                            r[u] = in ? s_rows[slot] : -1;
+                            w[u] = in ? s_wts[slot] : 0.f;
+                            part[u] = 0.f;
+                        }
+                        if constexpr (!SCALAR) {
+                            uint4 raw[UNROLL][NV];
+#pragma unroll
+                            for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+                                for (int k = 0; k < NV; ++k) {
+                                    raw[u][k] = make_uint4(0u, 0u, 0u, 0u);
+                                    if (r[u] >= 0) {
+                                        raw[u][k] = ldg16(value + static_cast<size_t>(r[u]) * D +
+                                                          (j + k * LPR) * VEC);
+                                    }
+                                }
+                            }
+#pragma unroll
+                            for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+                                for (int k = 0; k < NV; ++k) {
+                                    if (r[u] >= 0) {
+                                        float contrib[VEC];
+#pragma unroll
+                                        for (int e = 0; e < VEC; ++e) contrib[e] = w[u] * go[k][e];
+                                        red_add_vec<TG, VEC>(gval + static_cast<size_t>(r[u]) * D +
+                                                                 (j + k * LPR) * VEC,
+                                                             contrib);
+                                    }
+                                    float f[VEC];
+                                    unpack16<T>(raw[u][k], f);
+#pragma unroll
+                                    for (int e = 0; e < VEC; ++e)
+                                        part[u] = fmaf(f[e], go[k][e], part[u]);
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+                                for (int k = 0; k < NV; ++k) {
+                                    const int c = j + k * 32;
+                                    if (r[u] >= 0 && c < D) {
+                                        const size_t idx = static_cast<size_t>(r[u]) * D + c;
+                                        const float v = Elem<T>::to_f(__ldg(value + idx));
+                                        red_add_scalar(gval + idx, w[u] * go[k][0]);
+                                        part[u] = fmaf(v, go[k][0], part[u]);
+                                    }
+                                }
+                            }
+                        }
+                        // fold to PART partials per slot, then park them in shared memory
+#pragma unroll
+                        for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+                            for (int off = LPR / 2; off >= PART; off >>= 1)
+                                part[u] += __shfl_xor_sync(0xffffffffu, part[u], off);
+                            const int slot = base + u * RPI + g;
+                            if (slot < slot_end && j < PART) {
+                                s_part[(slot >> 2) * SSTRIDE + (slot & 3) * PART + j] = part[u];
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+
+                // ---- phase 3: lane = sample -------------------------------------
+                if (active) {
+                    float S[4];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float acc = 0.f;
+#pragma unroll
+                        for (int q = 0; q < PART; ++q) acc += s_part[lane * SSTRIDE + c * PART + q];
+                        S[c] = acc;
+                    }
+                    float g_attn = 0.f, g_x = 0.f, g_y = 0.f;
+                    if (geom.valid) {
+                        // Corners that do not exist contributed nothing to s_part
+                        // only if their slot was visited with r < 0, which stores 0.
+                        const float lw = geom.lw, lh = geom.lh;
+                        const float hw = 1.f - lw, hh = 1.f - lh;
+                        g_attn = hh * hw * S[0] + hh * lw * S[1] + lh * hw * S[2] + lh * lw * S[3];
+                        g_x = geom.wf * geom.a * (hh * (S[1] - S[0]) + lh * (S[3] - S[2]));
+                        g_y = geom.hf * geom.a * (hw * (S[2] - S[0]) + lw * (S[3] - S[1]));
+                    }
+                    store_pair(gl + 2 * gi, g_x, g_y);
+                    ga[gi] = Elem<T>::from_f(g_attn);
+                }
+                __syncwarp();
+            }
+        }
+        if (st.enabled) __syncthreads();
+    }
+}
+
+// fp32 accumulation buffer -> 16-bit grad_value
+template <typename T>
+__global__ void __launch_bounds__(256) msda_downcast_kernel(const float* __restrict__ acc,
+                                                            T* __restrict__ out, long long n) {
+    const long long nvec = n / 8;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+         i += stride) {
+        const float4 a = reinterpret_cast<const float4*>(acc)[2 * i];
+        const float4 b = reinterpret_cast<const float4*>(acc)[2 * i + 1];
+        const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        reinterpret_cast<uint4*>(out)[i] = pack16<T>(f);
+    }
+    for (long long i = nvec * 8 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+         i < n; i += stride) {
+        out[i] = Elem<T>::from_f(acc[i]);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+template <typename T, typename TG, int LPR, int NV, bool SCALAR>
+static cudaError_t launch_bwd_inst(const Params& p, int grid, size_t smem, cudaStream_t stream) {
+    auto kern = msda_bwd_kernel<T, TG, LPR, NV, SCALAR>;
+    if (smem > 48 * 1024) {
+        cudaError_t e =
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    kern<<<grid, kThreadsPerCta, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <typename T, typename TG>
+static cudaError_t launch_bwd_typed(const Params& p, const RowPlan& rp, int grid, size_t smem,
+                                    cudaStream_t stream) {
+    if (rp.scalar) return launch_bwd_inst<T, TG, 32, 8, true>(p, grid, smem, stream);
+    switch (rp.lpr * 100 + rp.nv) {
+        case 101: return launch_bwd_inst<T, TG, 1, 1, false>(p, grid, smem, stream);
+        case 201: return launch_bwd_inst<T, TG, 2, 1, false>(p, grid, smem, stream);
+        case 401: return launch_bwd_inst<T, TG, 4, 1, false>(p, grid, smem, stream);
+        case 801: return launch_bwd_inst<T, TG, 8, 1, false>(p, grid, smem, stream);
+        case 1601: return launch_bwd_inst<T, TG, 16, 1, false>(p, grid, smem, stream);
+        case 3201: return launch_bwd_inst<T, TG, 32, 1, false>(p, grid, smem, stream);
+        case 3202:
+            if constexpr (sizeof(T) == 4) {
+                return launch_bwd_inst<T, TG, 32, 2, false>(p, grid, smem, stream);
+            }
+            return cudaErrorInvalidValue;
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+size_t bwd_smem_bytes(const Params& p, size_t elem) {
+    size_t s = p.stage ? stage_smem_bytes(p.tasks_per_item, p.LP, elem) : 0;
+    s = (s + 15) & ~size_t(15);
+    const size_t warp_words = (2 * kSlots + kChunk * (4 * kPartMax + 1) + 3 + 3) & ~size_t(3);
+    return s + static_cast<size_t>(kWarpsPerCta) * warp_words * 4 + 16;
+}
+
+cudaError_t launch_backward(const Params& p, int dtype, int acc_f32, const RowPlan& rp, int grid,
+                            cudaStream_t stream) {
+    switch (dtype) {
+        case 0: return launch_bwd_typed<float, float>(p, rp, grid, bwd_smem_bytes(p, 4), stream);
+        case 1:
+            return acc_f32
+                       ? launch_bwd_typed<__half, float>(p, rp, grid, bwd_smem_bytes(p, 2), stream)
+                       : launch_bwd_typed<__half, __half>(p, rp, grid, bwd_smem_bytes(p, 2),
+                                                          stream);
+        case 2:
+            return acc_f32 ? launch_bwd_typed<__nv_bfloat16, float>(p, rp, grid,
+                                                                    bwd_smem_bytes(p, 2), stream)
+                           : launch_bwd_typed<__nv_bfloat16, __nv_bfloat16>(
+                                 p, rp, grid, bwd_smem_bytes(p, 2), stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_downcast(const float* acc, void* out, long long n, int dtype,
+                            cudaStream_t stream) {
+    if (n <= 0) return cudaSuccess;
+    long long blocks = (n / 8 + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == 1) {
+        msda_downcast_kernel<__half><<<(int)blocks, 256, 0, stream>>>(
+            acc, static_cast<__half*>(out), n);
+    } else if (dtype == 2) {
+        msda_downcast_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(
+            acc, static_cast<__nv_bfloat16*>(out), n);
+    } else {
+        return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace msda

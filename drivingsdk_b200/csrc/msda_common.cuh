@@ -1,0 +1,320 @@
+// Shared device-side pieces of the sm_100a multi-scale deformable attention
+// (MSDA) kernels: parameter blocks, the per-sample bilinear set-up, 16-byte
+// vector loads, vector reductions into global memory, and the bounded
+// bulk-copy (TMA) + mbarrier primitives used to stage location/weight tiles.
+//
+// Semantics follow the reference operator:
+//   * pixel coordinates  x = loc_x * W - 0.5,  y = loc_y * H - 0.5
+//     (kernels/multi_scale_deformable_attn/op_kernel/msda.h:367-368);
+//   * a sample takes part only if  x > -1 && y > -1 && x < W && y < H, which
+//     also drops NaN/Inf locations (msda.h:369-390);
+//   * corner (y0,x0) needs y0>=0 && x0>=0, (y0,x1) needs y0>=0 && x1<=W-1,
+//     (y1,x0) needs y1<=H-1 && x0>=0, (y1,x1) needs y1<=H-1 && x1<=W-1; a
+//     missing corner reads as zero and receives no gradient
+//     (op_kernel/arch35/multi_scale_deformable_attn.cpp:59-62);
+//   * corner weights hh*hw, hh*lw, lh*hw, lh*lw, each times the attention
+//     weight (msda.h:492-520).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace msda {
+
+constexpr int kMaxLevels = 64;      // L*P <= 64 implies L <= 64
+constexpr int kWarpsPerCta = 8;
+constexpr int kThreadsPerCta = kWarpsPerCta * 32;
+constexpr int kChunk = 32;          // samples handled by one warp pass
+constexpr int kSlots = 4 * kChunk;  // (sample, corner) pairs per warp pass
+constexpr int kSpinLimit = 1 << 22; // bound on mbarrier polling
+
+// Device status bits, sticky until read by msda_sm100_device_status().
+constexpr int kStatusStageTimeout = 1;  // a staged tile never arrived
+
+// Level geometry by value. A launch that received the shapes on the host puts
+// them here (kernel parameters live in the constant bank); a launch that
+// received device pointers leaves use_table = 0 and each CTA reads the two
+// small arrays from global memory once.
+struct LevelTable {
+    int h[kMaxLevels];
+    int w[kMaxLevels];
+    int start[kMaxLevels];
+};
+
+struct Params {
+    // forward operands
+    const void* value;   // [B, K, H, D]
+    const void* loc;     // [B, Q, H, L, P, 2]  (x, y) in [0, 1]
+    const void* attn;    // [B, Q, H, L, P]
+    void* out;           // [B, Q, H*D]
+    // backward operands
+    const void* grad_out;  // [B, Q, H*D]
+    void* grad_value;      // [B, K, H, D]; accumulation target (may be fp32 scratch)
+    void* grad_loc;        // like loc
+    void* grad_attn;       // like attn
+    // level geometry on the device (used when use_table == 0)
+    const int* shapes_dev;  // [L, 2] (H, W)
+    const int* start_dev;   // [L]
+    int B, K, H, D, L, Q, P;
+    int LP;             // L * P
+    int tasks_per_item; // consecutive (b, q, h) tasks one warp pass covers
+    int use_table;
+    int stage;          // 1: bulk-copy location/weight tiles into shared memory
+    long long ntasks;   // B * Q * H
+    long long nitems;   // ceil(ntasks / tasks_per_item)
+    int* status;        // device status word
+    LevelTable lv;
+};
+
+// ---------------------------------------------------------------------------
+// element types
+// ---------------------------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    static constexpr int kVec = 4;  // elements in 16 bytes
+    __device__ static __forceinline__ float to_f(float v) { return v; }
+    __device__ static __forceinline__ float from_f(float v) { return v; }
+};
+template <> struct Elem<__half> {
+    static constexpr int kVec = 8;
+    __device__ static __forceinline__ float to_f(__half v) { return __half2float(v); }
+    __device__ static __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+template <> struct Elem<__nv_bfloat16> {
+    static constexpr int kVec = 8;
+    __device__ static __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+    __device__ static __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+
+// 16-byte read-only load that does not allocate in L1: gathered rows are
+// reused across SMs (through L2), almost never within one.
+__device__ __forceinline__ uint4 ldg16(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+
+template <typename T>
+__device__ __forceinline__ void unpack16(const uint4& raw, float (&f)[Elem<T>::kVec]);
+template <>
+__device__ __forceinline__ void unpack16<float>(const uint4& raw, float (&f)[4]) {
+    f[0] = __uint_as_float(raw.x);
+    f[1] = __uint_as_float(raw.y);
+    f[2] = __uint_as_float(raw.z);
+    f[3] = __uint_as_float(raw.w);
+}
+template <>
+__device__ __forceinline__ void unpack16<__half>(const uint4& raw, float (&f)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+template <>
+__device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4& raw, float (&f)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ uint4 pack16(const float (&f)[Elem<T>::kVec]);
+template <>
+__device__ __forceinline__ uint4 pack16<float>(const float (&f)[4]) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]),
+                      __float_as_uint(f[3]));
+}
+template <>
+__device__ __forceinline__ uint4 pack16<__half>(const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <>
+__device__ __forceinline__ uint4 pack16<__nv_bfloat16>(const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// ---------------------------------------------------------------------------
+// reductions into global memory (no return value): one 16-byte vector op per
+// lane, so a group of lanes covering one row issues a single full-row request.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void red_add_f32x4(float* p, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(a), "f"(b), "f"(c),
+                 "f"(d)
+                 : "memory");
+}
+__device__ __forceinline__ void red_add_16x8(__half* p, const uint4& v) {
+    asm volatile("red.global.add.noftz.v4.f16x2 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
+                 "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ void red_add_16x8(__nv_bfloat16* p, const uint4& v) {
+    asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x),
+                 "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+// Adds VEC consecutive fp32 contributions to an accumulation row whose element
+// type is TG (fp32 scratch / fp32 grad_value, or the 16-bit grad_value itself).
+template <typename TG, int VEC>
+__device__ __forceinline__ void red_add_vec(TG* row, const float (&c)[VEC]);
+template <>
+__device__ __forceinline__ void red_add_vec<float, 4>(float* row, const float (&c)[4]) {
+    red_add_f32x4(row, c[0], c[1], c[2], c[3]);
+}
+template <>
+__device__ __forceinline__ void red_add_vec<float, 8>(float* row, const float (&c)[8]) {
+    red_add_f32x4(row, c[0], c[1], c[2], c[3]);
+    red_add_f32x4(row + 4, c[4], c[5], c[6], c[7]);
+}
+template <>
+__device__ __forceinline__ void red_add_vec<__half, 8>(__half* row, const float (&c)[8]) {
+    red_add_16x8(row, pack16<__half>(c));
+}
+template <>
+__device__ __forceinline__ void red_add_vec<__nv_bfloat16, 8>(__nv_bfloat16* row,
+                                                              const float (&c)[8]) {
+    red_add_16x8(row, pack16<__nv_bfloat16>(c));
+}
+
+// Stores two adjacent elements (x at p[0], y at p[1]) with one instruction.
+__device__ __forceinline__ void store_pair(float* p, float x, float y) {
+    *reinterpret_cast<float2*>(p) = make_float2(x, y);
+}
+__device__ __forceinline__ void store_pair(__half* p, float x, float y) {
+    *reinterpret_cast<__half2*>(p) = __floats2half2_rn(x, y);
+}
+__device__ __forceinline__ void store_pair(__nv_bfloat16* p, float x, float y) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(x, y);
+}
+
+__device__ __forceinline__ void red_add_scalar(float* p, float v) { atomicAdd(p, v); }
+__device__ __forceinline__ void red_add_scalar(__half* p, float v) {
+    atomicAdd(p, __float2half_rn(v));
+}
+__device__ __forceinline__ void red_add_scalar(__nv_bfloat16* p, float v) {
+    atomicAdd(p, __float2bfloat16_rn(v));
+}
+
+// ---------------------------------------------------------------------------
+// bulk copy (TMA, non-tensor form) + mbarrier, all waits bounded
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+// global -> this CTA's shared memory; source, destination and size must all be
+// multiples of 16 bytes. No cluster multicast.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes,
+                                         uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+            "r"(smem_u32(dst_smem)),
+        "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+// Polls until the phase with the given parity completes, or the spin limit is
+// reached. Returns false on timeout; the caller falls back to plain loads.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (int spin = 0; spin < kSpinLimit; ++spin) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+// ---------------------------------------------------------------------------
+// per-sample set-up: lane-parallel over the samples of one warp pass
+// ---------------------------------------------------------------------------
+struct SampleGeom {
+    float lw, lh;  // fractional offsets inside the cell
+    float a;       // attention weight (0 when the sample is dropped)
+    float wf, hf;  // level width / height as floats
+    bool valid;
+};
+
+// rows[c] is the value row ((b*K + start + y*W + x)*H + h) of corner c, or -1
+// when that corner does not exist; wts[c] is bilinear weight * attention.
+__device__ __forceinline__ void sample_setup(float lx, float ly, float a, int Wl, int Hl,
+                                             int row_base, int H, int4& rows, float4& wts,
+                                             SampleGeom& g) {
+    const float wf = static_cast<float>(Wl);
+    const float hf = static_cast<float>(Hl);
+    const float x = lx * wf - 0.5f;
+    const float y = ly * hf - 0.5f;
+    const bool valid = (x > -1.f) && (y > -1.f) && (x < wf) && (y < hf);
+    const float x0f = floorf(x);
+    const float y0f = floorf(y);
+    const float lw = x - x0f;
+    const float lh = y - y0f;
+    const float hw = 1.f - lw;
+    const float hh = 1.f - lh;
+    // For dropped samples the coordinates may be NaN/Inf: keep the integer
+    // conversion away from them.
+    const int x0 = valid ? static_cast<int>(x0f) : 0;
+    const int y0 = valid ? static_cast<int>(y0f) : 0;
+    const int x1 = x0 + 1;
+    const int y1 = y0 + 1;
+    const bool x0ok = valid && x0 >= 0;
+    const bool x1ok = valid && x1 <= Wl - 1;
+    const bool y0ok = valid && y0 >= 0;
+    const bool y1ok = valid && y1 <= Hl - 1;
+    const int r00 = row_base + (y0 * Wl + x0) * H;
+    rows.x = (y0ok && x0ok) ? r00 : -1;
+    rows.y = (y0ok && x1ok) ? r00 + H : -1;
+    rows.z = (y1ok && x0ok) ? r00 + Wl * H : -1;
+    rows.w = (y1ok && x1ok) ? r00 + Wl * H + H : -1;
+    // Selects, not multiplications by zero: lw/lh/a may be NaN or Inf here.
+    const float aa = valid ? a : 0.f;
+    wts.x = valid ? hh * hw * aa : 0.f;
+    wts.y = valid ? hh * lw * aa : 0.f;
+    wts.z = valid ? lh * hw * aa : 0.f;
+    wts.w = valid ? lh * lw * aa : 0.f;
+    g.lw = valid ? lw : 0.f;
+    g.lh = valid ? lh : 0.f;
+    g.a = aa;
+    g.wf = wf;
+    g.hf = hf;
+    g.valid = valid;
+}
+
+}  // namespace msda

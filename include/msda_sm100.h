@@ -1,0 +1,135 @@
+/* C ABI of the sm_100a multi-scale deformable attention (MSDA) kernels.
+ *
+ * This library sits where the reference's generated operator API sat:
+ * `aclnnMultiScaleDeformableAttn[GetWorkspaceSize]` and
+ * `aclnnMultiScaleDeformableAttnGrad[GetWorkspaceSize]`, reached through
+ * EXEC_NPU_CMD in mx_driving/csrc/MultiScaleDeformableAttn.cpp:63-64 and
+ * :115-116 (dispatch macro: include/csrc/OpApiCommon.h:527-614). A host
+ * binding checks dtypes and limits, allocates the results and calls in here.
+ *
+ * Conventions
+ *   - plain pointers and sizes only; every data pointer is DEVICE memory of the
+ *     current CUDA device, except `spatial_shapes` and `level_start_index`,
+ *     which may be host OR device memory (detected per call; host arrays are
+ *     passed to the kernel by value, device arrays are read by the kernel);
+ *   - layouts are the reference's (mx_driving/ops/multi_scale_deformable_attn.py:22-44):
+ *       value               [B, K, H, D]
+ *       spatial_shapes      [L, 2] int32, (height, width) per level
+ *       level_start_index   [L]    int32, first key of each level
+ *       sampling_locations  [B, Q, H, L, P, 2], (x, y) normalised to [0, 1]
+ *       attention_weights   [B, Q, H, L, P]
+ *       output, grad_output [B, Q, H*D]
+ *     all floating tensors share one dtype (MSDA_F32 / MSDA_F16 / MSDA_BF16);
+ *   - work is enqueued on `stream` (a cudaStream_t; NULL = default stream);
+ *     nothing here synchronises, allocates or frees;
+ *   - the caller owns every buffer; outputs are fully overwritten;
+ *   - return value: MSDA_OK or a negative msda_status; nothing is thrown;
+ *   - re-entrant: no mutable host state is shared between calls except the
+ *     tuning knobs below.
+ * Limits (same as the reference binding, MultiScaleDeformableAttn.cpp:46-48):
+ *   D <= 256, L * P <= 64. Additionally B*K*H and B*Q*H must be below 2^31.
+ */
+#ifndef MSDA_SM100_H_
+#define MSDA_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum msda_dtype {
+    MSDA_F32 = 0,
+    MSDA_F16 = 1,
+    MSDA_BF16 = 2
+} msda_dtype;
+
+typedef enum msda_status {
+    MSDA_OK = 0,
+    MSDA_ERR_NULL = -1,        /* a required pointer is NULL */
+    MSDA_ERR_DIMS = -2,        /* a dimension is <= 0 */
+    MSDA_ERR_LIMIT = -3,       /* D > 256, L*P > 64, or an index would overflow */
+    MSDA_ERR_ALIGN = -4,       /* a pointer is not aligned to its element size */
+    MSDA_ERR_DTYPE = -5,       /* unknown dtype code */
+    MSDA_ERR_WORKSPACE = -6,   /* workspace missing or too small */
+    MSDA_ERR_CUDA = -7         /* a CUDA runtime call failed; see msda_sm100_last_cuda_error */
+} msda_status;
+
+/* Forward. Replaces aclnnMultiScaleDeformableAttn
+ * (mx_driving/csrc/MultiScaleDeformableAttn.cpp:63-64; device kernel
+ * kernels/multi_scale_deformable_attn/op_kernel/multi_scale_deformable_attn.cpp:349-387).
+ * Writes output[B, Q, H*D] in `dtype`. */
+int msda_sm100_forward(const void* value, const int32_t* spatial_shapes,
+                       const int32_t* level_start_index, const void* sampling_locations,
+                       const void* attention_weights, void* output, int B, int K, int H, int D,
+                       int L, int Q, int P, int dtype, void* stream);
+
+/* Backward. Replaces aclnnMultiScaleDeformableAttnGrad
+ * (mx_driving/csrc/MultiScaleDeformableAttn.cpp:115-116; device kernel
+ * kernels/multi_scale_deformable_attn/op_kernel/multi_scale_deformable_attn_grad.cpp:312-341).
+ * grad_value [B,K,H,D] is zero-filled on `stream` by this call and then
+ * accumulated with atomics in its own dtype; grad_sampling_loc and
+ * grad_attn_weight are fully written. */
+int msda_sm100_backward(const void* value, const int32_t* spatial_shapes,
+                        const int32_t* level_start_index, const void* sampling_locations,
+                        const void* attention_weights, const void* grad_output, void* grad_value,
+                        void* grad_sampling_loc, void* grad_attn_weight, int B, int K, int H,
+                        int D, int L, int Q, int P, int dtype, void* stream);
+
+/* Backward with fp32 accumulation of grad_value for the 16-bit dtypes, which is
+ * what the reference does for fp16 (it upcasts, runs the fp32 kernel and casts
+ * the three gradients back: MultiScaleDeformableAttn.cpp:103-113). `workspace`
+ * is caller-owned device memory of at least
+ * msda_sm100_backward_workspace_bytes() bytes, 16-byte aligned; its contents
+ * on entry do not matter and are undefined on return. For MSDA_F32 the
+ * workspace is not used (it may be NULL) and the call equals
+ * msda_sm100_backward. This takes the role of the reference's
+ * aclnn...GetWorkspaceSize + workspace tensor
+ * (include/csrc/OpApiCommon.h:585-610). */
+size_t msda_sm100_backward_workspace_bytes(int B, int K, int H, int D, int dtype);
+int msda_sm100_backward_ws(const void* value, const int32_t* spatial_shapes,
+                           const int32_t* level_start_index, const void* sampling_locations,
+                           const void* attention_weights, const void* grad_output,
+                           void* grad_value, void* grad_sampling_loc, void* grad_attn_weight,
+                           void* workspace, size_t workspace_bytes, int B, int K, int H, int D,
+                           int L, int Q, int P, int dtype, void* stream);
+
+/* Algorithmic (compulsory) bytes one call moves: every operand read once and
+ * every result written once. Used by benchmarks for the bandwidth roofline. */
+size_t msda_sm100_forward_bytes(int B, int K, int H, int D, int L, int Q, int P, int dtype);
+size_t msda_sm100_backward_bytes(int B, int K, int H, int D, int L, int Q, int P, int dtype);
+
+/* Sticky device-side status of the current device (bit 0: a staged
+ * location/weight tile did not arrive within the polling limit and the kernel
+ * fell back to direct loads). Synchronises the device. clear != 0 resets it.
+ * Returns the status word (>= 0) or a negative msda_status. */
+int msda_sm100_device_status(int clear);
+
+/* Tuning knobs, process-wide. Returns the previous value, or MSDA_ERR_DIMS for
+ * an unknown knob. Values < 0 only query.
+ *   MSDA_TUNE_STAGE          0 = direct loads of locations/weights,
+ *                            1 = bulk-copy (TMA) staging into shared memory (default)
+ *   MSDA_TUNE_CTAS_PER_SM    persistent CTAs per SM for the forward kernel (default 4)
+ *   MSDA_TUNE_CTAS_PER_SM_BWD  same for the backward kernel (default 4) */
+typedef enum msda_tune {
+    MSDA_TUNE_STAGE = 0,
+    MSDA_TUNE_CTAS_PER_SM = 1,
+    MSDA_TUNE_CTAS_PER_SM_BWD = 2
+} msda_tune;
+int msda_sm100_tune(int knob, int value);
+
+/* Number of kernels this library has launched since load (all threads). */
+long long msda_sm100_launch_count(void);
+
+const char* msda_sm100_strerror(int status);
+/* cudaError_t of the most recent failing runtime call on this thread (0 if none). */
+int msda_sm100_last_cuda_error(void);
+/* ABI version of this header: bumps on any signature change. */
+int msda_sm100_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MSDA_SM100_H_ */

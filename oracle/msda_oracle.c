@@ -1,0 +1,239 @@
+/* CPU oracle for multi-scale deformable attention (MSDA), forward and backward.
+ *
+ * TEST INFRASTRUCTURE ONLY. Nothing in the product path may call this file;
+ * it exists so that tests, the smoke check and the benchmark's CPU-baseline
+ * leg can check the CUDA kernels against an independent statement of the
+ * reference's algorithm.
+ *
+ * It restates, in double precision and plain loops, what the reference defines:
+ *   - the CPU golden of the reference's unit test: per level, bilinear
+ *     grid_sample(align_corners=False, padding_mode="zeros") at 2*loc-1, i.e.
+ *     pixel coordinate loc*size - 0.5, weighted by the attention weights and
+ *     summed over levels and points
+ *     (tests/torch/test_multi_scale_deformable_attn.py:34-64), gradients by
+ *     differentiating that expression (:67-76);
+ *   - the device kernel's explicit rules, which agree with the golden: a sample
+ *     counts only if x > -1, y > -1, x < W, y < H
+ *     (kernels/multi_scale_deformable_attn/op_kernel/msda.h:367-390); corner
+ *     existence and weights
+ *     (op_kernel/arch35/multi_scale_deformable_attn.cpp:59-78); gradient
+ *     algebra (op_kernel/arch35/multi_scale_deformable_attn_grad.cpp:105-142,
+ *     op_kernel/multi_scale_deformable_attn_grad.cpp:215-242).
+ * Parity is pinned: tests/golden/ holds outputs of the reference's own golden
+ * functions on seeded inputs, and tests/test_oracle.py checks this file
+ * against them.
+ *
+ * Layouts: value [B,K,H,D]; shapes [L,2] (H,W); starts [L];
+ * loc [B,Q,H,L,P,2] (x,y); attn [B,Q,H,L,P]; out/grad_out [B,Q,H*D].
+ * Inputs are float (already rounded to the dtype under test); results double.
+ */
+#include <math.h>
+#include <pthread.h>
+#include <stddef.h>
+#include <string.h>
+
+/* ---- a minimal parallel-for over [0, n) with POSIX threads ---------------- */
+static int g_threads = 1;
+void msda_oracle_set_threads(int n) { g_threads = n < 1 ? 1 : (n > 256 ? 256 : n); }
+int msda_oracle_get_threads(void) { return g_threads; }
+
+typedef void (*range_fn)(long begin, long end, void* ctx);
+typedef struct {
+    range_fn fn;
+    void* ctx;
+    long begin, end;
+} job_t;
+static void* job_main(void* arg) {
+    job_t* j = (job_t*)arg;
+    j->fn(j->begin, j->end, j->ctx);
+    return NULL;
+}
+static void parallel_for(long n, range_fn fn, void* ctx) {
+    int nt = g_threads;
+    if (nt > n) nt = (int)(n > 0 ? n : 1);
+    if (nt <= 1) {
+        fn(0, n, ctx);
+        return;
+    }
+    pthread_t th[256];
+    job_t jobs[256];
+    for (int i = 0; i < nt; ++i) {
+        jobs[i].fn = fn;
+        jobs[i].ctx = ctx;
+        jobs[i].begin = n * i / nt;
+        jobs[i].end = n * (i + 1) / nt;
+        if (pthread_create(&th[i], NULL, job_main, &jobs[i]) != 0) {
+            /* could not start a thread: run this share inline */
+            fn(jobs[i].begin, jobs[i].end, ctx);
+            th[i] = 0;
+            jobs[i].fn = NULL;
+        }
+    }
+    for (int i = 0; i < nt; ++i)
+        if (jobs[i].fn) pthread_join(th[i], NULL);
+}
+
+typedef struct {
+    const float *value, *loc, *attn, *grad_out;
+    const int *shapes, *starts;
+    double *out, *grad_value, *grad_loc, *grad_attn;
+    int B, K, H, D, L, Q, P;
+} args_t;
+
+typedef struct {
+    int ok[4];      /* corner exists */
+    size_t row[4];  /* pixel index y*W + x inside the level */
+    double w[4];    /* bilinear weight (no attention factor) */
+    double lw, lh;
+    int valid;
+} corners_t;
+
+static void corners(double lx, double ly, int Hl, int Wl, corners_t* c) {
+    const double x = lx * (double)Wl - 0.5;
+    const double y = ly * (double)Hl - 0.5;
+    memset(c, 0, sizeof(*c));
+    /* written so that NaN compares false, as in the reference */
+    c->valid = (x > -1.0) && (y > -1.0) && (x < (double)Wl) && (y < (double)Hl);
+    if (!c->valid) return;
+    const double x0f = floor(x), y0f = floor(y);
+    const long x0 = (long)x0f, y0 = (long)y0f, x1 = x0 + 1, y1 = y0 + 1;
+    const double lw = x - x0f, lh = y - y0f, hw = 1.0 - lw, hh = 1.0 - lh;
+    c->lw = lw;
+    c->lh = lh;
+    c->w[0] = hh * hw; c->w[1] = hh * lw; c->w[2] = lh * hw; c->w[3] = lh * lw;
+    c->ok[0] = (y0 >= 0 && x0 >= 0);
+    c->ok[1] = (y0 >= 0 && x1 <= Wl - 1);
+    c->ok[2] = (y1 <= Hl - 1 && x0 >= 0);
+    c->ok[3] = (y1 <= Hl - 1 && x1 <= Wl - 1);
+    if (c->ok[0]) c->row[0] = (size_t)(y0 * Wl + x0);
+    if (c->ok[1]) c->row[1] = (size_t)(y0 * Wl + x1);
+    if (c->ok[2]) c->row[2] = (size_t)(y1 * Wl + x0);
+    if (c->ok[3]) c->row[3] = (size_t)(y1 * Wl + x1);
+}
+
+static void forward_range(long begin, long end, void* ctx) {
+    const args_t* A = (const args_t*)ctx;
+    const float *value = A->value, *loc = A->loc, *attn = A->attn;
+    const int *shapes = A->shapes, *starts = A->starts;
+    double* out = A->out;
+    const int K = A->K, H = A->H, D = A->D, L = A->L, Q = A->Q, P = A->P;
+    for (long t = begin; t < end; ++t) {
+        const int h = (int)(t % H);
+        const int b = (int)(t / ((long)Q * H));
+        double* o = out + (size_t)t * D;
+        for (int d = 0; d < D; ++d) o[d] = 0.0;
+        for (int l = 0; l < L; ++l) {
+            const int Hl = shapes[2 * l], Wl = shapes[2 * l + 1];
+            for (int p = 0; p < P; ++p) {
+                const size_t si = ((size_t)t * L + l) * P + p;
+                corners_t c;
+                corners((double)loc[2 * si], (double)loc[2 * si + 1], Hl, Wl, &c);
+                if (!c.valid) continue;
+                const double a = (double)attn[si];
+                for (int k = 0; k < 4; ++k) {
+                    if (!c.ok[k]) continue;
+                    const float* v =
+                        value + (((size_t)b * K + starts[l] + c.row[k]) * H + h) * (size_t)D;
+                    const double w = c.w[k] * a;
+                    for (int d = 0; d < D; ++d) o[d] += w * (double)v[d];
+                }
+            }
+        }
+    }
+}
+
+void msda_oracle_forward(const float* value, const int* shapes, const int* starts,
+                         const float* loc, const float* attn, double* out, int B, int K, int H,
+                         int D, int L, int Q, int P) {
+    args_t A;
+    memset(&A, 0, sizeof(A));
+    A.value = value; A.shapes = shapes; A.starts = starts; A.loc = loc; A.attn = attn;
+    A.out = out;
+    A.B = B; A.K = K; A.H = H; A.D = D; A.L = L; A.Q = Q; A.P = P;
+    parallel_for((long)B * Q * H, forward_range, &A);
+}
+
+/* one (batch, head) pair owns a disjoint set of grad_value rows, so pairs can
+ * run on different threads without atomics */
+static void backward_range(long begin, long end, void* ctx) {
+    const args_t* A = (const args_t*)ctx;
+    const float *value = A->value, *loc = A->loc, *attn = A->attn, *grad_out = A->grad_out;
+    const int *shapes = A->shapes, *starts = A->starts;
+    double *grad_value = A->grad_value, *grad_loc = A->grad_loc, *grad_attn = A->grad_attn;
+    const int K = A->K, H = A->H, D = A->D, L = A->L, Q = A->Q, P = A->P;
+    for (long bh = begin; bh < end; ++bh) {
+        const int b = (int)(bh / H), h = (int)(bh % H);
+        for (int q = 0; q < Q; ++q) {
+            const size_t t = ((size_t)b * Q + q) * H + h;
+            const float* go = grad_out + t * D;
+            for (int l = 0; l < L; ++l) {
+                const int Hl = shapes[2 * l], Wl = shapes[2 * l + 1];
+                for (int p = 0; p < P; ++p) {
+                    const size_t si = (t * L + l) * P + p;
+                    corners_t c;
+                    corners((double)loc[2 * si], (double)loc[2 * si + 1], Hl, Wl, &c);
+                    double ga = 0.0, gx = 0.0, gy = 0.0;
+                    if (c.valid) {
+                        const double a = (double)attn[si];
+                        double S[4] = {0.0, 0.0, 0.0, 0.0};
+                        for (int k = 0; k < 4; ++k) {
+                            if (!c.ok[k]) continue;
+                            const size_t off =
+                                (((size_t)b * K + starts[l] + c.row[k]) * H + h) * (size_t)D;
+                            const float* v = value + off;
+                            double* gv = grad_value + off;
+                            const double w = c.w[k] * a;
+                            double s = 0.0;
+                            for (int d = 0; d < D; ++d) {
+                                gv[d] += w * (double)go[d];
+                                s += (double)v[d] * (double)go[d];
+                            }
+                            S[k] = s;
+                        }
+                        const double hw = 1.0 - c.lw, hh = 1.0 - c.lh;
+                        ga = c.w[0] * S[0] + c.w[1] * S[1] + c.w[2] * S[2] + c.w[3] * S[3];
+                        gx = (double)Wl * a * (hh * (S[1] - S[0]) + c.lh * (S[3] - S[2]));
+                        gy = (double)Hl * a * (hw * (S[2] - S[0]) + c.lw * (S[3] - S[1]));
+                    }
+                    grad_attn[si] = ga;
+                    grad_loc[2 * si] = gx;
+                    grad_loc[2 * si + 1] = gy;
+                }
+            }
+        }
+    }
+}
+
+void msda_oracle_backward(const float* value, const int* shapes, const int* starts,
+                          const float* loc, const float* attn, const float* grad_out,
+                          double* grad_value, double* grad_loc, double* grad_attn, int B, int K,
+                          int H, int D, int L, int Q, int P) {
+    const size_t nval = (size_t)B * K * H * D;
+    for (size_t i = 0; i < nval; ++i) grad_value[i] = 0.0;
+    args_t A;
+    memset(&A, 0, sizeof(A));
+    A.value = value; A.shapes = shapes; A.starts = starts; A.loc = loc; A.attn = attn;
+    A.grad_out = grad_out;
+    A.grad_value = grad_value; A.grad_loc = grad_loc; A.grad_attn = grad_attn;
+    A.B = B; A.K = K; A.H = H; A.D = D; A.L = L; A.Q = Q; A.P = P;
+    parallel_for((long)B * H, backward_range, &A);
+}
+
+/* Distance of every sample's pixel coordinates from the nearest cell boundary
+ * (an integer), min over x and y. grad_loc is discontinuous there (the two
+ * one-sided derivatives differ), so parity checks skip samples that sit within
+ * float rounding of a boundary. */
+void msda_oracle_kink_distance(const int* shapes, const float* loc, double* dist, int B, int H,
+                               int L, int Q, int P) {
+    const long ntask = (long)B * Q * H;
+    for (long t = 0; t < ntask; ++t)
+        for (int l = 0; l < L; ++l)
+            for (int p = 0; p < P; ++p) {
+                const size_t si = ((size_t)t * L + l) * P + p;
+                const double x = (double)loc[2 * si] * shapes[2 * l + 1] - 0.5;
+                const double y = (double)loc[2 * si + 1] * shapes[2 * l] - 0.5;
+                const double dx = fabs(x - nearbyint(x)), dy = fabs(y - nearbyint(y));
+                dist[si] = (dx < dy) ? dx : dy;
+                if (!(dist[si] == dist[si])) dist[si] = 0.0; /* NaN: treat as on a kink */
+            }
+}
