@@ -1,0 +1,429 @@
+#!/usr/bin/env python
+"""MSDA forward+backward benchmark on B200: samples/s and HBM roofline fraction.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--dtype D]
+    python bench.py --impl reference ...        # the CPU implementation of the path
+
+One "step" = one forward + one backward of multi-scale deformable attention
+over one batch of synthetic inputs with the shapes of BEVFormer-base spatial
+cross-attention (6 camera views x 2500 queries, 8 heads x 32 channels, 4 levels
+x 8 points, 30825 keys); a "sample" is one batch entry (one camera view).
+Prints ONE JSON line:
+
+  value        samples/s over all ranks, operands resident in HBM, calls through the C ABI
+  e2e          the same through the public Python API with HOST (pinned) operands:
+               host->device copies of the inputs and device->host copies of all four
+               results are inside the timed region
+  roofline     the backward kernel (the dominant one): algorithmic bytes per launch /
+               CUDA-event time of that kernel alone, against the measured copy bandwidth
+  cpu_baseline the CPU restatement of the reference's path timed on the host cores
+
+With N > 1 (under torchrun, one rank per GPU) the batch is sharded: every rank
+holds its own 6 samples; there is no data-path collective, so scaling is weak.
+`--shard query` instead splits ONE batch's queries over the ranks and all-reduces
+grad_value with NCCL (strong scaling; reported with "scaling": "strong").
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "msda_fwd_bwd_samples_per_s"
+UNIT = "samples/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--workload", default="bevformer_sca")
+    ap.add_argument("--dtype", default="float32", choices=["float32", "float16", "bfloat16"])
+    ap.add_argument("--shard", default="batch", choices=["batch", "query"])
+    ap.add_argument("--stage", type=int, default=None, help="tuning: 0/1 bulk-copy staging")
+    ap.add_argument("--ctas-per-sm", type=int, default=None, help="tuning: forward kernel")
+    ap.add_argument("--ctas-per-sm-bwd", type=int, default=None, help="tuning: backward kernel")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0,
+                    help="budget of the CPU baseline sample")
+    return ap.parse_args()
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        mhz, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                mhz.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None,
+                "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(mhz), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- CPU baseline
+def cpu_baseline(workload, seconds):
+    """Times the CPU restatements of the reference's path on a bounded sample: whole batch
+    entries of the same workload, repeated until about `seconds` have passed. Two
+    implementations are timed — the PyTorch port of the reference's golden
+    (grid_sample + autograd, float32, all torch threads) and the threaded C oracle
+    (float64) — and the faster one is reported."""
+    import torch
+    from drivingsdk_b200 import workloads
+    from oracle import golden_torch, msda_oracle
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    msda_oracle.set_threads(cores)
+    sample_b = min(workload.B, 2)
+    w = workload.with_batch(sample_b)
+    inp = workloads.make_inputs(w)
+    n = lambda k: inp[k].numpy()
+
+    def run_torch():
+        golden_torch.msda_forward_backward(inp["value"], inp["shapes"], inp["loc"], inp["attn"],
+                                           inp["grad_out"])
+
+    def run_c():
+        msda_oracle.forward(n("value"), n("shapes"), n("starts"), n("loc"), n("attn"))
+        msda_oracle.backward(n("value"), n("shapes"), n("starts"), n("loc"), n("attn"),
+                             n("grad_out"))
+
+    results = {}
+    for name, fn in (("torch_port_f32", run_torch), ("c_oracle_f64", run_c)):
+        fn()  # warm-up
+        t0 = time.perf_counter()
+        reps = 0
+        while True:
+            fn()
+            reps += 1
+            if time.perf_counter() - t0 > seconds / 2 or reps >= 50:
+                break
+        dt = time.perf_counter() - t0
+        results[name] = sample_b * reps / dt
+    best = max(results, key=results.get)
+    return {"value": results[best], "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{sample_b} of {workload.B} batch entries of {workload.name}, fwd+bwd, "
+                      f"fastest of {{{', '.join(f'{k}: {v:.2f}' for k, v in results.items())}}} "
+                      f"({best})"}
+
+
+def run_reference_arm(args):
+    """--impl reference: the reference's CPU implementation of the path on the host cores.
+    Its device kernels need the vendor's NPU toolchain and cannot run here, and its CPU
+    golden is Python test code that does not travel with this tree, so the timed code is
+    the committed restatement of that golden (oracle/golden_torch.py, oracle/msda_oracle.c)."""
+    from drivingsdk_b200 import workloads
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w = workloads.WORKLOADS[args.workload]
+    seconds = max(4.0, min(60.0, 2.0 * (args.steps + args.warmup)))
+    base = cpu_baseline(w, seconds)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * w.B / base["value"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w.name, "B": w.B, "Q": w.Q, "H": w.H, "D": w.D, "K": w.K,
+                   "L": w.L, "P": w.P},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------- native arm
+def run_native(args):
+    import torch
+    import torch.distributed as dist
+
+    from drivingsdk_b200 import capi, workloads
+    import drivingsdk_b200 as sdk
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the native arm has no CPU fallback")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("bench.py: --gpus N > 1 must be launched with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    lib = capi.load()
+    for knob, val in ((capi.TUNE_STAGE, args.stage), (capi.TUNE_CTAS_PER_SM, args.ctas_per_sm),
+                      (capi.TUNE_CTAS_PER_SM_BWD, args.ctas_per_sm_bwd)):
+        if val is not None:
+            lib.msda_sm100_tune(knob, val)
+    dtype = getattr(torch, args.dtype)
+    code = capi.dtype_code(dtype)
+    esize = 4 if dtype == torch.float32 else 2
+    w = workloads.WORKLOADS[args.workload]
+    query_shard = args.shard == "query" and world > 1
+    if query_shard:
+        from drivingsdk_b200 import dist as sdist
+        q0, q1 = sdist.query_range(w.Q, world, rank)
+        w_local = w.with_queries(q1 - q0)
+    else:
+        w_local = w
+
+    # two rotating input sets; one step already touches far more than the 126 MB L2
+    NSETS = 2
+    sets, host_sets = [], []
+    shapes_i32 = starts_i32 = None
+    for i in range(NSETS):
+        inp = workloads.make_inputs(w_local, dtype, seed_offset=1000 * rank + i)
+        host = {k: inp[k].to(dtype).pin_memory() for k in ("value", "loc", "attn", "grad_out")}
+        host_sets.append(host)
+        sets.append({k: v.to(dev) for k, v in host.items()})
+        if shapes_i32 is None:
+            shapes_i32 = inp["shapes"].to(torch.int32).to(dev)
+            starts_i32 = inp["starts"].to(torch.int32).to(dev)
+    B, K, H, D, L, Q, P = w_local.B, w_local.K, w_local.H, w_local.D, w_local.L, w_local.Q, w_local.P
+    dims = (B, K, H, D, L, Q, P)
+    out = torch.empty(B, Q, H * D, device=dev, dtype=dtype)
+    gv = torch.empty(B, K, H, D, device=dev, dtype=dtype)
+    gl = torch.empty(B, Q, H, L, P, 2, device=dev, dtype=dtype)
+    ga = torch.empty(B, Q, H, L, P, device=dev, dtype=dtype)
+    ws_bytes = lib.msda_sm100_backward_workspace_bytes(B, K, H, D, code)
+    ws = torch.empty(max(ws_bytes, 16), device=dev, dtype=torch.uint8)
+    stream = torch.cuda.current_stream()
+
+    def step_c_abi(s):
+        capi.check(lib.msda_sm100_forward(
+            s["value"].data_ptr(), shapes_i32.data_ptr(), starts_i32.data_ptr(),
+            s["loc"].data_ptr(), s["attn"].data_ptr(), out.data_ptr(), *dims, code,
+            stream.cuda_stream), "forward")
+        capi.check(lib.msda_sm100_backward_ws(
+            s["value"].data_ptr(), shapes_i32.data_ptr(), starts_i32.data_ptr(),
+            s["loc"].data_ptr(), s["attn"].data_ptr(), s["grad_out"].data_ptr(), gv.data_ptr(),
+            gl.data_ptr(), ga.data_ptr(), ws.data_ptr(), ws_bytes, *dims, code,
+            stream.cuda_stream), "backward")
+        if query_shard:
+            dist.all_reduce(gv)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---------------- device-resident timing (the `value`) -------------------------
+    for i in range(args.warmup):
+        step_c_abi(sets[i % NSETS])
+    barrier()
+    K_steps = args.steps
+    # CUDA events the library records immediately around its forward and backward kernel
+    # launches (on the launch stream), one quadruple per timed step.
+    kev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(K_steps)]
+    for quad in kev:
+        for e in quad:
+            e.record(stream)  # materialise the underlying cudaEvent_t
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    launches0 = lib.msda_sm100_launch_count()
+    barrier()
+    ev0.record(stream)
+    for i in range(K_steps):
+        lib.msda_sm100_profile_events(*[e.cuda_event for e in kev[i]])
+        step_c_abi(sets[i % NSETS])
+    ev1.record(stream)
+    lib.msda_sm100_profile_events(None, None, None, None)
+    barrier()
+    total_ms = ev0.elapsed_time(ev1)
+    launches = lib.msda_sm100_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    fwd_ms = sum(q[0].elapsed_time(q[1]) for q in kev) / K_steps
+    bwd_ms = sum(q[2].elapsed_time(q[3]) for q in kev) / K_steps
+
+    t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms / K_steps
+    global_samples = w.B if query_shard else w.B * world
+    value = global_samples / (ms_per_step * 1e-3)
+
+    # ---------------- end-to-end through the Python API with host operands ----------
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(sdk, host_sets, shapes_i32, starts_i32, dev, dtype, world, query_shard,
+                      max(3, min(K_steps, 10)), global_samples, barrier)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = load_peaks()
+    fb, bb = workloads.compulsory_bytes(w_local, esize)
+    bwd_gbs = bb / (bwd_ms * 1e-3) / 1e9
+    fwd_gbs = fb / (fwd_ms * 1e-3) / 1e9
+    step_gbs = (fb + bb) / (ms_per_step * 1e-3) / 1e9
+    roofline = {
+        "bound": "hbm", "kernel": "msda_bwd_kernel", "achieved": bwd_gbs, "peak": peak,
+        "unit": "GB/s", "frac": bwd_gbs / peak, "traffic": TRAFFIC_BYTES.get((w.name, args.dtype)),
+        "peak_kind": peak_kind, "algorithmic_bytes": bb, "kernel_ms": bwd_ms,
+        "forward": {"kernel": "msda_fwd_kernel", "achieved": fwd_gbs, "frac": fwd_gbs / peak,
+                    "algorithmic_bytes": fb, "kernel_ms": fwd_ms},
+        "step": {"achieved": step_gbs, "frac": step_gbs / peak, "algorithmic_bytes": fb + bb},
+    }
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K_steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if query_shard else "weak", "vs_baseline": None,
+        "dtype": {"float32": "f32", "float16": "f16", "bfloat16": "bf16"}[args.dtype],
+        "data": "synthetic",
+        "config": {"workload": w.name, "B_per_rank": w_local.B, "Q_per_rank": w_local.Q,
+                   "H": H, "D": D, "K": K, "L": L, "P": P,
+                   "sharding": ("query+allreduce" if query_shard else "batch"),
+                   "l2": f"{NSETS} rotating input sets; one step moves {(fb + bb) / 1e6:.0f} MB "
+                         "of operands (> 126 MB L2)"},
+        "roofline": roofline, "clocks": clocks, "gpu_launches": int(launches) * world,
+        "tuning": {"stage": lib.msda_sm100_tune(capi.TUNE_STAGE, -1),
+                   "ctas_per_sm": lib.msda_sm100_tune(capi.TUNE_CTAS_PER_SM, -1),
+                   "ctas_per_sm_bwd": lib.msda_sm100_tune(capi.TUNE_CTAS_PER_SM_BWD, -1)},
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(w, args.cpu_seconds)
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ncu dram__bytes_read.sum + dram__bytes_write.sum of one backward-kernel launch, per
+# (workload, dtype); filled from the captures summarised under profiles/.
+TRAFFIC_BYTES = {}
+
+
+def run_e2e(sdk, host_sets, shapes_i32, starts_i32, dev, dtype, world, query_shard, steps,
+            global_samples, barrier):
+    """Public API, host operands: per step, H2D of value/locations/weights/grad_output from
+    pinned memory, forward, backward, D2H of output and the three gradients."""
+    import torch
+    import torch.distributed as dist
+    h0 = host_sets[0]
+    d_in = {k: torch.empty_like(v, device=dev) for k, v in h0.items()}
+    h_out = None
+    h2d = sum(v.numel() * v.element_size() for v in h0.values())
+
+    def one_step(host):
+        nonlocal h_out
+        for k in d_in:
+            d_in[k].copy_(host[k], non_blocking=True)
+        value = d_in["value"].detach().requires_grad_(True)
+        loc = d_in["loc"].detach().requires_grad_(True)
+        attn = d_in["attn"].detach().requires_grad_(True)
+        out = sdk.multi_scale_deformable_attn(value, shapes_i32, starts_i32, loc, attn)
+        out.backward(d_in["grad_out"])
+        gvalue = value.grad
+        if query_shard:
+            dist.all_reduce(gvalue)
+        res = (out.detach(), gvalue, loc.grad, attn.grad)
+        if h_out is None:
+            h_out = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res]
+        for h, r in zip(h_out, res):
+            h.copy_(r, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(2):
+        one_step(host_sets[i % len(host_sets)])
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        one_step(host_sets[i % len(host_sets)])
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / steps
+    d2h = sum(h.numel() * h.element_size() for h in h_out)
+    return {"value": global_samples / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms,
+            "steps": steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_native(args)
+
+
+if __name__ == "__main__":
+    main()

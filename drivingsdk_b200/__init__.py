@@ -1,0 +1,39 @@
+"""B200-native (sm_100a) multi-scale deformable attention behind DrivingSDK's API.
+
+Public surface, same names as the reference package exports for this path
+(mx_driving/__init__.py:106-110):
+
+    multi_scale_deformable_attn(value, value_spatial_shapes, value_level_start_index,
+                                sampling_locations, attention_weights) -> Tensor
+    MultiScaleDeformableAttnFunction          torch.autograd.Function
+    npu_multi_scale_deformable_attn_function  deprecated alias
+    patcher                                   the mmcv hook (default_patcher, MSDA, ...)
+
+The operator names are resolved on first use, so that the patcher (pure Python)
+can be imported on a machine without the compiled extension. Using an operator
+without the extension raises ImportError: there is no CPU or eager fallback.
+"""
+import importlib
+
+__version__ = "0.1.0"
+
+_OP_NAMES = (
+    "multi_scale_deformable_attn",
+    "MultiScaleDeformableAttnFunction",
+    "npu_multi_scale_deformable_attn_function",
+)
+
+__all__ = list(_OP_NAMES) + ["patcher", "default_patcher", "dist"]
+
+
+def __getattr__(name):
+    if name in _OP_NAMES:
+        mod = importlib.import_module(__name__ + ".ops.multi_scale_deformable_attn")
+        return getattr(mod, name)
+    if name == "_C":
+        return importlib.import_module(__name__ + "._C")
+    if name in ("patcher", "dist", "capi", "ops"):
+        return importlib.import_module(__name__ + "." + name)
+    if name == "default_patcher":
+        return importlib.import_module(__name__ + ".patcher").default_patcher
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -1,0 +1,66 @@
+"""ctypes view of the C-ABI library (``libmsda_sm100.so``, include/msda_sm100.h).
+
+This is the same boundary a non-Python host would bind. The torch extension
+``_C`` links against the library directly; this module exists for callers that
+hold raw device pointers (tests, the benchmark's kernel-only timing, other
+runtimes). Loading fails loudly when the library has not been built.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmsda_sm100.so")
+
+F32, F16, BF16 = 0, 1, 2
+TUNE_STAGE, TUNE_CTAS_PER_SM, TUNE_CTAS_PER_SM_BWD = 0, 1, 2
+
+# name -> (restype, argtypes); kept in step with include/msda_sm100.h
+_vp, _ip, _i, _sz = ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+_DIMS7 = [_i] * 7
+SIGNATURES = {
+    "msda_sm100_forward": (_i, [_vp, _ip, _ip, _vp, _vp, _vp] + _DIMS7 + [_i, _vp]),
+    "msda_sm100_backward": (_i, [_vp, _ip, _ip, _vp, _vp, _vp, _vp, _vp, _vp] + _DIMS7 + [_i, _vp]),
+    "msda_sm100_backward_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "msda_sm100_backward_ws": (_i, [_vp, _ip, _ip, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz]
+                               + _DIMS7 + [_i, _vp]),
+    "msda_sm100_forward_bytes": (_sz, _DIMS7 + [_i]),
+    "msda_sm100_backward_bytes": (_sz, _DIMS7 + [_i]),
+    "msda_sm100_device_status": (_i, [_i]),
+    "msda_sm100_tune": (_i, [_i, _i]),
+    "msda_sm100_profile_events": (None, [_vp, _vp, _vp, _vp]),
+    "msda_sm100_launch_count": (ctypes.c_longlong, []),
+    "msda_sm100_strerror": (ctypes.c_char_p, [_i]),
+    "msda_sm100_last_cuda_error": (_i, []),
+    "msda_sm100_abi_version": (_i, []),
+}
+
+_lib = None
+
+
+def load():
+    """Returns the loaded library with argument types set; raises if it is not built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is not built; run `python -m drivingsdk_b200.build`. "
+                "There is no CPU fallback.")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def dtype_code(torch_dtype) -> int:
+    import torch
+    return {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}[torch_dtype]
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        lib = load()
+        msg = lib.msda_sm100_strerror(rc).decode()
+        raise RuntimeError(f"{what}: {msg} (status {rc}, cuda error {lib.msda_sm100_last_cuda_error()})")

@@ -1,0 +1,189 @@
+// Torch extension `_C`: the two entry points the reference's extension exposes
+// for this path (mx_driving/csrc/pybind.cpp:110-111, include/csrc/functions.h:58-64)
+//     multi_scale_deformable_attn(value, shapes, level_start, loc, attn) -> Tensor
+//     multi_scale_deformable_attn_backward(value, shapes, level_start, loc, attn,
+//                                          grad_output) -> (Tensor, Tensor, Tensor)
+// with the reference binding's checks and messages
+// (mx_driving/csrc/MultiScaleDeformableAttn.cpp:28-118). Results are allocated
+// here with torch's caching allocator and the work is enqueued on the current
+// CUDA stream through the C ABI in include/msda_sm100.h. There is no CPU path:
+// non-CUDA tensors are an error.
+//
+// Differences from the reference binding, all on purpose:
+//   * bfloat16 is accepted next to float16/float32;
+//   * 16-bit inputs are not upcast to fp32 copies: the kernels read 16-bit
+//     operands, do fp32 arithmetic, accumulate grad_value in an fp32 workspace
+//     and write 16-bit results (same numerics as the reference's
+//     upcast-run-downcast, without the extra passes);
+//   * the number of rows of value_spatial_shapes must equal the level dimension
+//     of attention_weights (the reference tolerates fewer rows and zero-fills;
+//     no test of the reference exercises that).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <tuple>
+
+#include "../../include/msda_sm100.h"
+
+namespace {
+
+constexpr int64_t kBatch = 0, kQuery = 1, kHead = 2, kEmbed = 3, kLevel = 3, kPoint = 4;
+
+bool is_float_kind(at::ScalarType t) {
+    return t == at::kHalf || t == at::kFloat || t == at::kBFloat16;
+}
+
+int dtype_code(at::ScalarType t) {
+    if (t == at::kFloat) return MSDA_F32;
+    if (t == at::kHalf) return MSDA_F16;
+    return MSDA_BF16;
+}
+
+struct Dims {
+    int B, K, H, D, L, Q, P;
+};
+
+Dims check_inputs(const at::Tensor& value, const at::Tensor& shapes, const at::Tensor& starts,
+                  const at::Tensor& loc, const at::Tensor& attn) {
+    TORCH_CHECK(is_float_kind(value.scalar_type()),
+                "value: float16, bfloat16 or float32 tensor expected but got a tensor with dtype: ",
+                value.scalar_type());
+    TORCH_CHECK(shapes.scalar_type() == at::kInt,
+                "value_spatial_shapes: int32 tensor expected but got a tensor with dtype: ",
+                shapes.scalar_type());
+    TORCH_CHECK(starts.scalar_type() == at::kInt,
+                "value_level_start_index: int32 tensor expected but got a tensor with dtype: ",
+                starts.scalar_type());
+    TORCH_CHECK(is_float_kind(loc.scalar_type()),
+                "sampling_locations: float16, bfloat16 or float32 tensor expected but got a tensor "
+                "with dtype: ", loc.scalar_type());
+    TORCH_CHECK(is_float_kind(attn.scalar_type()),
+                "attention_weights: float16, bfloat16 or float32 tensor expected but got a tensor "
+                "with dtype: ", attn.scalar_type());
+    TORCH_CHECK(value.is_cuda() && loc.is_cuda() && attn.is_cuda(),
+                "multi_scale_deformable_attn: value, sampling_locations and attention_weights "
+                "must be CUDA tensors (this build has no CPU path)");
+    TORCH_CHECK(loc.scalar_type() == value.scalar_type() && attn.scalar_type() == value.scalar_type(),
+                "sampling_locations and attention_weights must have value's dtype");
+    TORCH_CHECK(value.dim() == 4, "value must be [bs, num_keys, num_heads, embed_dims]");
+    TORCH_CHECK(loc.dim() == 6 && loc.size(5) == 2,
+                "sampling_locations must be [bs, num_queries, num_heads, num_levels, num_points, 2]");
+    TORCH_CHECK(attn.dim() == 5,
+                "attention_weights must be [bs, num_queries, num_heads, num_levels, num_points]");
+    TORCH_CHECK(value.size(kEmbed) <= 256,
+                "The number of embedding dimensions should be less than or equal to 256");
+    TORCH_CHECK(loc.size(kLevel) * loc.size(kPoint) <= 64,
+                "The product of the number of levels and the number of points should be less than "
+                "or equal to 64");
+    Dims d;
+    d.B = static_cast<int>(value.size(0));
+    d.K = static_cast<int>(value.size(1));
+    d.H = static_cast<int>(value.size(2));
+    d.D = static_cast<int>(value.size(3));
+    d.Q = static_cast<int>(loc.size(kQuery));
+    d.L = static_cast<int>(loc.size(kLevel));
+    d.P = static_cast<int>(loc.size(kPoint));
+    TORCH_CHECK(loc.size(kBatch) == d.B && loc.size(kHead) == d.H,
+                "sampling_locations batch/head sizes do not match value");
+    TORCH_CHECK(attn.size(0) == d.B && attn.size(1) == d.Q && attn.size(2) == d.H &&
+                    attn.size(3) == d.L && attn.size(4) == d.P,
+                "attention_weights shape does not match sampling_locations");
+    TORCH_CHECK(shapes.numel() == 2 * d.L && starts.numel() == d.L,
+                "value_spatial_shapes must have one (H, W) row and value_level_start_index one "
+                "entry per level of attention_weights");
+    TORCH_CHECK(shapes.device() == starts.device(),
+                "value_spatial_shapes and value_level_start_index must live on the same device");
+    return d;
+}
+
+void raise_on_error(int rc, const char* what) {
+    if (rc == MSDA_OK) return;
+    if (rc == MSDA_ERR_CUDA) {
+        const auto ce = static_cast<cudaError_t>(msda_sm100_last_cuda_error());
+        TORCH_CHECK(false, what, ": CUDA error: ", cudaGetErrorString(ce));
+    }
+    TORCH_CHECK(false, what, ": ", msda_sm100_strerror(rc));
+}
+
+}  // namespace
+
+at::Tensor multi_scale_deformable_attn(const at::Tensor& value_in, const at::Tensor& shapes_in,
+                                       const at::Tensor& starts_in, const at::Tensor& loc_in,
+                                       const at::Tensor& attn_in) {
+    const Dims d = check_inputs(value_in, shapes_in, starts_in, loc_in, attn_in);
+    const c10::cuda::CUDAGuard guard(value_in.device());
+    // the reference op marks its inputs auto-contiguous
+    // (kernels/multi_scale_deformable_attn/op_host/multi_scale_deformable_attn.cpp:151-180)
+    const at::Tensor value = value_in.contiguous();
+    const at::Tensor loc = loc_in.contiguous();
+    const at::Tensor attn = attn_in.contiguous();
+    const at::Tensor shapes = shapes_in.contiguous();
+    const at::Tensor starts = starts_in.contiguous();
+
+    at::Tensor out = at::empty({d.B, d.Q, static_cast<int64_t>(d.H) * d.D}, value.options());
+    if (out.numel() == 0) return out;
+    const int rc = msda_sm100_forward(
+        value.data_ptr(), shapes.data_ptr<int32_t>(), starts.data_ptr<int32_t>(), loc.data_ptr(),
+        attn.data_ptr(), out.data_ptr(), d.B, d.K, d.H, d.D, d.L, d.Q, d.P,
+        dtype_code(value.scalar_type()), at::cuda::getCurrentCUDAStream().stream());
+    raise_on_error(rc, "multi_scale_deformable_attn");
+    return out;
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> multi_scale_deformable_attn_backward(
+    const at::Tensor& value_in, const at::Tensor& shapes_in, const at::Tensor& starts_in,
+    const at::Tensor& loc_in, const at::Tensor& attn_in, const at::Tensor& grad_out_in) {
+    const Dims d = check_inputs(value_in, shapes_in, starts_in, loc_in, attn_in);
+    TORCH_CHECK(is_float_kind(grad_out_in.scalar_type()),
+                "grad_output: float16, bfloat16 or float32 tensor expected but got a tensor with "
+                "dtype: ", grad_out_in.scalar_type());
+    TORCH_CHECK(grad_out_in.is_cuda(), "grad_output must be a CUDA tensor");
+    TORCH_CHECK(grad_out_in.numel() == static_cast<int64_t>(d.B) * d.Q * d.H * d.D,
+                "grad_output must be [bs, num_queries, num_heads * embed_dims]");
+    const c10::cuda::CUDAGuard guard(value_in.device());
+    const at::Tensor value = value_in.contiguous();
+    const at::Tensor loc = loc_in.contiguous();
+    const at::Tensor attn = attn_in.contiguous();
+    const at::Tensor shapes = shapes_in.contiguous();
+    const at::Tensor starts = starts_in.contiguous();
+    const at::Tensor grad_out = grad_out_in.to(value.scalar_type()).contiguous();
+
+    // grad_value is zero-filled by the C-ABI call on the same stream; the other
+    // two are fully written by the kernel (the reference allocates them with
+    // empty_like too, MultiScaleDeformableAttn.cpp:93-95).
+    at::Tensor grad_value = at::empty_like(value);
+    at::Tensor grad_loc = at::empty_like(loc);
+    at::Tensor grad_attn = at::empty_like(attn);
+    if (value.numel() == 0 || loc.numel() == 0) {
+        grad_value.zero_();
+        return std::make_tuple(grad_value, grad_loc, grad_attn);
+    }
+    const int dt = dtype_code(value.scalar_type());
+    at::Tensor workspace;
+    void* ws_ptr = nullptr;
+    size_t ws_bytes = msda_sm100_backward_workspace_bytes(d.B, d.K, d.H, d.D, dt);
+    if (ws_bytes > 0) {
+        workspace = at::empty({static_cast<int64_t>(ws_bytes / sizeof(float))},
+                              value.options().dtype(at::kFloat));
+        ws_ptr = workspace.data_ptr();
+    }
+    const int rc = msda_sm100_backward_ws(
+        value.data_ptr(), shapes.data_ptr<int32_t>(), starts.data_ptr<int32_t>(), loc.data_ptr(),
+        attn.data_ptr(), grad_out.data_ptr(), grad_value.data_ptr(), grad_loc.data_ptr(),
+        grad_attn.data_ptr(), ws_ptr, ws_bytes, d.B, d.K, d.H, d.D, d.L, d.Q, d.P, dt,
+        at::cuda::getCurrentCUDAStream().stream());
+    raise_on_error(rc, "multi_scale_deformable_attn_backward");
+    return std::make_tuple(grad_value, grad_loc, grad_attn);
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.doc() = "sm_100a multi-scale deformable attention (drop-in for mx_driving._C on this path)";
+    m.def("multi_scale_deformable_attn", &multi_scale_deformable_attn,
+          "MSDA forward: (value, value_spatial_shapes, value_level_start_index, "
+          "sampling_locations, attention_weights) -> output");
+    m.def("multi_scale_deformable_attn_backward", &multi_scale_deformable_attn_backward,
+          "MSDA backward: (value, value_spatial_shapes, value_level_start_index, "
+          "sampling_locations, attention_weights, grad_output) -> "
+          "(grad_value, grad_sampling_loc, grad_attn_weight)");
+}

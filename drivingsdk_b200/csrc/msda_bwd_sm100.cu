@@ -33,6 +33,13 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
     constexpr int PART = (LPR < kPartMax) ? LPR : kPartMax;  // partials per slot
     constexpr int SSTRIDE = 4 * PART + 1;                    // per-sample stride (bank spread)
     constexpr int UNROLL = (RPI >= 16) ? 2 : 4;
+    // 16-bit operands accumulated in fp32: a lane's 16-byte piece of the value row is 8
+    // channels, i.e. 32 bytes of the fp32 accumulation row. Two reductions at +0 and +16
+    // bytes of that span would touch every 32-byte sector of the row with half a sector each
+    // time; instead lane j adds the float4 pieces j and LPR + j, so each instruction covers
+    // whole sectors. The scatter does not depend on the value data, so any lane may add any
+    // channels — it only needs grad_out for those channels (gred below).
+    constexpr bool SPLIT_RED = !SCALAR && sizeof(T) == 2 && sizeof(TG) == 4;
 
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5;
@@ -154,6 +161,27 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                             go[k][0] = (c < D) ? Elem<T>::to_f(gout[obase + c]) : 0.f;
                         }
                     }
+                    float gred[2][4];
+                    if constexpr (SPLIT_RED) {
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            const uint2 raw = *reinterpret_cast<const uint2*>(
+                                gout + obase + (half * LPR + j) * 4);
+                            const uint32_t wds[2] = {raw.x, raw.y};
+#pragma unroll
+                            for (int i = 0; i < 2; ++i) {
+                                if constexpr (sizeof(T) == 2) {
+                                    T lo, hi;
+                                    const uint16_t l16 = static_cast<uint16_t>(wds[i] & 0xffffu);
+                                    const uint16_t h16 = static_cast<uint16_t>(wds[i] >> 16);
+                                    lo = *reinterpret_cast<const T*>(&l16);
+                                    hi = *reinterpret_cast<const T*>(&h16);
+                                    gred[half][2 * i] = Elem<T>::to_f(lo);
+                                    gred[half][2 * i + 1] = Elem<T>::to_f(hi);
+                                }
+                            }
+                        }
+                    }
 #pragma unroll 1
                     for (int base = slot_begin; base < slot_end; base += RPI * UNROLL) {
                         int r[UNROLL];
@@ -185,12 +213,26 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
 #pragma unroll
                                 for (int k = 0; k < NV; ++k) {
                                     if (r[u] >= 0) {
-                                        float contrib[VEC];
+                                        if constexpr (SPLIT_RED) {
+                                            float* row =
+                                                reinterpret_cast<float*>(gval) +
+                                                static_cast<size_t>(r[u]) * D;
+                                            red_add_f32x4(row + j * 4, w[u] * gred[0][0],
+                                                          w[u] * gred[0][1], w[u] * gred[0][2],
+                                                          w[u] * gred[0][3]);
+                                            red_add_f32x4(row + (LPR + j) * 4, w[u] * gred[1][0],
+                                                          w[u] * gred[1][1], w[u] * gred[1][2],
+                                                          w[u] * gred[1][3]);
+                                        } else {
+                                            float contrib[VEC];
 #pragma unroll
-                                        for (int e = 0; e < VEC; ++e) contrib[e] = w[u] * go[k][e];
-                                        red_add_vec<TG, VEC>(gval + static_cast<size_t>(r[u]) * D +
-                                                                 (j + k * LPR) * VEC,
-                                                             contrib);
+                                            for (int e = 0; e < VEC; ++e)
+                                                contrib[e] = w[u] * go[k][e];
+                                            red_add_vec<TG, VEC>(
+                                                gval + static_cast<size_t>(r[u]) * D +
+                                                    (j + k * LPR) * VEC,
+                                                contrib);
+                                        }
                                     }
                                     float f[VEC];
                                     unpack16<T>(raw[u][k], f);

@@ -24,6 +24,11 @@ std::atomic<int> g_tune_cps_fwd{4};
 std::atomic<int> g_tune_cps_bwd{4};
 std::atomic<long long> g_launches{0};
 thread_local int t_last_cuda_error = 0;
+thread_local cudaEvent_t t_prof[4] = {nullptr, nullptr, nullptr, nullptr};
+
+void prof_record(int which, cudaStream_t stream) {
+    if (t_prof[which] != nullptr) cudaEventRecord(t_prof[which], stream);
+}
 
 struct DeviceInfo {
     std::atomic<int> ready{0};
@@ -191,8 +196,10 @@ int backward_impl(const void* value, const int32_t* shapes, const int32_t* start
 
     cudaError_t ce = cudaMemsetAsync(acc, 0, acc_bytes, stream);
     if (ce != cudaSuccess) return fail_cuda(ce);
+    prof_record(2, stream);
     ce = msda::launch_backward(p, dtype, acc_f32 ? 1 : 0, rp, grid_for(p, dev, g_tune_cps_bwd.load()),
                                stream);
+    prof_record(3, stream);
     if (ce != cudaSuccess) return fail_cuda(ce);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     if (acc_f32) {
@@ -227,8 +234,11 @@ int msda_sm100_forward(const void* value, const int32_t* spatial_shapes,
     if (!aligned_to(output, elem_size(dtype))) return MSDA_ERR_ALIGN;
     p.out = output;
     const RowPlan rp = plan_rows(D, dtype, aligned_to(value, 16) && aligned_to(output, 16));
-    cudaError_t ce = msda::launch_forward(p, dtype, rp, grid_for(p, dev, g_tune_cps_fwd.load()),
-                                          static_cast<cudaStream_t>(stream_v));
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    prof_record(0, stream);
+    cudaError_t ce =
+        msda::launch_forward(p, dtype, rp, grid_for(p, dev, g_tune_cps_fwd.load()), stream);
+    prof_record(1, stream);
     if (ce != cudaSuccess) return fail_cuda(ce);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return MSDA_OK;
@@ -303,6 +313,13 @@ int msda_sm100_tune(int knob, int value) {
     }
     if (value < 0) return target->load();
     return target->exchange(value);
+}
+
+void msda_sm100_profile_events(void* fwd_start, void* fwd_stop, void* bwd_start, void* bwd_stop) {
+    t_prof[0] = static_cast<cudaEvent_t>(fwd_start);
+    t_prof[1] = static_cast<cudaEvent_t>(fwd_stop);
+    t_prof[2] = static_cast<cudaEvent_t>(bwd_start);
+    t_prof[3] = static_cast<cudaEvent_t>(bwd_stop);
 }
 
 long long msda_sm100_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -28,7 +28,7 @@ constexpr int kWarpsPerCta = 8;
 constexpr int kThreadsPerCta = kWarpsPerCta * 32;
 constexpr int kChunk = 32;          // samples handled by one warp pass
 constexpr int kSlots = 4 * kChunk;  // (sample, corner) pairs per warp pass
-constexpr int kSpinLimit = 1 << 22; // bound on mbarrier polling
+constexpr int kSpinLimit = 1 << 18; // bound on mbarrier polling
 
 // Device status bits, sticky until read by msda_sm100_device_status().
 constexpr int kStatusStageTimeout = 1;  // a staged tile never arrived
@@ -284,8 +284,13 @@ __device__ __forceinline__ void sample_setup(float lx, float ly, float a, int Wl
     const bool valid = (x > -1.f) && (y > -1.f) && (x < wf) && (y < hf);
     const float x0f = floorf(x);
     const float y0f = floorf(y);
-    const float lw = x - x0f;
-    const float lh = y - y0f;
+    // Fractions from one fused multiply-add each: lx*wf is taken exactly and
+    // (x0f + 0.5) is exact, so lw/lh carry one rounding at their own magnitude
+    // (< 1) instead of inheriting the rounding of x at magnitude ~W. The
+    // gradients multiply these fractions by W*attn*(S differences), which
+    // amplifies any error in them.
+    const float lw = fmaf(lx, wf, -(x0f + 0.5f));
+    const float lh = fmaf(ly, hf, -(y0f + 0.5f));
     const float hw = 1.f - lw;
     const float hh = 1.f - lh;
     // For dropped samples the coordinates may be NaN/Inf: keep the integer

@@ -1,0 +1,58 @@
+"""One-call hook that makes mmcv models use this package's MSDA operator.
+
+    from mx_driving.patcher import default_patcher
+    default_patcher.apply()
+
+Same surface as the reference's patcher for this path (mx_driving/patcher/__init__.py):
+``Patcher``, ``Patch``, ``AtomicPatch``, ``BasePatch``, ``PatchStatus``, ``PatchResult``,
+``MultiScaleDeformableAttention`` (alias ``MSDA``), ``default_patcher``, the legacy
+function ``msda(module, options)``, ``configure_patcher_logging`` and
+``set_patcher_log_level``. The reference's other predefined patches (deformable
+convolution, sparse convolution, dataset and optimizer shims, ...) belong to other
+operators and are not part of this package.
+"""
+from typing import Dict, List, Type
+
+from .patcher_logger import configure_patcher_logging, patcher_logger, set_patcher_log_level
+from .reporting import PatchResult, PatchStatus
+from .patch import AtomicPatch, BasePatch, Patch
+from .patcher import Patcher, replace_with
+from .mmcv_patch import MultiScaleDeformableAttention
+
+MSDA = MultiScaleDeformableAttention  # alias
+
+_ALL_PATCH_CLASSES: List[Type[Patch]] = [MultiScaleDeformableAttention]
+_DEFAULT_PATCH_CLASSES: List[Type[Patch]] = [MultiScaleDeformableAttention]
+
+
+def _create_default_patcher() -> Patcher:
+    patcher = Patcher()
+    patcher.add(*_DEFAULT_PATCH_CLASSES)
+    return patcher
+
+
+default_patcher = _create_default_patcher()
+
+_LEGACY_NAME_TO_CLASS: Dict[str, Type[Patch]] = {
+    cls.legacy_name: cls for cls in _ALL_PATCH_CLASSES if getattr(cls, "legacy_name", None)
+}
+
+
+def _create_legacy_patch_func(patch_cls: Type[Patch]):
+    """Old function-style API: ``func(module, options)`` applies the group's patches."""
+    def legacy_func(module, options):
+        for atomic in patch_cls.patches(options):
+            atomic.apply()
+    legacy_func.__name__ = patch_cls.legacy_name
+    return legacy_func
+
+
+msda = _create_legacy_patch_func(MultiScaleDeformableAttention)
+
+__all__ = [
+    "Patcher", "BasePatch", "Patch", "AtomicPatch", "replace_with",
+    "patcher_logger", "configure_patcher_logging", "set_patcher_log_level",
+    "PatchStatus", "PatchResult",
+    "default_patcher", "MultiScaleDeformableAttention", "MSDA", "msda",
+    "_ALL_PATCH_CLASSES", "_DEFAULT_PATCH_CLASSES", "_LEGACY_NAME_TO_CLASS",
+]

@@ -119,6 +119,14 @@ typedef enum msda_tune {
 } msda_tune;
 int msda_sm100_tune(int knob, int value);
 
+/* Optional timing hook for benchmarks, per host thread. While set, every
+ * forward call records (fwd_start, fwd_stop) and every backward call records
+ * (bwd_start, bwd_stop) — all cudaEvent_t created by the caller — immediately
+ * around its main kernel launch, on the launch stream, so that the kernel can
+ * be timed without the zero-fill or the down-conversion. Pass NULLs to clear.
+ * An event pair must not be reused before the caller has read it. */
+void msda_sm100_profile_events(void* fwd_start, void* fwd_stop, void* bwd_start, void* bwd_stop);
+
 /* Number of kernels this library has launched since load (all threads). */
 long long msda_sm100_launch_count(void);
 
