@@ -24,15 +24,21 @@
 namespace msda {
 
 constexpr int kPartMax = 8;  // partial dot products kept per (sample, corner)
+constexpr int kPartBytes = ((kChunk * (4 * kPartMax + 1) * 4 + 15) / 16) * 16;
+
+#ifndef MSDA_BWD_MIN_CTAS
+#define MSDA_BWD_MIN_CTAS 3
+#endif
 
 template <typename T, typename TG, int LPR, int NV, bool SCALAR>
-__global__ void __launch_bounds__(kThreadsPerCta)
+__global__ void __launch_bounds__(kThreadsPerCta, (SCALAR || NV > 1) ? 2 : MSDA_BWD_MIN_CTAS)
 msda_bwd_kernel(const __grid_constant__ Params p) {
     constexpr int VEC = SCALAR ? 1 : Elem<T>::kVec;
     constexpr int RPI = 32 / LPR;
     constexpr int PART = (LPR < kPartMax) ? LPR : kPartMax;  // partials per slot
     constexpr int SSTRIDE = 4 * PART + 1;                    // per-sample stride (bank spread)
     constexpr int UNROLL = (RPI >= 16) ? 2 : 4;
+    static_assert(kSlots % (RPI * UNROLL) == 0, "slot loop must tile the slot array");
     // 16-bit operands accumulated in fp32: a lane's 16-byte piece of the value row is 8
     // channels, i.e. 32 bytes of the fp32 accumulation row. Two reductions at +0 and +16
     // bytes of that span would touch every 32-byte sector of the row with half a sector each
@@ -47,23 +53,17 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
     const int g = lane / LPR;
     const int j = lane % LPR;
 
-    Stage<T> st = stage_init<T>(p, smem);
-    unsigned char* warp_base =
-        smem + (p.stage ? stage_smem_bytes(p.tasks_per_item, p.LP, sizeof(T)) : 0);
-    warp_base = reinterpret_cast<unsigned char*>(
-        (reinterpret_cast<uintptr_t>(warp_base) + 15) & ~uintptr_t(15));
-    constexpr int kWarpWords = 2 * kSlots + kChunk * (4 * kPartMax + 1) + 3;
-    constexpr int kWarpWordsAligned = (kWarpWords + 3) & ~3;
-    int* s_rows = reinterpret_cast<int*>(warp_base) + warp * kWarpWordsAligned;
-    float* s_wts = reinterpret_cast<float*>(s_rows + kSlots);
-    float* s_part = s_wts + kSlots;
+    unsigned char* wb = smem + static_cast<size_t>(warp) * p.warp_smem;
+    uint2* s_slot = reinterpret_cast<uint2*>(wb);
+    float* s_part = reinterpret_cast<float*>(wb + kSlotBytes);
+    WarpStage<T> st = warp_stage_init<T>(p, wb + kSlotBytes + kPartBytes, lane);
 
     const LaneLevels lv = load_lane_levels(p, lane);
     const T* __restrict__ value = static_cast<const T*>(p.value);
-    const T* __restrict__ gloc = static_cast<const T*>(p.loc);
-    const T* __restrict__ gattn = static_cast<const T*>(p.attn);
+    const unsigned char* vlane = static_cast<const unsigned char*>(p.value) + j * 16;
     const T* __restrict__ gout = static_cast<const T*>(p.grad_out);
     TG* __restrict__ gval = static_cast<TG*>(p.grad_value);
+    unsigned char* glane = static_cast<unsigned char*>(p.grad_value) + j * 16;
     T* __restrict__ gl = static_cast<T*>(p.grad_loc);
     T* __restrict__ ga = static_cast<T*>(p.grad_attn);
 
@@ -71,233 +71,212 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
     const int LP = p.LP;
     const int D = p.D;
     const int nchunks = (TPC == 1) ? (LP + kChunk - 1) / kChunk : 1;
-    const int QH = p.Q * p.H;
-    const long long ntiles = (p.nitems + kWarpsPerCta - 1) / kWarpsPerCta;
+    const long long stride = static_cast<long long>(gridDim.x) * kWarpsPerCta;
+    long long item = static_cast<long long>(blockIdx.x) * kWarpsPerCta + warp;
+    auto full = [&](long long it) { return (it + 1) * TPC <= p.ntasks; };
 
-    bool stage_ok = st.enabled;
-    if (stage_ok && threadIdx.x == 0 && blockIdx.x < ntiles && st.full(blockIdx.x)) {
-        st.issue(p, blockIdx.x, 0);
+    SampleRegs pre;
+    pre.lx = pre.ly = pre.a = 0.f;
+    bool have_pre = false;
+    if (item < p.nitems) {
+        if (st.ok) {
+            if (lane == 0 && full(item)) st.issue(p, item, 0);
+        } else {
+            pre = load_sample_direct<T>(p, item, 0, lane);
+            have_pre = true;
+        }
     }
 
-    int iter = 0;
-    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++iter) {
-        const int buf = iter & 1;
-        bool from_smem = false;
-        if (stage_ok) {
-            const long long next = tile + gridDim.x;
-            if (threadIdx.x == 0 && next < ntiles && st.full(next)) st.issue(p, next, buf ^ 1);
-            if (st.full(tile)) {
-                from_smem = mbar_wait(st.bar + buf, (iter >> 1) & 1);
-                if (!from_smem) {
-                    stage_ok = false;
-                    atomicOr(p.status, kStatusStageTimeout);
+    for (int n = 0; item < p.nitems; item += stride, ++n) {
+        const int buf = n & 1;
+        const long long next = item + stride;
+        const SampleRegs cur = pre;
+        bool have_cur = have_pre;
+        const T* sloc = nullptr;
+        const T* sattn = nullptr;
+        if (st.ok) {
+            have_cur = false;
+            if (lane == 0 && next < p.nitems && full(next)) st.issue(p, next, buf ^ 1);
+            if (full(item)) {
+                const bool arrived =
+                    __all_sync(0xffffffffu, mbar_wait(st.bar + buf, (n >> 1) & 1) ? 1 : 0) != 0;
+                if (arrived) {
+                    sloc = st.loc(p, buf);
+                    sattn = st.attn(p, buf);
+                } else {
+                    st.ok = false;
+                    if (lane == 0) atomicOr(p.status, kStatusStageTimeout);
                 }
             }
         }
+        if (!st.ok) {
+            have_pre = next < p.nitems;
+            if (have_pre) pre = load_sample_direct<T>(p, next, 0, lane);
+        }
 
-        const T* sloc = st.loc(buf);
-        const T* sattn = st.attn(buf);
-        const long long item = tile * kWarpsPerCta + warp;
-        if (item < p.nitems) {
-            const int t0 = static_cast<int>(item) * TPC;
-            const int ntask_here = min(TPC, static_cast<int>(p.ntasks - t0));
+        const int t0 = static_cast<int>(item) * TPC;
+        const int ntask_here = min(TPC, static_cast<int>(p.ntasks - t0));
 
-            for (int chunk = 0; chunk < nchunks; ++chunk) {
-                // ---- phase 1: lane = sample -------------------------------------
-                int tl, s;
-                lane_sample_index(p, chunk, lane, tl, s);
-                const bool active = (tl < ntask_here) && (s < LP);
-                int4 rows = make_int4(-1, -1, -1, -1);
-                float4 wts = make_float4(0.f, 0.f, 0.f, 0.f);
-                SampleGeom geom;
-                geom.lw = geom.lh = geom.a = geom.wf = geom.hf = 0.f;
-                geom.valid = false;
-                long long gi = 0;
-                if (active) {
-                    const int t = t0 + tl;
-                    gi = static_cast<long long>(t) * LP + s;
-                    float lx, ly, a;
-                    if (from_smem) {
-                        const int li = (warp * TPC + tl) * LP + s;
-                        lx = Elem<T>::to_f(sloc[2 * li]);
-                        ly = Elem<T>::to_f(sloc[2 * li + 1]);
-                        a = Elem<T>::to_f(sattn[li]);
-                    } else {
-                        lx = Elem<T>::to_f(gloc[2 * gi]);
-                        ly = Elem<T>::to_f(gloc[2 * gi + 1]);
-                        a = Elem<T>::to_f(gattn[gi]);
-                    }
-                    const int b = t / QH;
-                    const int h = t % p.H;
-                    const int c = (TPC == 1) ? chunk : 0;
-                    const int row_base = (b * p.K + lv.start(c)) * p.H + h;
-                    sample_setup(lx, ly, a, lv.w(c), lv.h(c), row_base, p.H, rows, wts, geom);
+        for (int chunk = 0; chunk < nchunks; ++chunk) {
+            // ---- phase 1: lane = sample -----------------------------------------
+            SampleGeom geom;
+            long long gi;
+            const bool active = phase1<T>(p, lv, chunk, lane, item, ntask_here, sloc, sattn,
+                                          have_cur, cur, s_slot, geom, gi);
+            __syncwarp();
+
+            // ---- phase 2: lane = (row slot, piece of row) -----------------------
+            for (int tl2 = 0; tl2 < ntask_here; ++tl2) {
+                int slot_begin, slot_end;
+                if (TPC == 1) {
+                    slot_begin = 0;
+                    slot_end = 4 * min(kChunk, LP - chunk * kChunk);
+                } else {
+                    slot_begin = tl2 * 4 * LP;
+                    slot_end = slot_begin + 4 * LP;
                 }
-                reinterpret_cast<int4*>(s_rows)[lane] = rows;
-                reinterpret_cast<float4*>(s_wts)[lane] = wts;
-                __syncwarp();
-
-                // ---- phase 2: lane = (row slot, piece of row) -------------------
-                for (int tl2 = 0; tl2 < ntask_here; ++tl2) {
-                    int slot_begin, slot_end;
-                    if (TPC == 1) {
-                        slot_begin = 0;
-                        slot_end = 4 * min(kChunk, LP - chunk * kChunk);
+                // this lane's piece of grad_out[b, q, h, :]
+                float go[NV][VEC];
+                const size_t obase = static_cast<size_t>(t0 + tl2) * D;
+#pragma unroll
+                for (int k = 0; k < NV; ++k) {
+                    if constexpr (!SCALAR) {
+                        const uint4 raw =
+                            *reinterpret_cast<const uint4*>(gout + obase + (j + k * LPR) * VEC);
+                        unpack16<T>(raw, go[k]);
                     } else {
-                        slot_begin = tl2 * 4 * LP;
-                        slot_end = slot_begin + 4 * LP;
+                        const int c = j + k * 32;
+                        go[k][0] = (c < D) ? Elem<T>::to_f(gout[obase + c]) : 0.f;
                     }
-                    // this lane's piece of grad_out[b, q, h, :]
-                    float go[NV][VEC];
-                    const size_t obase = static_cast<size_t>(t0 + tl2) * D;
+                }
+                float gred[2][4];
+                if constexpr (SPLIT_RED) {
 #pragma unroll
-                    for (int k = 0; k < NV; ++k) {
-                        if constexpr (!SCALAR) {
-                            const uint4 raw =
-                                *reinterpret_cast<const uint4*>(gout + obase + (j + k * LPR) * VEC);
-                            unpack16<T>(raw, go[k]);
-                        } else {
-                            const int c = j + k * 32;
-                            go[k][0] = (c < D) ? Elem<T>::to_f(gout[obase + c]) : 0.f;
+                    for (int half = 0; half < 2; ++half) {
+                        const T* src = gout + obase + (half * LPR + j) * 4;
+                        const uint2 raw = *reinterpret_cast<const uint2*>(src);
+                        const uint32_t wds[2] = {raw.x, raw.y};
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            const uint16_t l16 = static_cast<uint16_t>(wds[i] & 0xffffu);
+                            const uint16_t h16 = static_cast<uint16_t>(wds[i] >> 16);
+                            gred[half][2 * i] = Elem<T>::to_f(*reinterpret_cast<const T*>(&l16));
+                            gred[half][2 * i + 1] =
+                                Elem<T>::to_f(*reinterpret_cast<const T*>(&h16));
                         }
                     }
-                    float gred[2][4];
-                    if constexpr (SPLIT_RED) {
-#pragma unroll
-                        for (int half = 0; half < 2; ++half) {
-                            const uint2 raw = *reinterpret_cast<const uint2*>(
-                                gout + obase + (half * LPR + j) * 4);
-                            const uint32_t wds[2] = {raw.x, raw.y};
-#pragma unroll
-                            for (int i = 0; i < 2; ++i) {
-                                if constexpr (sizeof(T) == 2) {
-                                    T lo, hi;
-                                    const uint16_t l16 = static_cast<uint16_t>(wds[i] & 0xffffu);
-                                    const uint16_t h16 = static_cast<uint16_t>(wds[i] >> 16);
-                                    lo = *reinterpret_cast<const T*>(&l16);
-                                    hi = *reinterpret_cast<const T*>(&h16);
-                                    gred[half][2 * i] = Elem<T>::to_f(lo);
-                                    gred[half][2 * i + 1] = Elem<T>::to_f(hi);
-                                }
-                            }
-                        }
-                    }
+                }
 #pragma unroll 1
-                    for (int base = slot_begin; base < slot_end; base += RPI * UNROLL) {
-                        int r[UNROLL];
-                        float w[UNROLL];
-                        float part[UNROLL];
+                for (int base = slot_begin; base < slot_end; base += RPI * UNROLL) {
+                    uint2 rec[UNROLL];
+                    float part[UNROLL];
 #pragma unroll
-                        for (int u = 0; u < UNROLL; ++u) {
-                            const int slot = base + u * RPI + g;
-                            const bool in = slot < slot_end;
-                            r[u] = in ? s_rows[slot] : -1;
-                            w[u] = in ? s_wts[slot] : 0.f;
-                            part[u] = 0.f;
-                        }
-                        if constexpr (!SCALAR) {
-                            uint4 raw[UNROLL][NV];
-#pragma unroll
-                            for (int u = 0; u < UNROLL; ++u) {
-#pragma unroll
-                                for (int k = 0; k < NV; ++k) {
-                                    raw[u][k] = make_uint4(0u, 0u, 0u, 0u);
-                                    if (r[u] >= 0) {
-                                        raw[u][k] = ldg16(value + static_cast<size_t>(r[u]) * D +
-                                                          (j + k * LPR) * VEC);
-                                    }
-                                }
-                            }
-#pragma unroll
-                            for (int u = 0; u < UNROLL; ++u) {
-#pragma unroll
-                                for (int k = 0; k < NV; ++k) {
-                                    if (r[u] >= 0) {
-                                        if constexpr (SPLIT_RED) {
-                                            float* row =
-                                                reinterpret_cast<float*>(gval) +
-                                                static_cast<size_t>(r[u]) * D;
-                                            red_add_f32x4(row + j * 4, w[u] * gred[0][0],
-                                                          w[u] * gred[0][1], w[u] * gred[0][2],
-                                                          w[u] * gred[0][3]);
-                                            red_add_f32x4(row + (LPR + j) * 4, w[u] * gred[1][0],
-                                                          w[u] * gred[1][1], w[u] * gred[1][2],
-                                                          w[u] * gred[1][3]);
-                                        } else {
-                                            float contrib[VEC];
-#pragma unroll
-                                            for (int e = 0; e < VEC; ++e)
-                                                contrib[e] = w[u] * go[k][e];
-                                            red_add_vec<TG, VEC>(
-                                                gval + static_cast<size_t>(r[u]) * D +
-                                                    (j + k * LPR) * VEC,
-                                                contrib);
-                                        }
-                                    }
-                                    float f[VEC];
-                                    unpack16<T>(raw[u][k], f);
-#pragma unroll
-                                    for (int e = 0; e < VEC; ++e)
-                                        part[u] = fmaf(f[e], go[k][e], part[u]);
-                                }
-                            }
-                        } else {
-#pragma unroll
-                            for (int u = 0; u < UNROLL; ++u) {
-#pragma unroll
-                                for (int k = 0; k < NV; ++k) {
-                                    const int c = j + k * 32;
-                                    if (r[u] >= 0 && c < D) {
-                                        const size_t idx = static_cast<size_t>(r[u]) * D + c;
-                                        const float v = Elem<T>::to_f(__ldg(value + idx));
-                                        red_add_scalar(gval + idx, w[u] * go[k][0]);
-                                        part[u] = fmaf(v, go[k][0], part[u]);
-                                    }
-                                }
-                            }
-                        }
-                        // fold to PART partials per slot, then park them in shared memory
+                    for (int u = 0; u < UNROLL; ++u) {
+                        const int slot = base + u * RPI + g;
+                        rec[u] = s_slot[slot & (kSlots - 1)];
+                        if (TPC != 1 && slot >= slot_end) rec[u].x = kNoRow;
+                        part[u] = 0.f;
+                    }
+                    if constexpr (!SCALAR) {
+                        uint4 raw[UNROLL][NV];
 #pragma unroll
                         for (int u = 0; u < UNROLL; ++u) {
 #pragma unroll
-                            for (int off = LPR / 2; off >= PART; off >>= 1)
-                                part[u] += __shfl_xor_sync(0xffffffffu, part[u], off);
-                            const int slot = base + u * RPI + g;
-                            if (slot < slot_end && j < PART) {
-                                s_part[(slot >> 2) * SSTRIDE + (slot & 3) * PART + j] = part[u];
+                            for (int k = 0; k < NV; ++k) {
+                                raw[u][k] = make_uint4(0u, 0u, 0u, 0u);
+                                if (rec[u].x != kNoRow) {
+                                    raw[u][k] = ldg16(vlane + static_cast<size_t>(rec[u].x) * 16 +
+                                                      k * (LPR * 16));
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < UNROLL; ++u) {
+                            const float w = __uint_as_float(rec[u].y);
+#pragma unroll
+                            for (int k = 0; k < NV; ++k) {
+                                if (rec[u].x != kNoRow) {
+                                    if constexpr (SPLIT_RED) {
+                                        float* row = reinterpret_cast<float*>(
+                                            glane + static_cast<size_t>(rec[u].x) * 32);
+                                        red_add_f32x4(row, w * gred[0][0], w * gred[0][1],
+                                                      w * gred[0][2], w * gred[0][3]);
+                                        red_add_f32x4(row + LPR * 4, w * gred[1][0],
+                                                      w * gred[1][1], w * gred[1][2],
+                                                      w * gred[1][3]);
+                                    } else {
+                                        float contrib[VEC];
+#pragma unroll
+                                        for (int e = 0; e < VEC; ++e) contrib[e] = w * go[k][e];
+                                        red_add_vec<TG, VEC>(
+                                            reinterpret_cast<TG*>(
+                                                glane + static_cast<size_t>(rec[u].x) * 16 +
+                                                k * (LPR * 16)),
+                                            contrib);
+                                    }
+                                }
+                                float f[VEC];
+                                unpack16<T>(raw[u][k], f);
+#pragma unroll
+                                for (int e = 0; e < VEC; ++e)
+                                    part[u] = fmaf(f[e], go[k][e], part[u]);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int u = 0; u < UNROLL; ++u) {
+                            const float w = __uint_as_float(rec[u].y);
+#pragma unroll
+                            for (int k = 0; k < NV; ++k) {
+                                const int c = j + k * 32;
+                                if (rec[u].x != kNoRow && c < D) {
+                                    const size_t idx = static_cast<size_t>(rec[u].x) + c;
+                                    const float v = Elem<T>::to_f(__ldg(value + idx));
+                                    red_add_scalar(gval + idx, w * go[k][0]);
+                                    part[u] = fmaf(v, go[k][0], part[u]);
+                                }
                             }
                         }
                     }
-                }
-                __syncwarp();
-
-                // ---- phase 3: lane = sample -------------------------------------
-                if (active) {
-                    float S[4];
+                    // fold to PART partials per slot, then park them in shared memory
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        float acc = 0.f;
+                    for (int u = 0; u < UNROLL; ++u) {
 #pragma unroll
-                        for (int q = 0; q < PART; ++q) acc += s_part[lane * SSTRIDE + c * PART + q];
-                        S[c] = acc;
+                        for (int off = LPR / 2; off >= PART; off >>= 1)
+                            part[u] += __shfl_xor_sync(0xffffffffu, part[u], off);
+                        const int slot = base + u * RPI + g;
+                        if (slot < slot_end && j < PART) {
+                            s_part[(slot >> 2) * SSTRIDE + (slot & 3) * PART + j] = part[u];
+                        }
                     }
-                    float g_attn = 0.f, g_x = 0.f, g_y = 0.f;
-                    if (geom.valid) {
-                        // Corners that do not exist contributed nothing to s_part
-                        // only if their slot was visited with r < 0, which stores 0.
-                        const float lw = geom.lw, lh = geom.lh;
-                        const float hw = 1.f - lw, hh = 1.f - lh;
-                        g_attn = hh * hw * S[0] + hh * lw * S[1] + lh * hw * S[2] + lh * lw * S[3];
-                        g_x = geom.wf * geom.a * (hh * (S[1] - S[0]) + lh * (S[3] - S[2]));
-                        g_y = geom.hf * geom.a * (hw * (S[2] - S[0]) + lw * (S[3] - S[1]));
-                    }
-                    store_pair(gl + 2 * gi, g_x, g_y);
-                    ga[gi] = Elem<T>::from_f(g_attn);
                 }
-                __syncwarp();
             }
+            __syncwarp();
+
+            // ---- phase 3: lane = sample -----------------------------------------
+            if (active) {
+                float S[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float acc = 0.f;
+#pragma unroll
+                    for (int q = 0; q < PART; ++q) acc += s_part[lane * SSTRIDE + c * PART + q];
+                    S[c] = acc;
+                }
+                float g_attn = 0.f, g_x = 0.f, g_y = 0.f;
+                if (geom.valid) {
+                    // a corner that does not exist left a zero partial sum behind
+                    const float lw = geom.lw, lh = geom.lh;
+                    const float hw = 1.f - lw, hh = 1.f - lh;
+                    g_attn = hh * hw * S[0] + hh * lw * S[1] + lh * hw * S[2] + lh * lw * S[3];
+                    g_x = geom.wf * geom.a * (hh * (S[1] - S[0]) + lh * (S[3] - S[2]));
+                    g_y = geom.hf * geom.a * (hw * (S[2] - S[0]) + lw * (S[3] - S[1]));
+                }
+                store_pair(gl + 2 * gi, g_x, g_y);
+                ga[gi] = Elem<T>::from_f(g_attn);
+            }
+            __syncwarp();
         }
-        if (st.enabled) __syncthreads();
     }
 }
 
@@ -324,58 +303,57 @@ __global__ void __launch_bounds__(256) msda_downcast_kernel(const float* __restr
 // host side
 // ---------------------------------------------------------------------------
 template <typename T, typename TG, int LPR, int NV, bool SCALAR>
-static cudaError_t launch_bwd_inst(const Params& p, int grid, size_t smem, cudaStream_t stream) {
+static cudaError_t launch_bwd_inst(const Params& p, const LaunchShape& ls, size_t smem,
+                                   cudaStream_t stream) {
     auto kern = msda_bwd_kernel<T, TG, LPR, NV, SCALAR>;
     if (smem > 48 * 1024) {
         cudaError_t e =
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
+    int grid = 0;
+    cudaError_t e = persistent_grid(reinterpret_cast<const void*>(kern), smem, ls, p, &grid);
+    if (e != cudaSuccess) return e;
     kern<<<grid, kThreadsPerCta, smem, stream>>>(p);
     return cudaGetLastError();
 }
 
 template <typename T, typename TG>
-static cudaError_t launch_bwd_typed(const Params& p, const RowPlan& rp, int grid, size_t smem,
+static cudaError_t launch_bwd_typed(const Params& p, const RowPlan& rp, const LaunchShape& ls, size_t smem,
                                     cudaStream_t stream) {
-    if (rp.scalar) return launch_bwd_inst<T, TG, 32, 8, true>(p, grid, smem, stream);
+    if (rp.scalar) return launch_bwd_inst<T, TG, 32, 8, true>(p, ls, smem, stream);
     switch (rp.lpr * 100 + rp.nv) {
-        case 101: return launch_bwd_inst<T, TG, 1, 1, false>(p, grid, smem, stream);
-        case 201: return launch_bwd_inst<T, TG, 2, 1, false>(p, grid, smem, stream);
-        case 401: return launch_bwd_inst<T, TG, 4, 1, false>(p, grid, smem, stream);
-        case 801: return launch_bwd_inst<T, TG, 8, 1, false>(p, grid, smem, stream);
-        case 1601: return launch_bwd_inst<T, TG, 16, 1, false>(p, grid, smem, stream);
-        case 3201: return launch_bwd_inst<T, TG, 32, 1, false>(p, grid, smem, stream);
+        case 101: return launch_bwd_inst<T, TG, 1, 1, false>(p, ls, smem, stream);
+        case 201: return launch_bwd_inst<T, TG, 2, 1, false>(p, ls, smem, stream);
+        case 401: return launch_bwd_inst<T, TG, 4, 1, false>(p, ls, smem, stream);
+        case 801: return launch_bwd_inst<T, TG, 8, 1, false>(p, ls, smem, stream);
+        case 1601: return launch_bwd_inst<T, TG, 16, 1, false>(p, ls, smem, stream);
+        case 3201: return launch_bwd_inst<T, TG, 32, 1, false>(p, ls, smem, stream);
         case 3202:
             if constexpr (sizeof(T) == 4) {
-                return launch_bwd_inst<T, TG, 32, 2, false>(p, grid, smem, stream);
+                return launch_bwd_inst<T, TG, 32, 2, false>(p, ls, smem, stream);
             }
             return cudaErrorInvalidValue;
         default: return cudaErrorInvalidValue;
     }
 }
 
-size_t bwd_smem_bytes(const Params& p, size_t elem) {
-    size_t s = p.stage ? stage_smem_bytes(p.tasks_per_item, p.LP, elem) : 0;
-    s = (s + 15) & ~size_t(15);
-    const size_t warp_words = (2 * kSlots + kChunk * (4 * kPartMax + 1) + 3 + 3) & ~size_t(3);
-    return s + static_cast<size_t>(kWarpsPerCta) * warp_words * 4 + 16;
+uint32_t bwd_warp_smem(int samples_per_item, size_t elem) {
+    return warp_smem_bytes(samples_per_item, elem, kPartBytes);
 }
 
-cudaError_t launch_backward(const Params& p, int dtype, int acc_f32, const RowPlan& rp, int grid,
-                            cudaStream_t stream) {
+cudaError_t launch_backward(const Params& p, int dtype, int acc_f32, const RowPlan& rp,
+                            const LaunchShape& ls, cudaStream_t stream) {
+    const size_t smem = static_cast<size_t>(p.warp_smem) * kWarpsPerCta;
     switch (dtype) {
-        case 0: return launch_bwd_typed<float, float>(p, rp, grid, bwd_smem_bytes(p, 4), stream);
+        case 0: return launch_bwd_typed<float, float>(p, rp, ls, smem, stream);
         case 1:
-            return acc_f32
-                       ? launch_bwd_typed<__half, float>(p, rp, grid, bwd_smem_bytes(p, 2), stream)
-                       : launch_bwd_typed<__half, __half>(p, rp, grid, bwd_smem_bytes(p, 2),
-                                                          stream);
+            return acc_f32 ? launch_bwd_typed<__half, float>(p, rp, ls, smem, stream)
+                           : launch_bwd_typed<__half, __half>(p, rp, ls, smem, stream);
         case 2:
-            return acc_f32 ? launch_bwd_typed<__nv_bfloat16, float>(p, rp, grid,
-                                                                    bwd_smem_bytes(p, 2), stream)
-                           : launch_bwd_typed<__nv_bfloat16, __nv_bfloat16>(
-                                 p, rp, grid, bwd_smem_bytes(p, 2), stream);
+            return acc_f32
+                       ? launch_bwd_typed<__nv_bfloat16, float>(p, rp, ls, smem, stream)
+                       : launch_bwd_typed<__nv_bfloat16, __nv_bfloat16>(p, rp, ls, smem, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -20,8 +20,8 @@ constexpr int kMaxDevices = 64;
 __device__ int g_status_word;
 
 std::atomic<int> g_tune_stage{1};
-std::atomic<int> g_tune_cps_fwd{4};
-std::atomic<int> g_tune_cps_bwd{4};
+std::atomic<int> g_tune_cps_fwd{0};
+std::atomic<int> g_tune_cps_bwd{0};
 std::atomic<long long> g_launches{0};
 thread_local int t_last_cuda_error = 0;
 thread_local cudaEvent_t t_prof[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -105,6 +105,18 @@ RowPlan plan_rows(int D, int dtype, bool ptrs_16B_aligned) {
     return rp;
 }
 
+// Offsets of value rows travel as 32-bit counts of `row_units`: 16-byte pieces on the vector
+// path, elements on the scalar path.
+int set_row_units(Params& p, const RowPlan& rp, int dtype) {
+    const unsigned long long units =
+        rp.scalar ? static_cast<unsigned long long>(p.D)
+                  : static_cast<unsigned long long>(p.D) * elem_size(dtype) / 16;
+    const unsigned long long rows = static_cast<unsigned long long>(p.B) * p.K * p.H;
+    if (rows * units >= 0xffffffffull) return MSDA_ERR_LIMIT;
+    p.row_units = static_cast<uint32_t>(units);
+    return MSDA_OK;
+}
+
 // Fills the parts of Params common to both directions.
 int fill_common(Params& p, const DeviceInfo* dev, const void* value, const int32_t* shapes,
                 const int32_t* starts, const void* loc, const void* attn, int B, int K, int H,
@@ -140,17 +152,18 @@ int fill_common(Params& p, const DeviceInfo* dev, const void* value, const int32
         }
     }
     const size_t e = elem_size(dtype);
-    // Staging needs 16-byte aligned sources; tile sizes are multiples of 16 by
-    // construction (8 warps x tasks x samples x >= 2 bytes).
-    p.stage = (g_tune_stage.load() != 0 && aligned_to(loc, 16) && aligned_to(attn, 16)) ? 1 : 0;
+    p.fd_qh = msda::make_fastdiv(static_cast<uint32_t>(Q) * static_cast<uint32_t>(H));
+    p.fd_h = msda::make_fastdiv(static_cast<uint32_t>(H));
+    p.fd_lp = msda::make_fastdiv(static_cast<uint32_t>(p.LP));
+    // Bulk-copy staging needs 16-byte aligned sources and sizes: per item the weights take
+    // samples * e bytes and the locations twice that.
+    const size_t item_attn_bytes = static_cast<size_t>(p.tasks_per_item) * p.LP * e;
+    p.stage = (g_tune_stage.load() != 0 && aligned_to(loc, 16) && aligned_to(attn, 16) &&
+               item_attn_bytes % 16 == 0)
+                  ? 1
+                  : 0;
     if (!aligned_to(value, e) || !aligned_to(loc, e) || !aligned_to(attn, e)) return MSDA_ERR_ALIGN;
     return MSDA_OK;
-}
-
-int grid_for(const Params& p, const DeviceInfo* dev, int ctas_per_sm) {
-    const long long ntiles = (p.nitems + msda::kWarpsPerCta - 1) / msda::kWarpsPerCta;
-    long long cap = static_cast<long long>(dev->sm_count) * (ctas_per_sm > 0 ? ctas_per_sm : 1);
-    return static_cast<int>(ntiles < cap ? ntiles : cap);
 }
 
 int backward_impl(const void* value, const int32_t* shapes, const int32_t* starts, const void* loc,
@@ -189,6 +202,9 @@ int backward_impl(const void* value, const int32_t* shapes, const int32_t* start
     const bool vec_ok = aligned_to(value, 16) && aligned_to(grad_out, 16) && aligned_to(acc, 16);
     const RowPlan rp = plan_rows(D, dtype, vec_ok);
 
+    rc = set_row_units(p, rp, dtype);
+    if (rc != MSDA_OK) return rc;
+    p.warp_smem = msda::bwd_warp_smem(p.tasks_per_item * p.LP, e);
     p.grad_out = grad_out;
     p.grad_value = acc;
     p.grad_loc = grad_loc;
@@ -197,7 +213,7 @@ int backward_impl(const void* value, const int32_t* shapes, const int32_t* start
     cudaError_t ce = cudaMemsetAsync(acc, 0, acc_bytes, stream);
     if (ce != cudaSuccess) return fail_cuda(ce);
     prof_record(2, stream);
-    ce = msda::launch_backward(p, dtype, acc_f32 ? 1 : 0, rp, grid_for(p, dev, g_tune_cps_bwd.load()),
+    ce = msda::launch_backward(p, dtype, acc_f32 ? 1 : 0, rp, msda::LaunchShape{dev->sm_count, g_tune_cps_bwd.load()},
                                stream);
     prof_record(3, stream);
     if (ce != cudaSuccess) return fail_cuda(ce);
@@ -234,10 +250,13 @@ int msda_sm100_forward(const void* value, const int32_t* spatial_shapes,
     if (!aligned_to(output, elem_size(dtype))) return MSDA_ERR_ALIGN;
     p.out = output;
     const RowPlan rp = plan_rows(D, dtype, aligned_to(value, 16) && aligned_to(output, 16));
+    rc = set_row_units(p, rp, dtype);
+    if (rc != MSDA_OK) return rc;
+    p.warp_smem = msda::fwd_warp_smem(p.tasks_per_item * p.LP, elem_size(dtype));
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     prof_record(0, stream);
     cudaError_t ce =
-        msda::launch_forward(p, dtype, rp, grid_for(p, dev, g_tune_cps_fwd.load()), stream);
+        msda::launch_forward(p, dtype, rp, msda::LaunchShape{dev->sm_count, g_tune_cps_fwd.load()}, stream);
     prof_record(1, stream);
     if (ce != cudaSuccess) return fail_cuda(ce);
     g_launches.fetch_add(1, std::memory_order_relaxed);

@@ -33,6 +33,26 @@ constexpr int kSpinLimit = 1 << 18; // bound on mbarrier polling
 // Device status bits, sticky until read by msda_sm100_device_status().
 constexpr int kStatusStageTimeout = 1;  // a staged tile never arrived
 
+// Division by a runtime constant without a divide: q = (n * mul) >> shift, exact
+// for 0 <= n < 2^31 (round-up method with a 31 + ceil(log2 d) bit shift).
+struct FastDiv {
+    uint32_t mul;
+    uint32_t shift;
+};
+inline FastDiv make_fastdiv(uint32_t d) {
+    uint32_t s = 0;
+    while ((1ull << s) < d) ++s;
+    FastDiv f;
+    f.shift = 31 + s;
+    f.mul = static_cast<uint32_t>(((1ull << f.shift) + d - 1) / d);
+    return f;
+}
+__device__ __forceinline__ uint32_t fd_div(uint32_t n, const FastDiv& f) {
+    return static_cast<uint32_t>((static_cast<uint64_t>(n) * f.mul) >> f.shift);
+}
+
+constexpr uint32_t kNoRow = 0xffffffffu;  // slot record of a corner that does not exist
+
 // Level geometry by value. A launch that received the shapes on the host puts
 // them here (kernel parameters live in the constant bank); a launch that
 // received device pointers leaves use_table = 0 and each CTA reads the two
@@ -61,10 +81,13 @@ struct Params {
     int LP;             // L * P
     int tasks_per_item; // consecutive (b, q, h) tasks one warp pass covers
     int use_table;
-    int stage;          // 1: bulk-copy location/weight tiles into shared memory
+    int stage;          // 1: each warp bulk-copies its next item's locations/weights to shared memory
     long long ntasks;   // B * Q * H
     long long nitems;   // ceil(ntasks / tasks_per_item)
     int* status;        // device status word
+    uint32_t row_units;      // offset units per value row: 16-byte pieces, or elements (scalar path)
+    uint32_t warp_smem;      // bytes of dynamic shared memory per warp
+    FastDiv fd_qh, fd_h, fd_lp;  // division by Q*H, H, L*P
     LevelTable lv;
 };
 
@@ -272,11 +295,12 @@ struct SampleGeom {
     bool valid;
 };
 
-// rows[c] is the value row ((b*K + start + y*W + x)*H + h) of corner c, or -1
-// when that corner does not exist; wts[c] is bilinear weight * attention.
+// Produces the four slot records of one sample: rec[c] = {offset of the corner's value row in
+// `row_units` units, or kNoRow when that corner does not exist; bits of (bilinear weight *
+// attention)}. row_base = (b*K + level_start)*H + h.
 __device__ __forceinline__ void sample_setup(float lx, float ly, float a, int Wl, int Hl,
-                                             int row_base, int H, int4& rows, float4& wts,
-                                             SampleGeom& g) {
+                                             uint32_t row_base, uint32_t H, uint32_t row_units,
+                                             uint4& rec01, uint4& rec23, SampleGeom& g) {
     const float wf = static_cast<float>(Wl);
     const float hf = static_cast<float>(Hl);
     const float x = lx * wf - 0.5f;
@@ -297,23 +321,26 @@ __device__ __forceinline__ void sample_setup(float lx, float ly, float a, int Wl
     // conversion away from them.
     const int x0 = valid ? static_cast<int>(x0f) : 0;
     const int y0 = valid ? static_cast<int>(y0f) : 0;
-    const int x1 = x0 + 1;
-    const int y1 = y0 + 1;
     const bool x0ok = valid && x0 >= 0;
-    const bool x1ok = valid && x1 <= Wl - 1;
+    const bool x1ok = valid && x0 + 1 <= Wl - 1;
     const bool y0ok = valid && y0 >= 0;
-    const bool y1ok = valid && y1 <= Hl - 1;
-    const int r00 = row_base + (y0 * Wl + x0) * H;
-    rows.x = (y0ok && x0ok) ? r00 : -1;
-    rows.y = (y0ok && x1ok) ? r00 + H : -1;
-    rows.z = (y1ok && x0ok) ? r00 + Wl * H : -1;
-    rows.w = (y1ok && x1ok) ? r00 + Wl * H + H : -1;
+    const bool y1ok = valid && y0 + 1 <= Hl - 1;
+    const uint32_t step_x = H * row_units;             // next pixel, same head
+    const uint32_t step_y = static_cast<uint32_t>(Wl) * step_x;
+    // (y0*Wl + x0) may be negative (x0 or y0 == -1); unsigned wrap-around is fine because a
+    // record is only used when its corner exists, and then the sum is in range.
+    const uint32_t o00 =
+        (row_base + static_cast<uint32_t>(y0 * Wl + x0) * H) * row_units;
     // Selects, not multiplications by zero: lw/lh/a may be NaN or Inf here.
     const float aa = valid ? a : 0.f;
-    wts.x = valid ? hh * hw * aa : 0.f;
-    wts.y = valid ? hh * lw * aa : 0.f;
-    wts.z = valid ? lh * hw * aa : 0.f;
-    wts.w = valid ? lh * lw * aa : 0.f;
+    rec01.x = (y0ok && x0ok) ? o00 : kNoRow;
+    rec01.y = __float_as_uint(valid ? hh * hw * aa : 0.f);
+    rec01.z = (y0ok && x1ok) ? o00 + step_x : kNoRow;
+    rec01.w = __float_as_uint(valid ? hh * lw * aa : 0.f);
+    rec23.x = (y1ok && x0ok) ? o00 + step_y : kNoRow;
+    rec23.y = __float_as_uint(valid ? lh * hw * aa : 0.f);
+    rec23.z = (y1ok && x1ok) ? o00 + step_y + step_x : kNoRow;
+    rec23.w = __float_as_uint(valid ? lh * lw * aa : 0.f);
     g.lw = valid ? lw : 0.f;
     g.lh = valid ? lh : 0.f;
     g.a = aa;

@@ -5,12 +5,13 @@
 //  op_host/multi_scale_deformable_attn.cpp:32-114).
 //
 // One warp per (batch, query, head) task (several tasks per warp when L*P < 32).
-//   phase 1  lane = sample: read (x, y, weight) — from the bulk-copied shared
-//            tile or straight from global memory — and leave, per corner, the
-//            value row index (or -1) and the combined weight in shared memory.
+//   phase 1  lane = sample: take (x, y, weight) — bulk-copied to shared memory
+//            or loaded ahead into registers while the previous item was being
+//            gathered — and leave one 8-byte record per corner in shared
+//            memory: {offset of the value row, bilinear weight * attention}.
 //   phase 2  lane = (row slot, 16-byte piece of the row): the warp reads
 //            32/LPR whole rows per instruction (LPR lanes x 16 bytes = one
-//            contiguous row), several instructions in flight, and accumulates
+//            contiguous row), eight instructions in flight, and accumulates
 //            in fp32 registers.
 //   epilogue the row-slot groups are summed with xor shuffles and one group
 //            writes the D outputs as 16-byte stores.
@@ -19,14 +20,19 @@
 #include "msda_launch.h"
 #include "msda_tile.cuh"
 
+#ifndef MSDA_FWD_MIN_CTAS
+#define MSDA_FWD_MIN_CTAS 4
+#endif
+
 namespace msda {
 
 template <typename T, int LPR, int NV, bool SCALAR>
-__global__ void __launch_bounds__(kThreadsPerCta)
+__global__ void __launch_bounds__(kThreadsPerCta, (SCALAR || NV > 1) ? 2 : MSDA_FWD_MIN_CTAS)
 msda_fwd_kernel(const __grid_constant__ Params p) {
     constexpr int VEC = SCALAR ? 1 : Elem<T>::kVec;
     constexpr int RPI = 32 / LPR;                  // rows per warp instruction
     constexpr int UNROLL = (RPI >= 16) ? 2 : ((NV > 2) ? 4 : 8);
+    static_assert(kSlots % (RPI * UNROLL) == 0, "slot loop must tile the slot array");
 
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5;
@@ -34,191 +40,176 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
     const int g = lane / LPR;   // row slot within one instruction
     const int j = lane % LPR;   // 16-byte piece (or channel mod 32) within the row
 
-    Stage<T> st = stage_init<T>(p, smem);
-    unsigned char* warp_base =
-        smem + (p.stage ? stage_smem_bytes(p.tasks_per_item, p.LP, sizeof(T)) : 0);
-    warp_base = reinterpret_cast<unsigned char*>(
-        (reinterpret_cast<uintptr_t>(warp_base) + 15) & ~uintptr_t(15));
-    int* s_rows = reinterpret_cast<int*>(warp_base) + warp * 2 * kSlots;
-    float* s_wts = reinterpret_cast<float*>(s_rows + kSlots);
+    unsigned char* wb = smem + static_cast<size_t>(warp) * p.warp_smem;
+    uint2* s_slot = reinterpret_cast<uint2*>(wb);
+    WarpStage<T> st = warp_stage_init<T>(p, wb + kSlotBytes, lane);
 
     const LaneLevels lv = load_lane_levels(p, lane);
     const T* __restrict__ value = static_cast<const T*>(p.value);
-    const T* __restrict__ gloc = static_cast<const T*>(p.loc);
-    const T* __restrict__ gattn = static_cast<const T*>(p.attn);
+    const unsigned char* vlane = static_cast<const unsigned char*>(p.value) + j * 16;
     T* __restrict__ out = static_cast<T*>(p.out);
 
     const int TPC = p.tasks_per_item;
     const int LP = p.LP;
     const int D = p.D;
     const int nchunks = (TPC == 1) ? (LP + kChunk - 1) / kChunk : 1;
-    const int QH = p.Q * p.H;
-    const long long ntiles = (p.nitems + kWarpsPerCta - 1) / kWarpsPerCta;
+    const long long stride = static_cast<long long>(gridDim.x) * kWarpsPerCta;
+    long long item = static_cast<long long>(blockIdx.x) * kWarpsPerCta + warp;
+    auto full = [&](long long it) { return (it + 1) * TPC <= p.ntasks; };
 
-    bool stage_ok = st.enabled;
-    if (stage_ok && threadIdx.x == 0 && blockIdx.x < ntiles && st.full(blockIdx.x)) {
-        st.issue(p, blockIdx.x, 0);
+    SampleRegs pre;
+    pre.lx = pre.ly = pre.a = 0.f;
+    bool have_pre = false;
+    if (item < p.nitems) {
+        if (st.ok) {
+            if (lane == 0 && full(item)) st.issue(p, item, 0);
+        } else {
+            pre = load_sample_direct<T>(p, item, 0, lane);
+            have_pre = true;
+        }
     }
 
-    int iter = 0;
-    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++iter) {
-        const int buf = iter & 1;
-        bool from_smem = false;
-        if (stage_ok) {
-            const long long next = tile + gridDim.x;
-            if (threadIdx.x == 0 && next < ntiles && st.full(next)) st.issue(p, next, buf ^ 1);
-            if (st.full(tile)) {
-                from_smem = mbar_wait(st.bar + buf, (iter >> 1) & 1);
-                if (!from_smem) {
-                    stage_ok = false;
-                    atomicOr(p.status, kStatusStageTimeout);
+    for (int n = 0; item < p.nitems; item += stride, ++n) {
+        const int buf = n & 1;
+        const long long next = item + stride;
+        const SampleRegs cur = pre;
+        bool have_cur = have_pre;
+        const T* sloc = nullptr;
+        const T* sattn = nullptr;
+        if (st.ok) {
+            have_cur = false;
+            if (lane == 0 && next < p.nitems && full(next)) st.issue(p, next, buf ^ 1);
+            if (full(item)) {
+                const bool arrived =
+                    __all_sync(0xffffffffu, mbar_wait(st.bar + buf, (n >> 1) & 1) ? 1 : 0) != 0;
+                if (arrived) {
+                    sloc = st.loc(p, buf);
+                    sattn = st.attn(p, buf);
+                } else {
+                    st.ok = false;
+                    if (lane == 0) atomicOr(p.status, kStatusStageTimeout);
                 }
             }
         }
+        if (!st.ok) {
+            have_pre = next < p.nitems;
+            if (have_pre) pre = load_sample_direct<T>(p, next, 0, lane);
+        }
 
-        const T* sloc = st.loc(buf);
-        const T* sattn = st.attn(buf);
-        const long long item = tile * kWarpsPerCta + warp;
-        if (item < p.nitems) {
-            const int t0 = static_cast<int>(item) * TPC;
-            const int ntask_here = min(TPC, static_cast<int>(p.ntasks - t0));
-            float acc[NV][VEC];
+        const int t0 = static_cast<int>(item) * TPC;
+        const int ntask_here = min(TPC, static_cast<int>(p.ntasks - t0));
+        float acc[NV][VEC];
 
-            for (int chunk = 0; chunk < nchunks; ++chunk) {
-                // ---- phase 1: lane = sample -------------------------------------
-                int tl, s;
-                lane_sample_index(p, chunk, lane, tl, s);
-                const bool active = (tl < ntask_here) && (s < LP);
-                int4 rows = make_int4(-1, -1, -1, -1);
-                float4 wts = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (active) {
-                    const int t = t0 + tl;
-                    float lx, ly, a;
-                    if (from_smem) {
-                        const int li = (warp * TPC + tl) * LP + s;
-                        lx = Elem<T>::to_f(sloc[2 * li]);
-                        ly = Elem<T>::to_f(sloc[2 * li + 1]);
-                        a = Elem<T>::to_f(sattn[li]);
-                    } else {
-                        const long long gi = static_cast<long long>(t) * LP + s;
-                        lx = Elem<T>::to_f(gloc[2 * gi]);
-                        ly = Elem<T>::to_f(gloc[2 * gi + 1]);
-                        a = Elem<T>::to_f(gattn[gi]);
-                    }
-                    const int b = t / QH;
-                    const int h = t % p.H;
-                    const int c = (TPC == 1) ? chunk : 0;
-                    const int row_base = (b * p.K + lv.start(c)) * p.H + h;
-                    SampleGeom geom;
-                    sample_setup(lx, ly, a, lv.w(c), lv.h(c), row_base, p.H, rows, wts, geom);
+        for (int chunk = 0; chunk < nchunks; ++chunk) {
+            // ---- phase 1: lane = sample -----------------------------------------
+            SampleGeom geom;
+            long long gi;
+            phase1<T>(p, lv, chunk, lane, item, ntask_here, sloc, sattn, have_cur, cur, s_slot,
+                      geom, gi);
+            __syncwarp();
+
+            // ---- phase 2: lane = (row slot, piece of row) -----------------------
+            for (int tl2 = 0; tl2 < ntask_here; ++tl2) {
+                int slot_begin, slot_end;
+                if (TPC == 1) {
+                    slot_begin = 0;
+                    slot_end = 4 * min(kChunk, LP - chunk * kChunk);
+                } else {
+                    slot_begin = tl2 * 4 * LP;
+                    slot_end = slot_begin + 4 * LP;
                 }
-                reinterpret_cast<int4*>(s_rows)[lane] = rows;
-                reinterpret_cast<float4*>(s_wts)[lane] = wts;
-                __syncwarp();
-
-                // ---- phase 2: lane = (row slot, piece of row) -------------------
-                for (int tl2 = 0; tl2 < ntask_here; ++tl2) {
-                    int slot_begin, slot_end;
-                    if (TPC == 1) {
-                        slot_begin = 0;
-                        slot_end = 4 * min(kChunk, LP - chunk * kChunk);
-                    } else {
-                        slot_begin = tl2 * 4 * LP;
-                        slot_end = slot_begin + 4 * LP;
-                    }
-                    if (chunk == 0) {
+                if (chunk == 0) {
 #pragma unroll
-                        for (int k = 0; k < NV; ++k)
+                    for (int k = 0; k < NV; ++k)
 #pragma unroll
-                            for (int e = 0; e < VEC; ++e) acc[k][e] = 0.f;
-                    }
+                        for (int e = 0; e < VEC; ++e) acc[k][e] = 0.f;
+                }
 #pragma unroll 1
-                    for (int base = slot_begin; base < slot_end; base += RPI * UNROLL) {
-                        int r[UNROLL];
-                        float w[UNROLL];
+                for (int base = slot_begin; base < slot_end; base += RPI * UNROLL) {
+                    uint2 rec[UNROLL];
+#pragma unroll
+                    for (int u = 0; u < UNROLL; ++u) {
+                        const int slot = base + u * RPI + g;
+                        rec[u] = s_slot[slot & (kSlots - 1)];
+                        // with several tasks per item the slots past slot_end belong to the
+                        // next task; with one task they hold "no row" records already
+                        if (TPC != 1 && slot >= slot_end) rec[u].x = kNoRow;
+                    }
+                    if constexpr (!SCALAR) {
+                        uint4 raw[UNROLL][NV];
 #pragma unroll
                         for (int u = 0; u < UNROLL; ++u) {
-                            const int slot = base + u * RPI + g;
-                            const bool in = slot < slot_end;
-                            r[u] = in ? s_rows[slot] : -1;
-                            w[u] = in ? s_wts[slot] : 0.f;
+#pragma unroll
+                            for (int k = 0; k < NV; ++k) {
+                                raw[u][k] = make_uint4(0u, 0u, 0u, 0u);
+                                if (rec[u].x != kNoRow) {
+                                    raw[u][k] = ldg16(vlane + static_cast<size_t>(rec[u].x) * 16 +
+                                                      k * (LPR * 16));
+                                }
+                            }
                         }
-                        if constexpr (!SCALAR) {
-                            uint4 raw[UNROLL][NV];
 #pragma unroll
-                            for (int u = 0; u < UNROLL; ++u) {
+                        for (int u = 0; u < UNROLL; ++u) {
+                            const float w = __uint_as_float(rec[u].y);
 #pragma unroll
-                                for (int k = 0; k < NV; ++k) {
-                                    raw[u][k] = make_uint4(0u, 0u, 0u, 0u);
-                                    if (r[u] >= 0) {
-                                        raw[u][k] = ldg16(value + static_cast<size_t>(r[u]) * D +
-                                                          (j + k * LPR) * VEC);
-                                    }
+                            for (int k = 0; k < NV; ++k) {
+                                float f[VEC];
+                                unpack16<T>(raw[u][k], f);
+#pragma unroll
+                                for (int e = 0; e < VEC; ++e) acc[k][e] = fmaf(w, f[e], acc[k][e]);
+                            }
+                        }
+                    } else {
+                        float f[UNROLL][NV];
+#pragma unroll
+                        for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+                            for (int k = 0; k < NV; ++k) {
+                                const int c = j + k * 32;
+                                f[u][k] = 0.f;
+                                if (rec[u].x != kNoRow && c < D) {
+                                    f[u][k] = Elem<T>::to_f(
+                                        __ldg(value + static_cast<size_t>(rec[u].x) + c));
                                 }
                             }
+                        }
 #pragma unroll
-                            for (int u = 0; u < UNROLL; ++u) {
+                        for (int u = 0; u < UNROLL; ++u) {
+                            const float w = __uint_as_float(rec[u].y);
 #pragma unroll
-                                for (int k = 0; k < NV; ++k) {
-                                    float f[Elem<T>::kVec];
-                                    unpack16<T>(raw[u][k], f);
-#pragma unroll
-                                    for (int e = 0; e < VEC; ++e)
-                                        acc[k][e] = fmaf(w[u], f[e], acc[k][e]);
-                                }
-                            }
-                        } else {
-                            float f[UNROLL][NV];
-#pragma unroll
-                            for (int u = 0; u < UNROLL; ++u) {
-#pragma unroll
-                                for (int k = 0; k < NV; ++k) {
-                                    const int c = j + k * 32;
-                                    f[u][k] = 0.f;
-                                    if (r[u] >= 0 && c < D) {
-                                        f[u][k] = Elem<T>::to_f(
-                                            __ldg(value + static_cast<size_t>(r[u]) * D + c));
-                                    }
-                                }
-                            }
-#pragma unroll
-                            for (int u = 0; u < UNROLL; ++u)
-#pragma unroll
-                                for (int k = 0; k < NV; ++k)
-                                    acc[k][0] = fmaf(w[u], f[u][k], acc[k][0]);
+                            for (int k = 0; k < NV; ++k) acc[k][0] = fmaf(w, f[u][k], acc[k][0]);
                         }
                     }
+                }
 
-                    // ---- epilogue ----------------------------------------------
-                    if (chunk == nchunks - 1) {
-                        const size_t obase = static_cast<size_t>(t0 + tl2) * D;
+                // ---- epilogue ---------------------------------------------------
+                if (chunk == nchunks - 1) {
+                    const size_t obase = static_cast<size_t>(t0 + tl2) * D;
 #pragma unroll
-                        for (int k = 0; k < NV; ++k) {
+                    for (int k = 0; k < NV; ++k) {
 #pragma unroll
-                            for (int off = LPR; off < 32; off <<= 1) {
+                        for (int off = LPR; off < 32; off <<= 1) {
 #pragma unroll
-                                for (int e = 0; e < VEC; ++e)
-                                    acc[k][e] += __shfl_xor_sync(0xffffffffu, acc[k][e], off);
-                            }
-                            if (g == 0) {
-                                if constexpr (!SCALAR) {
-                                    float f[VEC];
+                            for (int e = 0; e < VEC; ++e)
+                                acc[k][e] += __shfl_xor_sync(0xffffffffu, acc[k][e], off);
+                        }
+                        if (g == 0) {
+                            if constexpr (!SCALAR) {
+                                float f[VEC];
 #pragma unroll
-                                    for (int e = 0; e < VEC; ++e) f[e] = acc[k][e];
-                                    *reinterpret_cast<uint4*>(out + obase + (j + k * LPR) * VEC) =
-                                        pack16<T>(f);
-                                } else {
-                                    const int c = j + k * 32;
-                                    if (c < D) out[obase + c] = Elem<T>::from_f(acc[k][0]);
-                                }
+                                for (int e = 0; e < VEC; ++e) f[e] = acc[k][e];
+                                *reinterpret_cast<uint4*>(out + obase + (j + k * LPR) * VEC) =
+                                    pack16<T>(f);
+                            } else {
+                                const int c = j + k * 32;
+                                if (c < D) out[obase + c] = Elem<T>::from_f(acc[k][0]);
                             }
                         }
                     }
                 }
-                __syncwarp();
             }
+            __syncwarp();
         }
-        if (st.enabled) __syncthreads();
     }
 }
 
@@ -226,45 +217,52 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
 // host side: instantiation table and launch
 // ---------------------------------------------------------------------------
 template <typename T, int LPR, int NV, bool SCALAR>
-static cudaError_t launch_fwd_inst(const Params& p, int grid, size_t smem, cudaStream_t stream) {
+static cudaError_t launch_fwd_inst(const Params& p, const LaunchShape& ls, size_t smem,
+                                   cudaStream_t stream) {
     auto kern = msda_fwd_kernel<T, LPR, NV, SCALAR>;
     if (smem > 48 * 1024) {
         cudaError_t e =
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
+    int grid = 0;
+    cudaError_t e = persistent_grid(reinterpret_cast<const void*>(kern), smem, ls, p, &grid);
+    if (e != cudaSuccess) return e;
     kern<<<grid, kThreadsPerCta, smem, stream>>>(p);
     return cudaGetLastError();
 }
 
 template <typename T>
-static cudaError_t launch_fwd_typed(const Params& p, const RowPlan& rp, int grid, size_t smem,
+static cudaError_t launch_fwd_typed(const Params& p, const RowPlan& rp, const LaunchShape& ls, size_t smem,
                                     cudaStream_t stream) {
-    if (rp.scalar) return launch_fwd_inst<T, 32, 8, true>(p, grid, smem, stream);
+    if (rp.scalar) return launch_fwd_inst<T, 32, 8, true>(p, ls, smem, stream);
     switch (rp.lpr * 100 + rp.nv) {
-        case 101: return launch_fwd_inst<T, 1, 1, false>(p, grid, smem, stream);
-        case 201: return launch_fwd_inst<T, 2, 1, false>(p, grid, smem, stream);
-        case 401: return launch_fwd_inst<T, 4, 1, false>(p, grid, smem, stream);
-        case 801: return launch_fwd_inst<T, 8, 1, false>(p, grid, smem, stream);
-        case 1601: return launch_fwd_inst<T, 16, 1, false>(p, grid, smem, stream);
-        case 3201: return launch_fwd_inst<T, 32, 1, false>(p, grid, smem, stream);
-        case 3202: return launch_fwd_inst<T, 32, 2, false>(p, grid, smem, stream);
+        case 101: return launch_fwd_inst<T, 1, 1, false>(p, ls, smem, stream);
+        case 201: return launch_fwd_inst<T, 2, 1, false>(p, ls, smem, stream);
+        case 401: return launch_fwd_inst<T, 4, 1, false>(p, ls, smem, stream);
+        case 801: return launch_fwd_inst<T, 8, 1, false>(p, ls, smem, stream);
+        case 1601: return launch_fwd_inst<T, 16, 1, false>(p, ls, smem, stream);
+        case 3201: return launch_fwd_inst<T, 32, 1, false>(p, ls, smem, stream);
+        case 3202:
+            if constexpr (sizeof(T) == 4) {
+                return launch_fwd_inst<T, 32, 2, false>(p, ls, smem, stream);
+            }
+            return cudaErrorInvalidValue;
         default: return cudaErrorInvalidValue;
     }
 }
 
-size_t fwd_smem_bytes(const Params& p, size_t elem) {
-    size_t s = p.stage ? stage_smem_bytes(p.tasks_per_item, p.LP, elem) : 0;
-    s = (s + 15) & ~size_t(15);
-    return s + static_cast<size_t>(kWarpsPerCta) * 2 * kSlots * 4 + 16;
+uint32_t fwd_warp_smem(int samples_per_item, size_t elem) {
+    return warp_smem_bytes(samples_per_item, elem, 0);
 }
 
-cudaError_t launch_forward(const Params& p, int dtype, const RowPlan& rp, int grid,
+cudaError_t launch_forward(const Params& p, int dtype, const RowPlan& rp, const LaunchShape& ls,
                            cudaStream_t stream) {
+    const size_t smem = static_cast<size_t>(p.warp_smem) * kWarpsPerCta;
     switch (dtype) {
-        case 0: return launch_fwd_typed<float>(p, rp, grid, fwd_smem_bytes(p, 4), stream);
-        case 1: return launch_fwd_typed<__half>(p, rp, grid, fwd_smem_bytes(p, 2), stream);
-        case 2: return launch_fwd_typed<__nv_bfloat16>(p, rp, grid, fwd_smem_bytes(p, 2), stream);
+        case 0: return launch_fwd_typed<float>(p, rp, ls, smem, stream);
+        case 1: return launch_fwd_typed<__half>(p, rp, ls, smem, stream);
+        case 2: return launch_fwd_typed<__nv_bfloat16>(p, rp, ls, smem, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -17,15 +17,39 @@ struct RowPlan {
     int nv;
 };
 
-cudaError_t launch_forward(const Params& p, int dtype, const RowPlan& rp, int grid,
+// Grid of a persistent launch: `ctas_per_sm` CTAs on each of `sm_count` SMs, or — when
+// ctas_per_sm <= 0 — as many as the occupancy calculator says are resident at once for this
+// kernel and shared-memory size (a CTA that is not resident from the start would run its
+// whole share of the work after the others have finished theirs).
+struct LaunchShape {
+    int sm_count;
+    int ctas_per_sm;
+};
+inline cudaError_t persistent_grid(const void* kernel, size_t smem, const LaunchShape& ls,
+                                   const Params& p, int* grid) {
+    int per_sm = ls.ctas_per_sm;
+    if (per_sm <= 0) {
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel,
+                                                                      kThreadsPerCta, smem);
+        if (e != cudaSuccess) return e;
+        if (per_sm < 1) per_sm = 1;
+    }
+    const long long ctas_needed = (p.nitems + kWarpsPerCta - 1) / kWarpsPerCta;
+    const long long cap = static_cast<long long>(ls.sm_count) * per_sm;
+    *grid = static_cast<int>(ctas_needed < cap ? ctas_needed : cap);
+    return cudaSuccess;
+}
+
+cudaError_t launch_forward(const Params& p, int dtype, const RowPlan& rp, const LaunchShape& ls,
                            cudaStream_t stream);
-size_t fwd_smem_bytes(const Params& p, size_t elem);
+// bytes of dynamic shared memory per warp (goes into Params::warp_smem)
+uint32_t fwd_warp_smem(int samples_per_item, size_t elem);
 
 // acc_f32 != 0: p.grad_value points at fp32 accumulation memory even though
 // the tensors are 16-bit (the caller converts afterwards).
-cudaError_t launch_backward(const Params& p, int dtype, int acc_f32, const RowPlan& rp, int grid,
-                            cudaStream_t stream);
-size_t bwd_smem_bytes(const Params& p, size_t elem);
+cudaError_t launch_backward(const Params& p, int dtype, int acc_f32, const RowPlan& rp,
+                            const LaunchShape& ls, cudaStream_t stream);
+uint32_t bwd_warp_smem(int samples_per_item, size_t elem);
 
 // out[i] = (T)acc[i] for n elements; dtype 1 = fp16, 2 = bf16.
 cudaError_t launch_downcast(const float* acc, void* out, long long n, int dtype,

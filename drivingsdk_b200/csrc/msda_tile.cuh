@@ -6,13 +6,17 @@
 // item  = what one warp handles in one pass: a single task when L*P >= 32
 //         (in ceil(L*P/32) chunks of 32 samples), or floor(32 / (L*P))
 //         consecutive tasks when L*P < 32, so that the lane-parallel set-up
-//         keeps most lanes busy for small L*P.
-// tile  = kWarpsPerCta consecutive items, one per warp of a CTA; its locations
-//         and weights are one contiguous range, which is what the bulk copy
-//         stages into shared memory.
-// CTAs walk tiles in increasing order with a grid stride, so at any moment the
-// whole GPU works on neighbouring queries of the same batch entry and that
-// entry's value pyramid stays L2-resident.
+//         keeps most lanes busy for small L*P. An item's locations and weights
+//         are one contiguous range of memory.
+// Warps are persistent: warp w of CTA c starts at item c*8 + w and advances by
+// gridDim.x*8, so at any moment the whole GPU works on neighbouring queries of
+// the same batch entry and that entry's value pyramid stays L2-resident.
+//
+// While a warp gathers for its current item, the locations and weights of its
+// next item are already on their way: either one lane issues two bulk copies
+// (cp.async.bulk, global -> shared, completion on a per-warp mbarrier) into
+// the warp's other staging buffer, or — where the item's byte ranges are not
+// multiples of 16 — every lane loads its next sample into registers.
 #pragma once
 
 #include "msda_common.cuh"
@@ -29,13 +33,14 @@ struct LaneLevels {
     __device__ __forceinline__ int start(int c) const { return c ? start1 : start0; }
 };
 
+// Which (task within the item, sample within the task) a lane handles in a chunk.
 __device__ __forceinline__ void lane_sample_index(const Params& p, int chunk, int lane,
                                                   int& task_local, int& s) {
     if (p.tasks_per_item == 1) {
         task_local = 0;
         s = chunk * kChunk + lane;
     } else {
-        task_local = lane / p.LP;
+        task_local = static_cast<int>(fd_div(static_cast<uint32_t>(lane), p.fd_lp));
         s = lane - task_local * p.LP;
     }
 }
@@ -67,60 +72,142 @@ __device__ __forceinline__ LaneLevels load_lane_levels(const Params& p, int lane
     return lv;
 }
 
-// Double-buffered staging of one tile's locations and weights.
-template <typename T>
-struct Stage {
-    T* loc0;        // buffer 0 of the location tile; buffer 1 follows it
-    T* attn0;       // buffer 0 of the weight tile; buffer 1 follows it
-    uint64_t* bar;  // two barriers
-    uint32_t loc_bytes, attn_bytes;
-    long long samples_per_tile;
-    long long total_samples;
-    bool enabled;
+// Shared memory of one warp, in this order (all 16-byte aligned):
+//   uint2 slot[kSlots]            records of the current chunk           1024 B
+//   [backward only] float part[]  partial dot products                   part_bytes
+//   uint64_t bar[2]               staging barriers                       16 B
+//   T stage[2][3 * SPI]           staged (x, y) pairs then weights, SPI = samples per item
+constexpr int kSlotBytes = kSlots * 8;
 
-    __device__ __forceinline__ bool full(long long tile) const {
-        return (tile + 1) * samples_per_tile <= total_samples;
+__host__ __device__ inline uint32_t stage_bytes_per_buffer(int samples_per_item, size_t e) {
+    return static_cast<uint32_t>((3 * samples_per_item * e + 15) & ~size_t(15));
+}
+__host__ __device__ inline uint32_t warp_smem_bytes(int samples_per_item, size_t e,
+                                                    uint32_t part_bytes) {
+    return kSlotBytes + part_bytes + 16 + 2 * stage_bytes_per_buffer(samples_per_item, e);
+}
+
+// One lane's sample of chunk 0, loaded ahead of time.
+struct SampleRegs {
+    float lx, ly, a;
+};
+
+// Per-warp staging state. Only the two pointers and the flag live in registers; sizes are
+// recomputed from the kernel parameters (constant bank) where needed.
+template <typename T>
+struct WarpStage {
+    uint64_t* bar;       // [2], followed by the two buffers
+    bool ok;             // staging in use (cleared for good after a timeout)
+
+    __device__ __forceinline__ static uint32_t attn_bytes(const Params& p) {
+        return static_cast<uint32_t>(p.tasks_per_item * p.LP * sizeof(T));
     }
-    __device__ __forceinline__ T* loc(int buf) const { return loc0 + buf * 2 * samples_per_tile; }
-    __device__ __forceinline__ T* attn(int buf) const { return attn0 + buf * samples_per_tile; }
-    __device__ __forceinline__ void issue(const Params& p, long long tile, int buf) const {
-        const T* gl = static_cast<const T*>(p.loc) + tile * samples_per_tile * 2;
-        const T* ga = static_cast<const T*>(p.attn) + tile * samples_per_tile;
-        mbar_expect_tx(bar + buf, loc_bytes + attn_bytes);
-        bulk_g2s(loc(buf), gl, loc_bytes, bar + buf);
-        bulk_g2s(attn(buf), ga, attn_bytes, bar + buf);
+    __device__ __forceinline__ unsigned char* buffer(const Params& p, int b) const {
+        return reinterpret_cast<unsigned char*>(bar) + 16 +
+               b * stage_bytes_per_buffer(p.tasks_per_item * p.LP, sizeof(T));
+    }
+    __device__ __forceinline__ const T* loc(const Params& p, int b) const {
+        return reinterpret_cast<const T*>(buffer(p, b));
+    }
+    __device__ __forceinline__ const T* attn(const Params& p, int b) const {
+        return reinterpret_cast<const T*>(buffer(p, b) + 2 * attn_bytes(p));
+    }
+    // lane 0 only
+    __device__ __forceinline__ void issue(const Params& p, long long item, int b) const {
+        const long long spi = static_cast<long long>(p.tasks_per_item) * p.LP;
+        const T* gl = static_cast<const T*>(p.loc) + item * spi * 2;
+        const T* ga = static_cast<const T*>(p.attn) + item * spi;
+        const uint32_t ab = attn_bytes(p);
+        unsigned char* dst = buffer(p, b);
+        mbar_expect_tx(bar + b, 3 * ab);
+        bulk_g2s(dst, gl, 2 * ab, bar + b);
+        bulk_g2s(dst + 2 * ab, ga, ab, bar + b);
     }
 };
 
-// Carves the staging buffers out of dynamic shared memory (16-byte aligned)
-// and initialises the barriers. Must be called by all threads of the CTA.
 template <typename T>
-__device__ __forceinline__ Stage<T> stage_init(const Params& p, unsigned char* smem) {
-    Stage<T> st;
-    st.samples_per_tile = static_cast<long long>(kWarpsPerCta) * p.tasks_per_item * p.LP;
-    st.total_samples = p.ntasks * p.LP;
-    st.attn_bytes = static_cast<uint32_t>(st.samples_per_tile * sizeof(T));
-    st.loc_bytes = 2 * st.attn_bytes;
-    st.enabled = p.stage != 0;
-    st.bar = reinterpret_cast<uint64_t*>(smem);
-    unsigned char* q = smem + 16;
-    st.loc0 = reinterpret_cast<T*>(q);
-    st.attn0 = reinterpret_cast<T*>(q + 2 * st.loc_bytes);
-    if (st.enabled) {
-        if (threadIdx.x == 0) {
-            mbar_init(&st.bar[0], 1);
-            mbar_init(&st.bar[1], 1);
+__device__ __forceinline__ WarpStage<T> warp_stage_init(const Params& p, unsigned char* base,
+                                                        int lane) {
+    WarpStage<T> st;
+    st.bar = reinterpret_cast<uint64_t*>(base);
+    st.ok = p.stage != 0;
+    if (st.ok) {
+        if (lane == 0) {
+            mbar_init(st.bar, 1);
+            mbar_init(st.bar + 1, 1);
             mbar_fence_init();
         }
-        __syncthreads();
+        __syncwarp();
     }
     return st;
 }
 
-// Bytes of dynamic shared memory stage_init() consumes for element size e.
-__host__ __device__ inline size_t stage_smem_bytes(int tasks_per_item, int LP, size_t e) {
-    const size_t samples = static_cast<size_t>(kWarpsPerCta) * tasks_per_item * LP;
-    return 16 + 2 * 3 * samples * e;
+// Loads this lane's sample of `item` (chunk `chunk`) straight from global memory.
+template <typename T>
+__device__ __forceinline__ SampleRegs load_sample_direct(const Params& p, long long item, int chunk,
+                                                         int lane) {
+    SampleRegs r;
+    r.lx = r.ly = r.a = 0.f;
+    int tl, s;
+    lane_sample_index(p, chunk, lane, tl, s);
+    const long long t = item * p.tasks_per_item + tl;
+    if (tl < p.tasks_per_item && s < p.LP && t < p.ntasks) {
+        const long long gi = t * p.LP + s;
+        const T* gl = static_cast<const T*>(p.loc);
+        r.lx = Elem<T>::to_f(gl[2 * gi]);
+        r.ly = Elem<T>::to_f(gl[2 * gi + 1]);
+        r.a = Elem<T>::to_f(static_cast<const T*>(p.attn)[gi]);
+    }
+    return r;
+}
+
+// Phase 1 of one chunk: lane = sample. Obtains (x, y, weight) — from the staged buffer, from
+// the registers loaded ahead, or directly — and leaves the four slot records of the sample in
+// shared memory. Returns whether this lane holds a sample; `gi` is its global sample index.
+template <typename T>
+__device__ __forceinline__ bool phase1(const Params& p, const LaneLevels& lv, int chunk, int lane,
+                                       long long item, int ntask_here, const T* sloc,
+                                       const T* sattn, bool have_regs, const SampleRegs& regs,
+                                       uint2* s_slot, SampleGeom& geom, long long& gi) {
+    int tl, s;
+    lane_sample_index(p, chunk, lane, tl, s);
+    const bool active = (tl < ntask_here) && (s < p.LP);
+    uint4 rec01 = make_uint4(kNoRow, 0u, kNoRow, 0u);
+    uint4 rec23 = rec01;
+    geom.lw = geom.lh = geom.a = geom.wf = geom.hf = 0.f;
+    geom.valid = false;
+    gi = 0;
+    if (active) {
+        const uint32_t t = static_cast<uint32_t>(item) * p.tasks_per_item + tl;
+        gi = static_cast<long long>(t) * p.LP + s;
+        float lx, ly, a;
+        if (sloc != nullptr) {
+            const int li = tl * p.LP + s;
+            lx = Elem<T>::to_f(sloc[2 * li]);
+            ly = Elem<T>::to_f(sloc[2 * li + 1]);
+            a = Elem<T>::to_f(sattn[li]);
+        } else if (have_regs && chunk == 0) {
+            lx = regs.lx;
+            ly = regs.ly;
+            a = regs.a;
+        } else {
+            const T* gl = static_cast<const T*>(p.loc);
+            lx = Elem<T>::to_f(gl[2 * gi]);
+            ly = Elem<T>::to_f(gl[2 * gi + 1]);
+            a = Elem<T>::to_f(static_cast<const T*>(p.attn)[gi]);
+        }
+        const uint32_t b = fd_div(t, p.fd_qh);
+        const uint32_t h = t - fd_div(t, p.fd_h) * p.H;
+        const int c = (p.tasks_per_item == 1) ? chunk : 0;
+        const uint32_t row_base =
+            (b * static_cast<uint32_t>(p.K) + static_cast<uint32_t>(lv.start(c))) * p.H + h;
+        sample_setup(lx, ly, a, lv.w(c), lv.h(c), row_base, static_cast<uint32_t>(p.H),
+                     p.row_units, rec01, rec23, geom);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(s_slot) + 2 * lane;
+    dst[0] = rec01;
+    dst[1] = rec23;
+    return active;
 }
 
 }  // namespace msda

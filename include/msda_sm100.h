@@ -108,10 +108,12 @@ int msda_sm100_device_status(int clear);
 
 /* Tuning knobs, process-wide. Returns the previous value, or MSDA_ERR_DIMS for
  * an unknown knob. Values < 0 only query.
- *   MSDA_TUNE_STAGE          0 = direct loads of locations/weights,
- *                            1 = bulk-copy (TMA) staging into shared memory (default)
- *   MSDA_TUNE_CTAS_PER_SM    persistent CTAs per SM for the forward kernel (default 4)
- *   MSDA_TUNE_CTAS_PER_SM_BWD  same for the backward kernel (default 4) */
+ *   MSDA_TUNE_STAGE          how a warp gets its next item's locations/weights early:
+ *                            0 = register loads, 1 = bulk copy (TMA) into shared memory
+ *                            (default; falls back to 0 where sizes are not multiples of 16)
+ *   MSDA_TUNE_CTAS_PER_SM    persistent CTAs per SM for the forward kernel
+ *                            (default 0 = as many as are resident at once)
+ *   MSDA_TUNE_CTAS_PER_SM_BWD  same for the backward kernel */
 typedef enum msda_tune {
     MSDA_TUNE_STAGE = 0,
     MSDA_TUNE_CTAS_PER_SM = 1,

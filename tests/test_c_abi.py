@@ -1,0 +1,77 @@
+"""The C-ABI library: loads, exports everything the header declares, validates arguments.
+No kernel is launched here (CPU only)."""
+import ctypes
+import os
+import re
+
+from drivingsdk_b200 import capi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "msda_sm100.h")
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(msda_sm100_\w+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported():
+    lib = ctypes.CDLL(capi.LIB_PATH)
+    names = declared_functions()
+    assert len(names) >= 12
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/msda_sm100.h but not exported"
+
+
+def test_python_signature_table_matches_header():
+    assert sorted(capi.SIGNATURES) == declared_functions()
+
+
+def test_abi_version_and_messages():
+    lib = capi.load()
+    assert lib.msda_sm100_abi_version() == 1
+    assert lib.msda_sm100_strerror(0) == b"ok"
+    for code in range(-7, 0):
+        assert lib.msda_sm100_strerror(code) not in (b"ok", b"unknown status")
+    assert lib.msda_sm100_strerror(-99) == b"unknown status"
+
+
+def test_argument_validation_needs_no_device():
+    lib = capi.load()
+    dims = (1, 4, 2, 8, 1, 3, 2)
+    one = ctypes.c_void_p(16)  # non-null dummy; validation fails before it is ever used
+    # null pointer
+    assert lib.msda_sm100_forward(None, one, one, one, one, one, *dims, capi.F32, None) == -1
+    # unknown dtype
+    assert lib.msda_sm100_forward(one, one, one, one, one, one, *dims, 9, None) == -5
+    # non-positive dimension
+    assert lib.msda_sm100_forward(one, one, one, one, one, one, 0, 4, 2, 8, 1, 3, 2, capi.F32, None) == -2
+    # D > 256
+    assert lib.msda_sm100_forward(one, one, one, one, one, one, 1, 4, 2, 257, 1, 3, 2, capi.F32, None) == -3
+    # L * P > 64
+    assert lib.msda_sm100_forward(one, one, one, one, one, one, 1, 4, 2, 8, 5, 3, 13, capi.F32, None) == -3
+    # backward: same checks
+    assert lib.msda_sm100_backward(one, one, one, one, one, None, one, one, one, *dims, capi.F32, None) == -1
+    assert lib.msda_sm100_backward_ws(one, one, one, one, one, one, one, one, one, None, 0,
+                                      1, 4, 2, 300, 1, 3, 2, capi.BF16, None) == -3
+
+
+def test_byte_counts_follow_the_roofline_formulas():
+    lib = capi.load()
+    B, K, H, D, L, Q, P = 6, 30825, 8, 32, 4, 2500, 8
+    v, s, o = B * K * H * D, B * Q * H * L * P, B * Q * H * D
+    assert lib.msda_sm100_forward_bytes(B, K, H, D, L, Q, P, capi.F32) == 4 * (v + 3 * s + o)
+    assert lib.msda_sm100_backward_bytes(B, K, H, D, L, Q, P, capi.F32) == 4 * (2 * v + 6 * s + o)
+    assert lib.msda_sm100_forward_bytes(B, K, H, D, L, Q, P, capi.BF16) == 2 * (v + 3 * s + o)
+    assert lib.msda_sm100_backward_workspace_bytes(B, K, H, D, capi.F32) == 0
+    assert lib.msda_sm100_backward_workspace_bytes(B, K, H, D, capi.BF16) == 4 * v
+
+
+def test_tuning_knobs_round_trip():
+    lib = capi.load()
+    old = lib.msda_sm100_tune(capi.TUNE_STAGE, 0)
+    assert lib.msda_sm100_tune(capi.TUNE_STAGE, -1) == 0
+    lib.msda_sm100_tune(capi.TUNE_STAGE, old)
+    assert lib.msda_sm100_tune(capi.TUNE_STAGE, -1) == old
+    assert lib.msda_sm100_tune(99, 1) == -2

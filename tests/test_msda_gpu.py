@@ -279,3 +279,48 @@ def test_repeat_runs_agree():
     assert torch.equal(a[0], b[0])
     torch.testing.assert_close(a[1], b[1], rtol=1e-4, atol=1e-5)
     assert torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])
+
+
+def test_mmcv_hook_end_to_end():
+    """A stand-in for mmcv's autograd function, patched by the hook, called the way mmcv
+    models call it (six arguments), forward and backward, against the oracle."""
+    import sys
+    import types
+    from drivingsdk_b200.patcher import MSDA, Patcher, PatchStatus
+
+    class MultiScaleDeformableAttnFunction(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, value, shapes, starts, loc, attn, im2col_step):
+            raise AssertionError("the stock implementation must have been replaced")
+
+        @staticmethod
+        def backward(ctx, grad_output):
+            raise AssertionError("the stock implementation must have been replaced")
+
+    root, ops = types.ModuleType("mmcv"), types.ModuleType("mmcv.ops")
+    mod = types.ModuleType("mmcv.ops.multi_scale_deform_attn")
+    mod.MultiScaleDeformableAttnFunction = MultiScaleDeformableAttnFunction
+    root.ops, ops.multi_scale_deform_attn = ops, mod
+    names = ("mmcv", "mmcv.ops", "mmcv.ops.multi_scale_deform_attn")
+    saved = {k: sys.modules.get(k) for k in names}
+    sys.modules.update(dict(zip(names, (root, ops, mod))))
+    try:
+        p = Patcher().add(MSDA)
+        p.apply()
+        assert [r.status for r in p.results] == [PatchStatus.APPLIED] * 2
+        w = workloads.WORKLOADS["toy"].with_queries(128)
+        inp = workloads.make_inputs(w, torch.float32)
+        dev = parity.to_device(inp, torch.float32)
+        value = dev["value"].clone().requires_grad_(True)
+        loc = dev["loc"].clone().requires_grad_(True)
+        attn = dev["attn"].clone().requires_grad_(True)
+        out = mod.MultiScaleDeformableAttnFunction.apply(value, dev["shapes"], dev["starts"],
+                                                         loc, attn, 64)
+        out.backward(dev["grad_out"])
+        parity.compare_all(inp, (out.detach(), value.grad, loc.grad, attn.grad), torch.float32)
+    finally:
+        for k, v in saved.items():
+            if v is None:
+                sys.modules.pop(k, None)
+            else:
+                sys.modules[k] = v
