@@ -71,32 +71,34 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
     const int LP = p.LP;
     const int D = p.D;
     const int nchunks = (TPC == 1) ? (LP + kChunk - 1) / kChunk : 1;
-    const long long stride = static_cast<long long>(gridDim.x) * kWarpsPerCta;
-    long long item = static_cast<long long>(blockIdx.x) * kWarpsPerCta + warp;
+    ItemWalk walk = make_walk(p, warp);
+    const bool l1 = p.l1_allocate != 0;
     auto full = [&](long long it) { return (it + 1) * TPC <= p.ntasks; };
 
     SampleRegs pre;
     pre.lx = pre.ly = pre.a = 0.f;
     bool have_pre = false;
-    if (item < p.nitems) {
+    if (walk.idx < walk.end) {
         if (st.ok) {
-            if (lane == 0 && full(item)) st.issue(p, item, 0);
+            if (lane == 0 && full(walk.item())) st.issue(p, walk.item(), 0);
         } else {
-            pre = load_sample_direct<T>(p, item, 0, lane);
+            pre = load_sample_direct<T>(p, walk.item(), 0, lane);
             have_pre = true;
         }
     }
 
-    for (int n = 0; item < p.nitems; item += stride, ++n) {
+    for (int n = 0; walk.idx < walk.end; walk.idx += walk.stride, ++n) {
         const int buf = n & 1;
-        const long long next = item + stride;
+        const long long item = walk.item();
+        const bool has_next = walk.idx + walk.stride < walk.end;
+        const long long next = walk.item_at(walk.idx + walk.stride);
         const SampleRegs cur = pre;
         bool have_cur = have_pre;
         const T* sloc = nullptr;
         const T* sattn = nullptr;
         if (st.ok) {
             have_cur = false;
-            if (lane == 0 && next < p.nitems && full(next)) st.issue(p, next, buf ^ 1);
+            if (lane == 0 && has_next && full(next)) st.issue(p, next, buf ^ 1);
             if (full(item)) {
                 const bool arrived =
                     __all_sync(0xffffffffu, mbar_wait(st.bar + buf, (n >> 1) & 1) ? 1 : 0) != 0;
@@ -110,7 +112,7 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
             }
         }
         if (!st.ok) {
-            have_pre = next < p.nitems;
+            have_pre = has_next;
             if (have_pre) pre = load_sample_direct<T>(p, next, 0, lane);
         }
 
@@ -185,8 +187,10 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                             for (int k = 0; k < NV; ++k) {
                                 raw[u][k] = make_uint4(0u, 0u, 0u, 0u);
                                 if (rec[u].x != kNoRow) {
-                                    raw[u][k] = ldg16(vlane + static_cast<size_t>(rec[u].x) * 16 +
-                                                      k * (LPR * 16));
+                                    const void* src = vlane +
+                                                      static_cast<size_t>(rec[u].x) * 16 +
+                                                      k * (LPR * 16);
+                                    raw[u][k] = l1 ? ldg16_l1(src) : ldg16(src);
                                 }
                             }
                         }
@@ -314,7 +318,9 @@ static cudaError_t launch_bwd_inst(const Params& p, const LaunchShape& ls, size_
     int grid = 0;
     cudaError_t e = persistent_grid(reinterpret_cast<const void*>(kern), smem, ls, p, &grid);
     if (e != cudaSuccess) return e;
-    kern<<<grid, kThreadsPerCta, smem, stream>>>(p);
+    Params q = p;
+    q.l1_allocate = ls.l1_allocate;
+    kern<<<grid, kThreadsPerCta, smem, stream>>>(q);
     return cudaGetLastError();
 }
 

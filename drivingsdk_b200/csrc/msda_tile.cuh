@@ -72,6 +72,22 @@ __device__ __forceinline__ LaneLevels load_lane_levels(const Params& p, int lane
     return lv;
 }
 
+// The sequence of items one warp walks through: warp w of CTA c takes items c*8 + w, then
+// + gridDim*8, ... (a CTA's eight warps hold eight consecutive tasks, i.e. with eight heads all
+// heads of one query).
+struct ItemWalk {
+    long long idx, stride, end;
+    __device__ __forceinline__ long long item() const { return idx; }
+    __device__ __forceinline__ long long item_at(long long i) const { return i; }
+};
+__device__ __forceinline__ ItemWalk make_walk(const Params& p, int warp) {
+    ItemWalk w;
+    w.idx = static_cast<long long>(blockIdx.x) * kWarpsPerCta + warp;
+    w.stride = static_cast<long long>(gridDim.x) * kWarpsPerCta;
+    w.end = p.nitems;
+    return w;
+}
+
 // Shared memory of one warp, in this order (all 16-byte aligned):
 //   uint2 slot[kSlots]            records of the current chunk           1024 B
 //   [backward only] float part[]  partial dot products                   part_bytes

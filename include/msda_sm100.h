@@ -113,11 +113,13 @@ int msda_sm100_device_status(int clear);
  *                            (default; falls back to 0 where sizes are not multiples of 16)
  *   MSDA_TUNE_CTAS_PER_SM    persistent CTAs per SM for the forward kernel
  *                            (default 0 = as many as are resident at once)
- *   MSDA_TUNE_CTAS_PER_SM_BWD  same for the backward kernel */
+ *   MSDA_TUNE_CTAS_PER_SM_BWD  same for the backward kernel
+ *   MSDA_TUNE_L1_ALLOCATE    1 = gathered value rows may allocate in L1 (default), 0 = not */
 typedef enum msda_tune {
     MSDA_TUNE_STAGE = 0,
     MSDA_TUNE_CTAS_PER_SM = 1,
-    MSDA_TUNE_CTAS_PER_SM_BWD = 2
+    MSDA_TUNE_CTAS_PER_SM_BWD = 2,
+    MSDA_TUNE_L1_ALLOCATE = 3
 } msda_tune;
 int msda_sm100_tune(int knob, int value);
 
