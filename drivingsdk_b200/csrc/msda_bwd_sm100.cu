@@ -18,6 +18,8 @@
 // over more than 8 lanes, xor shuffles first fold it to 8 partials. In phase 3
 // lane = sample again: it sums the partials of its four corners, forms the
 // three gradients and stores them next to its neighbours' (coalesced).
+#include <type_traits>
+
 #include "msda_launch.h"
 #include "msda_tile.cuh"
 
@@ -26,8 +28,14 @@ namespace msda {
 constexpr int kPartMax = 8;  // partial dot products kept per (sample, corner)
 constexpr int kPartBytes = ((kChunk * (4 * kPartMax + 1) * 4 + 15) / 16) * 16;
 
+// Compile-time tuning, chosen by measurement on B200: three resident CTAs per SM (80
+// registers per thread) and four rows in flight per lane; the kernel is bound by the rate
+// at which L2 retires vector reductions, and more warps in flight made that worse.
 #ifndef MSDA_BWD_MIN_CTAS
 #define MSDA_BWD_MIN_CTAS 3
+#endif
+#ifndef MSDA_BWD_UNROLL
+#define MSDA_BWD_UNROLL 4
 #endif
 
 template <typename T, typename TG, int LPR, int NV, bool SCALAR>
@@ -37,8 +45,9 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
     constexpr int RPI = 32 / LPR;
     constexpr int PART = (LPR < kPartMax) ? LPR : kPartMax;  // partials per slot
     constexpr int SSTRIDE = 4 * PART + 1;                    // per-sample stride (bank spread)
-    constexpr int UNROLL = (RPI >= 16) ? 2 : 4;
-    static_assert(kSlots % (RPI * UNROLL) == 0, "slot loop must tile the slot array");
+    constexpr int UNROLL = (RPI >= 16) ? 2 : MSDA_BWD_UNROLL;
+    constexpr int STEP = RPI * UNROLL;
+    static_assert(kSlots % STEP == 0 && STEP <= kSlotPad, "slot loop must tile the slots");
     // 16-bit operands accumulated in fp32: a lane's 16-byte piece of the value row is 8
     // channels, i.e. 32 bytes of the fp32 accumulation row. Two reductions at +0 and +16
     // bytes of that span would touch every 32-byte sector of the row with half a sector each
@@ -72,33 +81,22 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
     const int D = p.D;
     const int nchunks = (TPC == 1) ? (LP + kChunk - 1) / kChunk : 1;
     ItemWalk walk = make_walk(p, warp);
-    const bool l1 = p.l1_allocate != 0;
     auto full = [&](long long it) { return (it + 1) * TPC <= p.ntasks; };
 
-    SampleRegs pre;
-    pre.lx = pre.ly = pre.a = 0.f;
-    bool have_pre = false;
-    if (walk.idx < walk.end) {
-        if (st.ok) {
-            if (lane == 0 && full(walk.item())) st.issue(p, walk.item(), 0);
-        } else {
-            pre = load_sample_direct<T>(p, walk.item(), 0, lane);
-            have_pre = true;
-        }
+    if (st.ok && lane == 0 && walk.idx < walk.end && full(walk.item())) {
+        st.issue(p, walk.item(), 0);
     }
 
     for (int n = 0; walk.idx < walk.end; walk.idx += walk.stride, ++n) {
         const int buf = n & 1;
         const long long item = walk.item();
-        const bool has_next = walk.idx + walk.stride < walk.end;
-        const long long next = walk.item_at(walk.idx + walk.stride);
-        const SampleRegs cur = pre;
-        bool have_cur = have_pre;
         const T* sloc = nullptr;
         const T* sattn = nullptr;
         if (st.ok) {
-            have_cur = false;
-            if (lane == 0 && has_next && full(next)) st.issue(p, next, buf ^ 1);
+            const long long next = walk.item_at(walk.idx + walk.stride);
+            if (lane == 0 && walk.idx + walk.stride < walk.end && full(next)) {
+                st.issue(p, next, buf ^ 1);
+            }
             if (full(item)) {
                 const bool arrived =
                     __all_sync(0xffffffffu, mbar_wait(st.bar + buf, (n >> 1) & 1) ? 1 : 0) != 0;
@@ -111,10 +109,6 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                 }
             }
         }
-        if (!st.ok) {
-            have_pre = has_next;
-            if (have_pre) pre = load_sample_direct<T>(p, next, 0, lane);
-        }
 
         const int t0 = static_cast<int>(item) * TPC;
         const int ntask_here = min(TPC, static_cast<int>(p.ntasks - t0));
@@ -123,19 +117,21 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
             // ---- phase 1: lane = sample -----------------------------------------
             SampleGeom geom;
             long long gi;
-            const bool active = phase1<T>(p, lv, chunk, lane, item, ntask_here, sloc, sattn,
-                                          have_cur, cur, s_slot, geom, gi);
+            const bool active =
+                phase1<T>(p, lv, chunk, lane, item, ntask_here, sloc, sattn, s_slot, geom, gi);
             __syncwarp();
 
             // ---- phase 2: lane = (row slot, piece of row) -----------------------
             for (int tl2 = 0; tl2 < ntask_here; ++tl2) {
-                int slot_begin, slot_end;
+                int slot_begin, slot_end, unguarded_end;
                 if (TPC == 1) {
                     slot_begin = 0;
                     slot_end = 4 * min(kChunk, LP - chunk * kChunk);
+                    unguarded_end = slot_end;
                 } else {
                     slot_begin = tl2 * 4 * LP;
                     slot_end = slot_begin + 4 * LP;
+                    unguarded_end = slot_end - STEP + 1;
                 }
                 // this lane's piece of grad_out[b, q, h, :]
                 float go[NV][VEC];
@@ -168,47 +164,44 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                         }
                     }
                 }
-#pragma unroll 1
-                for (int base = slot_begin; base < slot_end; base += RPI * UNROLL) {
+
+                auto scatter_gather = [&](int base, auto guarded_tag) {
+                    constexpr bool GUARDED = decltype(guarded_tag)::value;
+                    const uint2* sp = s_slot + base + g;
                     uint2 rec[UNROLL];
                     float part[UNROLL];
 #pragma unroll
                     for (int u = 0; u < UNROLL; ++u) {
-                        const int slot = base + u * RPI + g;
-                        rec[u] = s_slot[slot & (kSlots - 1)];
-                        if (TPC != 1 && slot >= slot_end) rec[u].x = kNoRow;
+                        rec[u] = sp[u * RPI];
+                        if (GUARDED && base + u * RPI + g >= slot_end) rec[u].x = kNoRow;
                         part[u] = 0.f;
                     }
                     if constexpr (!SCALAR) {
+                        // A missing corner loads row 0 instead of branching around the load;
+                        // it is skipped below, so it neither scatters nor contributes.
                         uint4 raw[UNROLL][NV];
 #pragma unroll
                         for (int u = 0; u < UNROLL; ++u) {
+                            const uint32_t off = (rec[u].x != kNoRow) ? rec[u].x : 0u;
 #pragma unroll
-                            for (int k = 0; k < NV; ++k) {
-                                raw[u][k] = make_uint4(0u, 0u, 0u, 0u);
-                                if (rec[u].x != kNoRow) {
-                                    const void* src = vlane +
-                                                      static_cast<size_t>(rec[u].x) * 16 +
-                                                      k * (LPR * 16);
-                                    raw[u][k] = l1 ? ldg16_l1(src) : ldg16(src);
-                                }
-                            }
+                            for (int k = 0; k < NV; ++k)
+                                raw[u][k] =
+                                    ldg16(vlane + static_cast<size_t>(off) * 16 + k * (LPR * 16));
                         }
 #pragma unroll
                         for (int u = 0; u < UNROLL; ++u) {
-                            const float w = __uint_as_float(rec[u].y);
+                            if (rec[u].x != kNoRow) {
+                                const float w = __uint_as_float(rec[u].y);
+                                if constexpr (SPLIT_RED) {
+                                    float* row = reinterpret_cast<float*>(
+                                        glane + static_cast<size_t>(rec[u].x) * 32);
+                                    red_add_f32x4(row, w * gred[0][0], w * gred[0][1],
+                                                  w * gred[0][2], w * gred[0][3]);
+                                    red_add_f32x4(row + LPR * 4, w * gred[1][0], w * gred[1][1],
+                                                  w * gred[1][2], w * gred[1][3]);
+                                } else {
 #pragma unroll
-                            for (int k = 0; k < NV; ++k) {
-                                if (rec[u].x != kNoRow) {
-                                    if constexpr (SPLIT_RED) {
-                                        float* row = reinterpret_cast<float*>(
-                                            glane + static_cast<size_t>(rec[u].x) * 32);
-                                        red_add_f32x4(row, w * gred[0][0], w * gred[0][1],
-                                                      w * gred[0][2], w * gred[0][3]);
-                                        red_add_f32x4(row + LPR * 4, w * gred[1][0],
-                                                      w * gred[1][1], w * gred[1][2],
-                                                      w * gred[1][3]);
-                                    } else {
+                                    for (int k = 0; k < NV; ++k) {
                                         float contrib[VEC];
 #pragma unroll
                                         for (int e = 0; e < VEC; ++e) contrib[e] = w * go[k][e];
@@ -219,11 +212,14 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                                             contrib);
                                     }
                                 }
-                                float f[VEC];
-                                unpack16<T>(raw[u][k], f);
 #pragma unroll
-                                for (int e = 0; e < VEC; ++e)
-                                    part[u] = fmaf(f[e], go[k][e], part[u]);
+                                for (int k = 0; k < NV; ++k) {
+                                    float f[VEC];
+                                    unpack16<T>(raw[u][k], f);
+#pragma unroll
+                                    for (int e = 0; e < VEC; ++e)
+                                        part[u] = fmaf(f[e], go[k][e], part[u]);
+                                }
                             }
                         }
                     } else {
@@ -249,11 +245,17 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                         for (int off = LPR / 2; off >= PART; off >>= 1)
                             part[u] += __shfl_xor_sync(0xffffffffu, part[u], off);
                         const int slot = base + u * RPI + g;
-                        if (slot < slot_end && j < PART) {
+                        if ((!GUARDED || slot < slot_end) && j < PART) {
                             s_part[(slot >> 2) * SSTRIDE + (slot & 3) * PART + j] = part[u];
                         }
                     }
-                }
+                };
+
+                int base = slot_begin;
+#pragma unroll 1
+                for (; base < unguarded_end; base += STEP) scatter_gather(base, std::false_type{});
+#pragma unroll 1
+                for (; base < slot_end; base += STEP) scatter_gather(base, std::true_type{});
             }
             __syncwarp();
 
@@ -318,9 +320,7 @@ static cudaError_t launch_bwd_inst(const Params& p, const LaunchShape& ls, size_
     int grid = 0;
     cudaError_t e = persistent_grid(reinterpret_cast<const void*>(kern), smem, ls, p, &grid);
     if (e != cudaSuccess) return e;
-    Params q = p;
-    q.l1_allocate = ls.l1_allocate;
-    kern<<<grid, kThreadsPerCta, smem, stream>>>(q);
+    kern<<<grid, kThreadsPerCta, smem, stream>>>(p);
     return cudaGetLastError();
 }
 

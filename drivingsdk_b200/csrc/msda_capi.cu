@@ -22,7 +22,6 @@ __device__ int g_status_word;
 std::atomic<int> g_tune_stage{1};
 std::atomic<int> g_tune_cps_fwd{0};
 std::atomic<int> g_tune_cps_bwd{0};
-std::atomic<int> g_tune_l1{1};
 std::atomic<long long> g_launches{0};
 thread_local int t_last_cuda_error = 0;
 thread_local cudaEvent_t t_prof[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -214,7 +213,7 @@ int backward_impl(const void* value, const int32_t* shapes, const int32_t* start
     cudaError_t ce = cudaMemsetAsync(acc, 0, acc_bytes, stream);
     if (ce != cudaSuccess) return fail_cuda(ce);
     prof_record(2, stream);
-    ce = msda::launch_backward(p, dtype, acc_f32 ? 1 : 0, rp, msda::LaunchShape{dev->sm_count, g_tune_cps_bwd.load(), g_tune_l1.load()},
+    ce = msda::launch_backward(p, dtype, acc_f32 ? 1 : 0, rp, msda::LaunchShape{dev->sm_count, g_tune_cps_bwd.load()},
                                stream);
     prof_record(3, stream);
     if (ce != cudaSuccess) return fail_cuda(ce);
@@ -257,7 +256,7 @@ int msda_sm100_forward(const void* value, const int32_t* spatial_shapes,
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     prof_record(0, stream);
     cudaError_t ce =
-        msda::launch_forward(p, dtype, rp, msda::LaunchShape{dev->sm_count, g_tune_cps_fwd.load(), g_tune_l1.load()}, stream);
+        msda::launch_forward(p, dtype, rp, msda::LaunchShape{dev->sm_count, g_tune_cps_fwd.load()}, stream);
     prof_record(1, stream);
     if (ce != cudaSuccess) return fail_cuda(ce);
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -329,7 +328,6 @@ int msda_sm100_tune(int knob, int value) {
         case MSDA_TUNE_STAGE: target = &g_tune_stage; break;
         case MSDA_TUNE_CTAS_PER_SM: target = &g_tune_cps_fwd; break;
         case MSDA_TUNE_CTAS_PER_SM_BWD: target = &g_tune_cps_bwd; break;
-        case MSDA_TUNE_L1_ALLOCATE: target = &g_tune_l1; break;
         default: return MSDA_ERR_DIMS;
     }
     if (value < 0) return target->load();

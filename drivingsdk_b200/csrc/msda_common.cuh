@@ -28,6 +28,7 @@ constexpr int kWarpsPerCta = 8;
 constexpr int kThreadsPerCta = kWarpsPerCta * 32;
 constexpr int kChunk = 32;          // samples handled by one warp pass
 constexpr int kSlots = 4 * kChunk;  // (sample, corner) pairs per warp pass
+constexpr int kSlotPad = 64;         // readable (never used) records past the last slot
 constexpr int kSpinLimit = 1 << 18; // bound on mbarrier polling
 
 // Device status bits, sticky until read by msda_sm100_device_status().
@@ -81,11 +82,11 @@ struct Params {
     int LP;             // L * P
     int tasks_per_item; // consecutive (b, q, h) tasks one warp pass covers
     int use_table;
-    int stage;          // 1: each warp bulk-copies its next item's locations/weights to shared memory
+    int stage;          // 1: each warp bulk-copies its next item's locations/weights to shared
+                        // memory while it works on the current one; 0: direct loads
     long long ntasks;   // B * Q * H
     long long nitems;   // ceil(ntasks / tasks_per_item)
     int* status;        // device status word
-    int l1_allocate;         // 1: gathered value rows may allocate in L1
     uint32_t row_units;      // offset units per value row: 16-byte pieces, or elements (scalar path)
     uint32_t warp_smem;      // bytes of dynamic shared memory per warp
     FastDiv fd_qh, fd_h, fd_lp;  // division by Q*H, H, L*P
@@ -112,17 +113,10 @@ template <> struct Elem<__nv_bfloat16> {
     __device__ static __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
 };
 
-// 16-byte read-only loads of gathered value rows, without and with allocation in L1. Rows are
-// reused mostly across SMs (through L2); letting them allocate in L1 as well measured a few
-// percent faster on pyramids whose smallest levels are hit often, and never slower.
+// 16-byte read-only load of a piece of a gathered value row. Rows are reused mostly across
+// SMs (through L2); letting them allocate in L1 as well (evict-last) measured a few percent
+// faster on pyramids whose smallest levels are hit often, and never slower.
 __device__ __forceinline__ uint4 ldg16(const void* p) {
-    uint4 r;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                 : "l"(p));
-    return r;
-}
-__device__ __forceinline__ uint4 ldg16_l1(const void* p) {
     uint4 r;
     asm volatile("ld.global.nc.L1::evict_last.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)

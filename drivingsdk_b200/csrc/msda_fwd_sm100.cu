@@ -6,22 +6,30 @@
 //
 // One warp per (batch, query, head) task (several tasks per warp when L*P < 32).
 //   phase 1  lane = sample: take (x, y, weight) — bulk-copied to shared memory
-//            or loaded ahead into registers while the previous item was being
-//            gathered — and leave one 8-byte record per corner in shared
-//            memory: {offset of the value row, bilinear weight * attention}.
+//            while the previous item was being gathered — and leave one
+//            8-byte record per corner in shared memory: {offset of the value
+//            row, bilinear weight * attention}.
 //   phase 2  lane = (row slot, 16-byte piece of the row): the warp reads
 //            32/LPR whole rows per instruction (LPR lanes x 16 bytes = one
-//            contiguous row), eight instructions in flight, and accumulates
+//            contiguous row), four instructions in flight, and accumulates
 //            in fp32 registers.
 //   epilogue the row-slot groups are summed with xor shuffles and one group
 //            writes the D outputs as 16-byte stores.
 // Rows whose byte length is not 16 * 2^k take the SCALAR instantiation: lane =
 // channel (mod 32), one row per instruction.
+#include <type_traits>
+
 #include "msda_launch.h"
 #include "msda_tile.cuh"
 
+// Compile-time tuning, chosen by measurement on B200 (BEVFormer / Deformable-DETR shapes):
+// four resident CTAs per SM (64 registers per thread, no spills) with four row loads in
+// flight per lane beat both deeper unrolling (spills) and more CTAs (fewer registers).
 #ifndef MSDA_FWD_MIN_CTAS
 #define MSDA_FWD_MIN_CTAS 4
+#endif
+#ifndef MSDA_FWD_UNROLL
+#define MSDA_FWD_UNROLL 4
 #endif
 
 namespace msda {
@@ -31,8 +39,10 @@ __global__ void __launch_bounds__(kThreadsPerCta, (SCALAR || NV > 1) ? 2 : MSDA_
 msda_fwd_kernel(const __grid_constant__ Params p) {
     constexpr int VEC = SCALAR ? 1 : Elem<T>::kVec;
     constexpr int RPI = 32 / LPR;                  // rows per warp instruction
-    constexpr int UNROLL = (RPI >= 16) ? 2 : ((NV > 2) ? 4 : 8);
-    static_assert(kSlots % (RPI * UNROLL) == 0, "slot loop must tile the slot array");
+    constexpr int UNROLL =
+        (RPI >= 16) ? 2 : ((NV > 2) ? 4 : MSDA_FWD_UNROLL);
+    constexpr int STEP = RPI * UNROLL;             // slots per trip of the gather loop
+    static_assert(kSlots % STEP == 0 && STEP <= kSlotPad, "slot loop must tile the slots");
 
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5;
@@ -54,33 +64,22 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
     const int D = p.D;
     const int nchunks = (TPC == 1) ? (LP + kChunk - 1) / kChunk : 1;
     ItemWalk walk = make_walk(p, warp);
-    const bool l1 = p.l1_allocate != 0;
     auto full = [&](long long it) { return (it + 1) * TPC <= p.ntasks; };
 
-    SampleRegs pre;
-    pre.lx = pre.ly = pre.a = 0.f;
-    bool have_pre = false;
-    if (walk.idx < walk.end) {
-        if (st.ok) {
-            if (lane == 0 && full(walk.item())) st.issue(p, walk.item(), 0);
-        } else {
-            pre = load_sample_direct<T>(p, walk.item(), 0, lane);
-            have_pre = true;
-        }
+    if (st.ok && lane == 0 && walk.idx < walk.end && full(walk.item())) {
+        st.issue(p, walk.item(), 0);
     }
 
     for (int n = 0; walk.idx < walk.end; walk.idx += walk.stride, ++n) {
         const int buf = n & 1;
         const long long item = walk.item();
-        const bool has_next = walk.idx + walk.stride < walk.end;
-        const long long next = walk.item_at(walk.idx + walk.stride);
-        const SampleRegs cur = pre;
-        bool have_cur = have_pre;
         const T* sloc = nullptr;
         const T* sattn = nullptr;
         if (st.ok) {
-            have_cur = false;
-            if (lane == 0 && has_next && full(next)) st.issue(p, next, buf ^ 1);
+            const long long next = walk.item_at(walk.idx + walk.stride);
+            if (lane == 0 && walk.idx + walk.stride < walk.end && full(next)) {
+                st.issue(p, next, buf ^ 1);
+            }
             if (full(item)) {
                 const bool arrived =
                     __all_sync(0xffffffffu, mbar_wait(st.bar + buf, (n >> 1) & 1) ? 1 : 0) != 0;
@@ -93,10 +92,6 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
                 }
             }
         }
-        if (!st.ok) {
-            have_pre = has_next;
-            if (have_pre) pre = load_sample_direct<T>(p, next, 0, lane);
-        }
 
         const int t0 = static_cast<int>(item) * TPC;
         const int ntask_here = min(TPC, static_cast<int>(p.ntasks - t0));
@@ -106,19 +101,22 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
             // ---- phase 1: lane = sample -----------------------------------------
             SampleGeom geom;
             long long gi;
-            phase1<T>(p, lv, chunk, lane, item, ntask_here, sloc, sattn, have_cur, cur, s_slot,
-                      geom, gi);
+            phase1<T>(p, lv, chunk, lane, item, ntask_here, sloc, sattn, s_slot, geom, gi);
             __syncwarp();
 
             // ---- phase 2: lane = (row slot, piece of row) -----------------------
             for (int tl2 = 0; tl2 < ntask_here; ++tl2) {
-                int slot_begin, slot_end;
+                int slot_begin, slot_end, unguarded_end;
                 if (TPC == 1) {
+                    // slots past the last sample hold "no row" records: no guard needed
                     slot_begin = 0;
                     slot_end = 4 * min(kChunk, LP - chunk * kChunk);
+                    unguarded_end = slot_end;
                 } else {
+                    // slots past slot_end belong to the next task: the last trip is guarded
                     slot_begin = tl2 * 4 * LP;
                     slot_end = slot_begin + 4 * LP;
+                    unguarded_end = slot_end - STEP + 1;
                 }
                 if (chunk == 0) {
 #pragma unroll
@@ -126,30 +124,28 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
 #pragma unroll
                         for (int e = 0; e < VEC; ++e) acc[k][e] = 0.f;
                 }
-#pragma unroll 1
-                for (int base = slot_begin; base < slot_end; base += RPI * UNROLL) {
+
+                auto gather = [&](int base, auto guarded_tag) {
+                    constexpr bool GUARDED = decltype(guarded_tag)::value;
+                    const uint2* sp = s_slot + base + g;
                     uint2 rec[UNROLL];
 #pragma unroll
                     for (int u = 0; u < UNROLL; ++u) {
-                        const int slot = base + u * RPI + g;
-                        rec[u] = s_slot[slot & (kSlots - 1)];
-                        // with several tasks per item the slots past slot_end belong to the
-                        // next task; with one task they hold "no row" records already
-                        if (TPC != 1 && slot >= slot_end) rec[u].x = kNoRow;
+                        rec[u] = sp[u * RPI];
+                        if (GUARDED && base + u * RPI + g >= slot_end) rec[u].x = kNoRow;
                     }
                     if constexpr (!SCALAR) {
+                        // A missing corner loads nothing and reads as zeros (its weight is
+                        // zero as well, so it adds nothing — and no 0 * NaN can arise).
                         uint4 raw[UNROLL][NV];
 #pragma unroll
                         for (int u = 0; u < UNROLL; ++u) {
 #pragma unroll
                             for (int k = 0; k < NV; ++k) {
                                 raw[u][k] = make_uint4(0u, 0u, 0u, 0u);
-                                if (rec[u].x != kNoRow) {
-                                    const void* src = vlane +
-                                                      static_cast<size_t>(rec[u].x) * 16 +
-                                                      k * (LPR * 16);
-                                    raw[u][k] = l1 ? ldg16_l1(src) : ldg16(src);
-                                }
+                                if (rec[u].x != kNoRow)
+                                    raw[u][k] = ldg16(vlane + static_cast<size_t>(rec[u].x) * 16 +
+                                                      k * (LPR * 16));
                             }
                         }
 #pragma unroll
@@ -184,7 +180,13 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
                             for (int k = 0; k < NV; ++k) acc[k][0] = fmaf(w, f[u][k], acc[k][0]);
                         }
                     }
-                }
+                };
+
+                int base = slot_begin;
+#pragma unroll 1
+                for (; base < unguarded_end; base += STEP) gather(base, std::false_type{});
+#pragma unroll 1
+                for (; base < slot_end; base += STEP) gather(base, std::true_type{});
 
                 // ---- epilogue ---------------------------------------------------
                 if (chunk == nchunks - 1) {
@@ -232,9 +234,7 @@ static cudaError_t launch_fwd_inst(const Params& p, const LaunchShape& ls, size_
     int grid = 0;
     cudaError_t e = persistent_grid(reinterpret_cast<const void*>(kern), smem, ls, p, &grid);
     if (e != cudaSuccess) return e;
-    Params q = p;
-    q.l1_allocate = ls.l1_allocate;
-    kern<<<grid, kThreadsPerCta, smem, stream>>>(q);
+    kern<<<grid, kThreadsPerCta, smem, stream>>>(p);
     return cudaGetLastError();
 }
 

@@ -24,7 +24,6 @@ struct RowPlan {
 struct LaunchShape {
     int sm_count;
     int ctas_per_sm;
-    int l1_allocate;
 };
 inline cudaError_t persistent_grid(const void* kernel, size_t smem, const LaunchShape& ls,
                                    const Params& p, int* grid) {

@@ -13,10 +13,11 @@
 // the same batch entry and that entry's value pyramid stays L2-resident.
 //
 // While a warp gathers for its current item, the locations and weights of its
-// next item are already on their way: either one lane issues two bulk copies
+// next item are already on their way: one lane issues two bulk copies
 // (cp.async.bulk, global -> shared, completion on a per-warp mbarrier) into
-// the warp's other staging buffer, or — where the item's byte ranges are not
-// multiples of 16 — every lane loads its next sample into registers.
+// the warp's other staging buffer. Where an item's byte ranges are not
+// multiples of 16 (odd L*P with odd task counts, misaligned tensors) the warp
+// loads its samples directly instead.
 #pragma once
 
 #include "msda_common.cuh"
@@ -89,11 +90,11 @@ __device__ __forceinline__ ItemWalk make_walk(const Params& p, int warp) {
 }
 
 // Shared memory of one warp, in this order (all 16-byte aligned):
-//   uint2 slot[kSlots]            records of the current chunk           1024 B
+//   uint2 slot[kSlots + kSlotPad] records of the current chunk (+ padding) 1536 B
 //   [backward only] float part[]  partial dot products                   part_bytes
 //   uint64_t bar[2]               staging barriers                       16 B
 //   T stage[2][3 * SPI]           staged (x, y) pairs then weights, SPI = samples per item
-constexpr int kSlotBytes = kSlots * 8;
+constexpr int kSlotBytes = (kSlots + kSlotPad) * 8;
 
 __host__ __device__ inline uint32_t stage_bytes_per_buffer(int samples_per_item, size_t e) {
     return static_cast<uint32_t>((3 * samples_per_item * e + 15) & ~size_t(15));
@@ -102,11 +103,6 @@ __host__ __device__ inline uint32_t warp_smem_bytes(int samples_per_item, size_t
                                                     uint32_t part_bytes) {
     return kSlotBytes + part_bytes + 16 + 2 * stage_bytes_per_buffer(samples_per_item, e);
 }
-
-// One lane's sample of chunk 0, loaded ahead of time.
-struct SampleRegs {
-    float lx, ly, a;
-};
 
 // Per-warp staging state. Only the two pointers and the flag live in registers; sizes are
 // recomputed from the kernel parameters (constant bank) where needed.
@@ -158,33 +154,14 @@ __device__ __forceinline__ WarpStage<T> warp_stage_init(const Params& p, unsigne
     return st;
 }
 
-// Loads this lane's sample of `item` (chunk `chunk`) straight from global memory.
-template <typename T>
-__device__ __forceinline__ SampleRegs load_sample_direct(const Params& p, long long item, int chunk,
-                                                         int lane) {
-    SampleRegs r;
-    r.lx = r.ly = r.a = 0.f;
-    int tl, s;
-    lane_sample_index(p, chunk, lane, tl, s);
-    const long long t = item * p.tasks_per_item + tl;
-    if (tl < p.tasks_per_item && s < p.LP && t < p.ntasks) {
-        const long long gi = t * p.LP + s;
-        const T* gl = static_cast<const T*>(p.loc);
-        r.lx = Elem<T>::to_f(gl[2 * gi]);
-        r.ly = Elem<T>::to_f(gl[2 * gi + 1]);
-        r.a = Elem<T>::to_f(static_cast<const T*>(p.attn)[gi]);
-    }
-    return r;
-}
-
-// Phase 1 of one chunk: lane = sample. Obtains (x, y, weight) — from the staged buffer, from
-// the registers loaded ahead, or directly — and leaves the four slot records of the sample in
-// shared memory. Returns whether this lane holds a sample; `gi` is its global sample index.
+// Phase 1 of one chunk: lane = sample. Obtains (x, y, weight) — from the staged buffer or
+// directly — and leaves the four slot records of the sample in shared memory. Returns whether
+// this lane holds a sample; `gi` is its global sample index.
 template <typename T>
 __device__ __forceinline__ bool phase1(const Params& p, const LaneLevels& lv, int chunk, int lane,
                                        long long item, int ntask_here, const T* sloc,
-                                       const T* sattn, bool have_regs, const SampleRegs& regs,
-                                       uint2* s_slot, SampleGeom& geom, long long& gi) {
+                                       const T* sattn, uint2* s_slot, SampleGeom& geom,
+                                       long long& gi) {
     int tl, s;
     lane_sample_index(p, chunk, lane, tl, s);
     const bool active = (tl < ntask_here) && (s < p.LP);
@@ -202,10 +179,6 @@ __device__ __forceinline__ bool phase1(const Params& p, const LaneLevels& lv, in
             lx = Elem<T>::to_f(sloc[2 * li]);
             ly = Elem<T>::to_f(sloc[2 * li + 1]);
             a = Elem<T>::to_f(sattn[li]);
-        } else if (have_regs && chunk == 0) {
-            lx = regs.lx;
-            ly = regs.ly;
-            a = regs.a;
         } else {
             const T* gl = static_cast<const T*>(p.loc);
             lx = Elem<T>::to_f(gl[2 * gi]);

@@ -108,18 +108,17 @@ int msda_sm100_device_status(int clear);
 
 /* Tuning knobs, process-wide. Returns the previous value, or MSDA_ERR_DIMS for
  * an unknown knob. Values < 0 only query.
- *   MSDA_TUNE_STAGE          how a warp gets its next item's locations/weights early:
- *                            0 = register loads, 1 = bulk copy (TMA) into shared memory
- *                            (default; falls back to 0 where sizes are not multiples of 16)
+ *   MSDA_TUNE_STAGE          1 = a warp bulk-copies (TMA) its next item's locations/weights
+ *                            into shared memory while it works on the current item
+ *                            (default; not used where sizes are not multiples of 16),
+ *                            0 = direct loads
  *   MSDA_TUNE_CTAS_PER_SM    persistent CTAs per SM for the forward kernel
  *                            (default 0 = as many as are resident at once)
- *   MSDA_TUNE_CTAS_PER_SM_BWD  same for the backward kernel
- *   MSDA_TUNE_L1_ALLOCATE    1 = gathered value rows may allocate in L1 (default), 0 = not */
+ *   MSDA_TUNE_CTAS_PER_SM_BWD  same for the backward kernel */
 typedef enum msda_tune {
     MSDA_TUNE_STAGE = 0,
     MSDA_TUNE_CTAS_PER_SM = 1,
-    MSDA_TUNE_CTAS_PER_SM_BWD = 2,
-    MSDA_TUNE_L1_ALLOCATE = 3
+    MSDA_TUNE_CTAS_PER_SM_BWD = 2
 } msda_tune;
 int msda_sm100_tune(int knob, int value);
 
