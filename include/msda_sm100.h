@@ -95,6 +95,39 @@ int msda_sm100_backward_ws(const void* value, const int32_t* spatial_shapes,
                            void* workspace, size_t workspace_bytes, int B, int K, int H, int D,
                            int L, int Q, int P, int dtype, void* stream);
 
+/* Backward for callers that cannot allocate device memory. It has no counterpart
+ * in the reference (there the framework allocates the operator's workspace for
+ * it). Who needs it: a host whose device memory is fully planned before the
+ * first operator runs — an inference/training runtime that owns all memory in
+ * its own arena, a plug-in inside such a process, a latency-critical loop where
+ * calling the device allocator is forbidden — and that therefore cannot hand a
+ * workspace to msda_sm100_backward_ws(). The fp32 accumulation scratch lives
+ * inside the library instead: one static device array of
+ * MSDA_SM100_STATIC_SCRATCH_BYTES bytes, reserved by the driver on every GPU
+ * that loads this library and held until the process exits.
+ *   - Same operands, results and numerics as msda_sm100_backward_ws(); the
+ *     caller still passes every input and output. For MSDA_F32 no scratch is
+ *     involved and the call equals msda_sm100_backward().
+ *   - Limit: 4 * B*K*H*D bytes must not exceed MSDA_SM100_STATIC_SCRATCH_BYTES
+ *     (16-bit dtypes); larger problems are refused with MSDA_ERR_WORKSPACE
+ *     before anything is enqueued.
+ *   - It calls no allocation or free routine. The first call on each device
+ *     looks up the array's device address (and makes the driver load the
+ *     module there); make that first call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps whatever the last
+ *     call left in it; each call zero-fills the part it uses, on `stream`,
+ *     before accumulating. Two calls that overlap on the GPU (different
+ *     streams, or different host threads without stream ordering) race on it:
+ *     serialise them. */
+#define MSDA_SM100_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+size_t msda_sm100_static_scratch_bytes(void);
+int msda_sm100_backward_static(const void* value, const int32_t* spatial_shapes,
+                               const int32_t* level_start_index, const void* sampling_locations,
+                               const void* attention_weights, const void* grad_output,
+                               void* grad_value, void* grad_sampling_loc, void* grad_attn_weight,
+                               int B, int K, int H, int D, int L, int Q, int P, int dtype,
+                               void* stream);
+
 /* Algorithmic (compulsory) bytes one call moves: every operand read once and
  * every result written once. Used by benchmarks for the bandwidth roofline. */
 size_t msda_sm100_forward_bytes(int B, int K, int H, int D, int L, int Q, int P, int dtype);
