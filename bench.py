@@ -170,6 +170,14 @@ def cpu_baseline(workload, seconds):
                       f"({best})"}
 
 
+def workload_config(w, w_local, query_shard):
+    """The `config` object of the JSON line; identical for both arms."""
+    return {"workload": w.name, "B_per_rank": w_local.B, "Q_per_rank": w_local.Q,
+            "H": w.H, "D": w.D, "K": w.K, "L": w.L, "P": w.P,
+            "sharding": ("query+allreduce" if query_shard else "batch"),
+            "l2": "2 rotating input sets; one step moves more operand bytes than the 126 MB L2"}
+
+
 def run_reference_arm(args):
     """--impl reference: the reference's CPU implementation of the path on the host cores.
     Its device kernels need the vendor's NPU toolchain and cannot run here, and its CPU
@@ -187,8 +195,7 @@ def run_reference_arm(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * w.B / base["value"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w.name, "B": w.B, "Q": w.Q, "H": w.H, "D": w.D, "K": w.K,
-                   "L": w.L, "P": w.P},
+        "config": workload_config(w, w, args.shard == "query" and args.gpus > 1),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
@@ -344,11 +351,7 @@ def run_native(args):
         "scaling": "strong" if query_shard else "weak", "vs_baseline": None,
         "dtype": {"float32": "f32", "float16": "f16", "bfloat16": "bf16"}[args.dtype],
         "data": "synthetic",
-        "config": {"workload": w.name, "B_per_rank": w_local.B, "Q_per_rank": w_local.Q,
-                   "H": H, "D": D, "K": K, "L": L, "P": P,
-                   "sharding": ("query+allreduce" if query_shard else "batch"),
-                   "l2": f"{NSETS} rotating input sets; one step moves {(fb + bb) / 1e6:.0f} MB "
-                         "of operands (> 126 MB L2)"},
+        "config": workload_config(w, w_local, query_shard),
         "roofline": roofline, "clocks": clocks, "gpu_launches": int(launches) * world,
         "tuning": {"stage": lib.msda_sm100_tune(capi.TUNE_STAGE, -1),
                    "ctas_per_sm": lib.msda_sm100_tune(capi.TUNE_CTAS_PER_SM, -1),

@@ -261,7 +261,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
                  : "memory");
 }
 // global -> this CTA's shared memory; source, destination and size must all be
-// multiples of 16 bytes. No cluster multicast.
+// multiples of 16 bytes. Plain single-CTA form.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes,
                                          uint64_t* bar) {
     asm volatile(
