@@ -165,13 +165,14 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                     }
                 }
 
-                auto scatter_gather = [&](int base, auto guarded_tag) {
+                auto scatter_gather = [&](int base, auto unroll_tag, auto guarded_tag) {
+                    constexpr int U = decltype(unroll_tag)::value;   // rows in flight per lane
                     constexpr bool GUARDED = decltype(guarded_tag)::value;
                     const uint2* sp = s_slot + base + g;
-                    uint2 rec[UNROLL];
-                    float part[UNROLL];
+                    uint2 rec[U];
+                    float part[U];
 #pragma unroll
-                    for (int u = 0; u < UNROLL; ++u) {
+                    for (int u = 0; u < U; ++u) {
                         rec[u] = sp[u * RPI];
                         if (GUARDED && base + u * RPI + g >= slot_end) rec[u].x = kNoRow;
                         part[u] = 0.f;
@@ -179,9 +180,9 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                     if constexpr (!SCALAR) {
                         // A missing corner loads row 0 instead of branching around the load;
                         // it is skipped below, so it neither scatters nor contributes.
-                        uint4 raw[UNROLL][NV];
+                        uint4 raw[U][NV];
 #pragma unroll
-                        for (int u = 0; u < UNROLL; ++u) {
+                        for (int u = 0; u < U; ++u) {
                             const uint32_t off = (rec[u].x != kNoRow) ? rec[u].x : 0u;
 #pragma unroll
                             for (int k = 0; k < NV; ++k)
@@ -189,7 +190,7 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                                     ldg16(vlane + static_cast<size_t>(off) * 16 + k * (LPR * 16));
                         }
 #pragma unroll
-                        for (int u = 0; u < UNROLL; ++u) {
+                        for (int u = 0; u < U; ++u) {
                             if (rec[u].x != kNoRow) {
                                 const float w = __uint_as_float(rec[u].y);
                                 if constexpr (SPLIT_RED) {
@@ -224,7 +225,7 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                         }
                     } else {
 #pragma unroll
-                        for (int u = 0; u < UNROLL; ++u) {
+                        for (int u = 0; u < U; ++u) {
                             const float w = __uint_as_float(rec[u].y);
 #pragma unroll
                             for (int k = 0; k < NV; ++k) {
@@ -240,7 +241,7 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                     }
                     // fold to PART partials per slot, then park them in shared memory
 #pragma unroll
-                    for (int u = 0; u < UNROLL; ++u) {
+                    for (int u = 0; u < U; ++u) {
 #pragma unroll
                         for (int off = LPR / 2; off >= PART; off >>= 1)
                             part[u] += __shfl_xor_sync(0xffffffffu, part[u], off);
@@ -253,9 +254,11 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
 
                 int base = slot_begin;
 #pragma unroll 1
-                for (; base < unguarded_end; base += STEP) scatter_gather(base, std::false_type{});
+                for (; base < unguarded_end; base += STEP)
+                    scatter_gather(base, std::integral_constant<int, UNROLL>{}, std::false_type{});
 #pragma unroll 1
-                for (; base < slot_end; base += STEP) scatter_gather(base, std::true_type{});
+                for (; base < slot_end; base += STEP)
+                    scatter_gather(base, std::integral_constant<int, UNROLL>{}, std::true_type{});
             }
             __syncwarp();
 

@@ -125,21 +125,22 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
                         for (int e = 0; e < VEC; ++e) acc[k][e] = 0.f;
                 }
 
-                auto gather = [&](int base, auto guarded_tag) {
+                auto gather = [&](int base, auto unroll_tag, auto guarded_tag) {
+                    constexpr int U = decltype(unroll_tag)::value;   // rows in flight per lane
                     constexpr bool GUARDED = decltype(guarded_tag)::value;
                     const uint2* sp = s_slot + base + g;
-                    uint2 rec[UNROLL];
+                    uint2 rec[U];
 #pragma unroll
-                    for (int u = 0; u < UNROLL; ++u) {
+                    for (int u = 0; u < U; ++u) {
                         rec[u] = sp[u * RPI];
                         if (GUARDED && base + u * RPI + g >= slot_end) rec[u].x = kNoRow;
                     }
                     if constexpr (!SCALAR) {
                         // A missing corner loads nothing and reads as zeros (its weight is
                         // zero as well, so it adds nothing — and no 0 * NaN can arise).
-                        uint4 raw[UNROLL][NV];
+                        uint4 raw[U][NV];
 #pragma unroll
-                        for (int u = 0; u < UNROLL; ++u) {
+                        for (int u = 0; u < U; ++u) {
 #pragma unroll
                             for (int k = 0; k < NV; ++k) {
                                 raw[u][k] = make_uint4(0u, 0u, 0u, 0u);
@@ -149,7 +150,7 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
                             }
                         }
 #pragma unroll
-                        for (int u = 0; u < UNROLL; ++u) {
+                        for (int u = 0; u < U; ++u) {
                             const float w = __uint_as_float(rec[u].y);
 #pragma unroll
                             for (int k = 0; k < NV; ++k) {
@@ -160,9 +161,9 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
                             }
                         }
                     } else {
-                        float f[UNROLL][NV];
+                        float f[U][NV];
 #pragma unroll
-                        for (int u = 0; u < UNROLL; ++u) {
+                        for (int u = 0; u < U; ++u) {
 #pragma unroll
                             for (int k = 0; k < NV; ++k) {
                                 const int c = j + k * 32;
@@ -174,7 +175,7 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
                             }
                         }
 #pragma unroll
-                        for (int u = 0; u < UNROLL; ++u) {
+                        for (int u = 0; u < U; ++u) {
                             const float w = __uint_as_float(rec[u].y);
 #pragma unroll
                             for (int k = 0; k < NV; ++k) acc[k][0] = fmaf(w, f[u][k], acc[k][0]);
@@ -182,11 +183,20 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
                     }
                 };
 
+                // full trips, then shorter ones, then single guarded instructions: a task with
+                // few slots (small L*P) does not pay for instructions that carry no row
                 int base = slot_begin;
 #pragma unroll 1
-                for (; base < unguarded_end; base += STEP) gather(base, std::false_type{});
+                for (; base < unguarded_end; base += STEP)
+                    gather(base, std::integral_constant<int, UNROLL>{}, std::false_type{});
+                if constexpr (UNROLL > 2) {
 #pragma unroll 1
-                for (; base < slot_end; base += STEP) gather(base, std::true_type{});
+                    for (; base + 2 * RPI <= slot_end; base += 2 * RPI)
+                        gather(base, std::integral_constant<int, 2>{}, std::false_type{});
+                }
+#pragma unroll 1
+                for (; base < slot_end; base += RPI)
+                    gather(base, std::integral_constant<int, 1>{}, std::true_type{});
 
                 // ---- epilogue ---------------------------------------------------
                 if (chunk == nchunks - 1) {
