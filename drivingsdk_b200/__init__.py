@@ -8,6 +8,9 @@ Public surface, same names as the reference package exports for this path
     MultiScaleDeformableAttnFunction          torch.autograd.Function
     npu_multi_scale_deformable_attn_function  deprecated alias
     patcher                                   the mmcv hook (default_patcher, MSDA, ...)
+    geometric_kernel_attention(value, spatial_shapes, level_start_index, sampling_locations,
+                               attention_weights) -> Tensor   (nearest-pixel sibling operator,
+                               mx_driving/ops/geometric_kernel_attention.py:27-54)
 
 The operator names are resolved on first use, so that the patcher (pure Python)
 can be imported on a machine without the compiled extension. Using an operator
@@ -22,13 +25,17 @@ _OP_NAMES = (
     "MultiScaleDeformableAttnFunction",
     "npu_multi_scale_deformable_attn_function",
 )
+_GKA_NAMES = ("geometric_kernel_attention", "GeometricKernelAttentionFunc")
 
-__all__ = list(_OP_NAMES) + ["patcher", "default_patcher", "dist"]
+__all__ = list(_OP_NAMES) + list(_GKA_NAMES) + ["patcher", "default_patcher", "dist"]
 
 
 def __getattr__(name):
     if name in _OP_NAMES:
         mod = importlib.import_module(__name__ + ".ops.multi_scale_deformable_attn")
+        return getattr(mod, name)
+    if name in _GKA_NAMES:
+        mod = importlib.import_module(__name__ + ".ops.geometric_kernel_attention")
         return getattr(mod, name)
     if name == "_C":
         return importlib.import_module(__name__ + "._C")

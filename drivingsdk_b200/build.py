@@ -19,11 +19,13 @@ ROOT = os.path.dirname(PKG)
 LIB = os.path.join(PKG, "libmsda_sm100.so")
 EXT = os.path.join(PKG, "_C.so")
 
-CUDA_SOURCES = ["msda_capi.cu", "msda_fwd_sm100.cu", "msda_bwd_sm100.cu",
-                "msda_static_scratch.cu"]
-CUDA_HEADERS = ["msda_common.cuh", "msda_tile.cuh", "msda_launch.h"]
+CUDA_SOURCES = ["msda_capi.cu", "msda_fwd_sm100.cu", "msda_bwd_sm100.cu", "gka_fwd_sm100.cu",
+                "gka_bwd_sm100.cu", "msda_static_scratch.cu"]
+CUDA_HEADERS = ["msda_common.cuh", "msda_tile.cuh", "msda_launch.h", "msda_fwd_kernel.cuh",
+                "msda_bwd_kernel.cuh"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC", "-shared"]
+              "-Xcompiler", "-fPIC"]
+OBJ_DIR = os.path.join(PKG, "build")
 
 
 def _nvcc() -> str:
@@ -47,14 +49,28 @@ def _run(cmd, log_name):
 
 
 def build_library(force=False, verbose_ptxas=False) -> str:
+    """nvcc each .cu to an object (in parallel: the kernel files hold many template
+    instantiations), then link the shared library."""
+    from concurrent.futures import ThreadPoolExecutor
     srcs = [os.path.join(CSRC, s) for s in CUDA_SOURCES]
     deps = srcs + [os.path.join(CSRC, h) for h in CUDA_HEADERS] + [
         os.path.join(ROOT, "include", "msda_sm100.h")]
-    if force or _stale(LIB, deps):
-        flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if verbose_ptxas else [])
-        out = _run([_nvcc()] + flags + srcs + ["-o", LIB], "nvcc")
-        if verbose_ptxas:
-            sys.stdout.write(out)
+    if not (force or _stale(LIB, deps)):
+        return LIB
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if verbose_ptxas else [])
+    objs = [os.path.join(OBJ_DIR, os.path.basename(s)[:-3] + ".o") for s in srcs]
+
+    def compile_one(pair):
+        src, obj = pair
+        return _run([_nvcc()] + flags + ["-c", src, "-o", obj], "nvcc -c " + os.path.basename(src))
+
+    with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 1)) as pool:
+        logs = list(pool.map(compile_one, zip(srcs, objs)))
+    if verbose_ptxas:
+        sys.stdout.write("".join(logs))
+    _run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared"] + objs + ["-o", LIB],
+         "nvcc link")
     return LIB
 
 

@@ -1,5 +1,5 @@
-// Torch extension `_C`: the two entry points the reference's extension exposes
-// for this path (mx_driving/csrc/pybind.cpp:110-111, include/csrc/functions.h:58-64)
+// Torch extension `_C`: the entry points the reference's extension exposes for multi-scale
+// deformable attention (and, further down, geometric kernel attention) (mx_driving/csrc/pybind.cpp:110-111, include/csrc/functions.h:58-64)
 //     multi_scale_deformable_attn(value, shapes, level_start, loc, attn) -> Tensor
 //     multi_scale_deformable_attn_backward(value, shapes, level_start, loc, attn,
 //                                          grad_output) -> (Tensor, Tensor, Tensor)
@@ -177,6 +177,125 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> multi_scale_deformable_attn_backw
     return std::make_tuple(grad_value, grad_loc, grad_attn);
 }
 
+// ---------------------------------------------------------------------------
+// geometric kernel attention (mx_driving/csrc/GeometricKernelAttentionFunc.cpp:34-118,
+// pybind.cpp:131-132): nearest-pixel sampling at integer locations clamped into each level.
+// ---------------------------------------------------------------------------
+namespace {
+
+Dims check_gka_inputs(const at::Tensor& value, const at::Tensor& shapes, const at::Tensor& starts,
+                      const at::Tensor& loc, const at::Tensor& attn) {
+    TORCH_CHECK(is_float_kind(value.scalar_type()),
+                "value: float16, bfloat16 or float32 tensor expected but got a tensor with dtype: ",
+                value.scalar_type());
+    TORCH_CHECK(shapes.scalar_type() == at::kInt || shapes.scalar_type() == at::kLong,
+                "spatial_spatial_shapes: int32 or int64 tensor expected but got a tensor with "
+                "dtype: ", shapes.scalar_type());
+    TORCH_CHECK(starts.scalar_type() == at::kInt || starts.scalar_type() == at::kLong,
+                "level_start_index: int32 or int64 tensor expected but got a tensor with dtype: ",
+                starts.scalar_type());
+    TORCH_CHECK(is_float_kind(loc.scalar_type()) || loc.scalar_type() == at::kInt ||
+                    loc.scalar_type() == at::kLong,
+                "sampling_locations: float16, bfloat16, float32, int32 or int64 tensor expected "
+                "but got a tensor with dtype: ", loc.scalar_type());
+    TORCH_CHECK(is_float_kind(attn.scalar_type()),
+                "attention_weights: float16, bfloat16 or float32 tensor expected but got a tensor "
+                "with dtype: ", attn.scalar_type());
+    TORCH_CHECK(value.is_cuda() && loc.is_cuda() && attn.is_cuda(),
+                "geometric_kernel_attention: value, sampling_locations and attention_weights "
+                "must be CUDA tensors (this build has no CPU path)");
+    TORCH_CHECK(value.dim() == 4 && loc.dim() == 6 && loc.size(5) == 2 && attn.dim() == 5,
+                "geometric_kernel_attention: value [bs, keys, heads, dims], sampling_locations "
+                "[bs, queries, heads, levels, points, 2], attention_weights [bs, queries, heads, "
+                "levels, points] expected");
+    TORCH_CHECK(value.size(kEmbed) <= 256,
+                "The number of embedding dimensions should be less than or equal to 256");
+    TORCH_CHECK(loc.size(kLevel) * loc.size(kPoint) <= 64,
+                "The product of the number of levels and the number of points should be less than "
+                "or equal to 64");
+    Dims d;
+    d.B = static_cast<int>(value.size(0));
+    d.K = static_cast<int>(value.size(1));
+    d.H = static_cast<int>(value.size(2));
+    d.D = static_cast<int>(value.size(3));
+    d.Q = static_cast<int>(attn.size(1));
+    d.L = static_cast<int>(attn.size(3));
+    d.P = static_cast<int>(attn.size(4));
+    TORCH_CHECK(attn.size(0) == d.B && attn.size(2) == d.H && loc.size(0) == d.B &&
+                    loc.size(1) == d.Q && loc.size(2) == d.H && loc.size(3) == d.L &&
+                    loc.size(4) == d.P,
+                "sampling_locations / attention_weights shapes do not match value");
+    TORCH_CHECK(shapes.numel() == 2 * d.L && starts.numel() == d.L,
+                "spatial_shapes must have one (H, W) row and level_start_index one entry per level");
+    return d;
+}
+
+}  // namespace
+
+void geometric_kernel_attention_forward(const at::Tensor& value_in, const at::Tensor& shapes_in,
+                                        const at::Tensor& starts_in, const at::Tensor& loc_in,
+                                        const at::Tensor& attn_in, at::Tensor& output) {
+    const Dims d = check_gka_inputs(value_in, shapes_in, starts_in, loc_in, attn_in);
+    TORCH_CHECK(output.is_cuda() && output.is_contiguous() &&
+                    output.scalar_type() == value_in.scalar_type() &&
+                    output.numel() == static_cast<int64_t>(d.B) * d.Q * d.H * d.D,
+                "output must be a contiguous CUDA tensor [bs, num_queries, num_heads * dims] of "
+                "value's dtype");
+    const c10::cuda::CUDAGuard guard(value_in.device());
+    const at::Tensor value = value_in.contiguous();
+    // integer pixel coordinates travel in value's dtype (exact up to 2048 in float16)
+    const at::Tensor loc = loc_in.to(value.scalar_type()).contiguous();
+    const at::Tensor attn = attn_in.to(value.scalar_type()).contiguous();
+    const at::Tensor shapes = shapes_in.to(at::kInt).contiguous();
+    const at::Tensor starts = starts_in.to(at::kInt).contiguous();
+    if (output.numel() == 0) return;
+    const int rc = gka_sm100_forward(
+        value.data_ptr(), shapes.data_ptr<int32_t>(), starts.data_ptr<int32_t>(), loc.data_ptr(),
+        attn.data_ptr(), output.data_ptr(), d.B, d.K, d.H, d.D, d.L, d.Q, d.P,
+        dtype_code(value.scalar_type()), at::cuda::getCurrentCUDAStream().stream());
+    raise_on_error(rc, "geometric_kernel_attention_forward");
+}
+
+std::tuple<at::Tensor, at::Tensor> geometric_kernel_attention_backward(
+    const at::Tensor& value_in, const at::Tensor& shapes_in, const at::Tensor& starts_in,
+    const at::Tensor& loc_in, const at::Tensor& attn_in, const at::Tensor& grad_out_in) {
+    const Dims d = check_gka_inputs(value_in, shapes_in, starts_in, loc_in, attn_in);
+    TORCH_CHECK(is_float_kind(grad_out_in.scalar_type()) && grad_out_in.is_cuda(),
+                "grad_output: float16, bfloat16 or float32 CUDA tensor expected");
+    TORCH_CHECK(d.D % 8 == 0, "embed_dims must be a multiple of 8, but embed_dims is ", d.D, ".");
+    TORCH_CHECK(grad_out_in.numel() == static_cast<int64_t>(d.B) * d.Q * d.H * d.D,
+                "grad_output must be [bs, num_queries, num_heads * dims]");
+    const c10::cuda::CUDAGuard guard(value_in.device());
+    const at::Tensor value = value_in.contiguous();
+    const at::Tensor loc = loc_in.to(value.scalar_type()).contiguous();
+    const at::Tensor attn = attn_in.to(value.scalar_type()).contiguous();
+    const at::Tensor shapes = shapes_in.to(at::kInt).contiguous();
+    const at::Tensor starts = starts_in.to(at::kInt).contiguous();
+    const at::Tensor grad_out = grad_out_in.to(value.scalar_type()).contiguous();
+    at::Tensor grad_value = at::empty_like(value);
+    at::Tensor grad_attn = at::empty_like(attn);
+    if (value.numel() == 0 || attn.numel() == 0) {
+        grad_value.zero_();
+        return std::make_tuple(grad_value, grad_attn);
+    }
+    const int dt = dtype_code(value.scalar_type());
+    at::Tensor workspace;
+    void* ws_ptr = nullptr;
+    const size_t ws_bytes = msda_sm100_backward_workspace_bytes(d.B, d.K, d.H, d.D, dt);
+    if (ws_bytes > 0) {
+        workspace = at::empty({static_cast<int64_t>(ws_bytes / sizeof(float))},
+                              value.options().dtype(at::kFloat));
+        ws_ptr = workspace.data_ptr();
+    }
+    const int rc = gka_sm100_backward_ws(
+        value.data_ptr(), shapes.data_ptr<int32_t>(), starts.data_ptr<int32_t>(), loc.data_ptr(),
+        attn.data_ptr(), grad_out.data_ptr(), grad_value.data_ptr(), grad_attn.data_ptr(), ws_ptr,
+        ws_bytes, d.B, d.K, d.H, d.D, d.L, d.Q, d.P, dt,
+        at::cuda::getCurrentCUDAStream().stream());
+    raise_on_error(rc, "geometric_kernel_attention_backward");
+    return std::make_tuple(grad_value, grad_attn);
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "sm_100a multi-scale deformable attention (drop-in for mx_driving._C on this path)";
     m.def("multi_scale_deformable_attn", &multi_scale_deformable_attn,
@@ -186,4 +305,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           "MSDA backward: (value, value_spatial_shapes, value_level_start_index, "
           "sampling_locations, attention_weights, grad_output) -> "
           "(grad_value, grad_sampling_loc, grad_attn_weight)");
+    m.def("geometric_kernel_attention_forward", &geometric_kernel_attention_forward,
+          "GKA forward: (value, spatial_shapes, level_start_index, sampling_locations, "
+          "attention_weights, output) fills output");
+    m.def("geometric_kernel_attention_backward", &geometric_kernel_attention_backward,
+          "GKA backward: (value, spatial_shapes, level_start_index, sampling_locations, "
+          "attention_weights, grad_output) -> (grad_value, grad_attn_weights)");
 }

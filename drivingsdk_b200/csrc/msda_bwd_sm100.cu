@@ -18,276 +18,9 @@
 // over more than 8 lanes, xor shuffles first fold it to 8 partials. In phase 3
 // lane = sample again: it sums the partials of its four corners, forms the
 // three gradients and stores them next to its neighbours' (coalesced).
-#include <type_traits>
-
-#include "msda_launch.h"
-#include "msda_tile.cuh"
+#include "msda_bwd_kernel.cuh"
 
 namespace msda {
-
-constexpr int kPartMax = 8;  // partial dot products kept per (sample, corner)
-constexpr int kPartBytes = ((kChunk * (4 * kPartMax + 1) * 4 + 15) / 16) * 16;
-
-// Compile-time tuning, chosen by measurement on B200: three resident CTAs per SM (80
-// registers per thread) and four rows in flight per lane; the kernel is bound by the rate
-// at which L2 retires vector reductions, and more warps in flight made that worse.
-#ifndef MSDA_BWD_MIN_CTAS
-#define MSDA_BWD_MIN_CTAS 3
-#endif
-#ifndef MSDA_BWD_UNROLL
-#define MSDA_BWD_UNROLL 4
-#endif
-
-template <typename T, typename TG, int LPR, int NV, bool SCALAR>
-__global__ void __launch_bounds__(kThreadsPerCta, (SCALAR || NV > 1) ? 2 : MSDA_BWD_MIN_CTAS)
-msda_bwd_kernel(const __grid_constant__ Params p) {
-    constexpr int VEC = SCALAR ? 1 : Elem<T>::kVec;
-    constexpr int RPI = 32 / LPR;
-    constexpr int PART = (LPR < kPartMax) ? LPR : kPartMax;  // partials per slot
-    constexpr int SSTRIDE = 4 * PART + 1;                    // per-sample stride (bank spread)
-    constexpr int UNROLL = (RPI >= 16) ? 2 : MSDA_BWD_UNROLL;
-    constexpr int STEP = RPI * UNROLL;
-    static_assert(kSlots % STEP == 0 && STEP <= kSlotPad, "slot loop must tile the slots");
-    // 16-bit operands accumulated in fp32: a lane's 16-byte piece of the value row is 8
-    // channels, i.e. 32 bytes of the fp32 accumulation row. Two reductions at +0 and +16
-    // bytes of that span would touch every 32-byte sector of the row with half a sector each
-    // time; instead lane j adds the float4 pieces j and LPR + j, so each instruction covers
-    // whole sectors. The scatter does not depend on the value data, so any lane may add any
-    // channels — it only needs grad_out for those channels (gred below).
-    constexpr bool SPLIT_RED = !SCALAR && sizeof(T) == 2 && sizeof(TG) == 4;
-
-    extern __shared__ __align__(128) unsigned char smem[];
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-    const int g = lane / LPR;
-    const int j = lane % LPR;
-
-    unsigned char* wb = smem + static_cast<size_t>(warp) * p.warp_smem;
-    uint2* s_slot = reinterpret_cast<uint2*>(wb);
-    float* s_part = reinterpret_cast<float*>(wb + kSlotBytes);
-    WarpStage<T> st = warp_stage_init<T>(p, wb + kSlotBytes + kPartBytes, lane);
-
-    const LaneLevels lv = load_lane_levels(p, lane);
-    const T* __restrict__ value = static_cast<const T*>(p.value);
-    const unsigned char* vlane = static_cast<const unsigned char*>(p.value) + j * 16;
-    const T* __restrict__ gout = static_cast<const T*>(p.grad_out);
-    TG* __restrict__ gval = static_cast<TG*>(p.grad_value);
-    unsigned char* glane = static_cast<unsigned char*>(p.grad_value) + j * 16;
-    T* __restrict__ gl = static_cast<T*>(p.grad_loc);
-    T* __restrict__ ga = static_cast<T*>(p.grad_attn);
-
-    const int TPC = p.tasks_per_item;
-    const int LP = p.LP;
-    const int D = p.D;
-    const int nchunks = (TPC == 1) ? (LP + kChunk - 1) / kChunk : 1;
-    ItemWalk walk = make_walk(p, warp);
-    auto full = [&](long long it) { return (it + 1) * TPC <= p.ntasks; };
-
-    if (st.ok && lane == 0 && walk.idx < walk.end && full(walk.item())) {
-        st.issue(p, walk.item(), 0);
-    }
-
-    for (int n = 0; walk.idx < walk.end; walk.idx += walk.stride, ++n) {
-        const int buf = n & 1;
-        const long long item = walk.item();
-        const T* sloc = nullptr;
-        const T* sattn = nullptr;
-        if (st.ok) {
-            const long long next = walk.item_at(walk.idx + walk.stride);
-            if (lane == 0 && walk.idx + walk.stride < walk.end && full(next)) {
-                st.issue(p, next, buf ^ 1);
-            }
-            if (full(item)) {
-                const bool arrived =
-                    __all_sync(0xffffffffu, mbar_wait(st.bar + buf, (n >> 1) & 1) ? 1 : 0) != 0;
-                if (arrived) {
-                    sloc = st.loc(p, buf);
-                    sattn = st.attn(p, buf);
-                } else {
-                    st.ok = false;
-                    if (lane == 0) atomicOr(p.status, kStatusStageTimeout);
-                }
-            }
-        }
-
-        const int t0 = static_cast<int>(item) * TPC;
-        const int ntask_here = min(TPC, static_cast<int>(p.ntasks - t0));
-
-        for (int chunk = 0; chunk < nchunks; ++chunk) {
-            // ---- phase 1: lane = sample -----------------------------------------
-            SampleGeom geom;
-            long long gi;
-            const bool active =
-                phase1<T>(p, lv, chunk, lane, item, ntask_here, sloc, sattn, s_slot, geom, gi);
-            __syncwarp();
-
-            // ---- phase 2: lane = (row slot, piece of row) -----------------------
-            for (int tl2 = 0; tl2 < ntask_here; ++tl2) {
-                int slot_begin, slot_end, unguarded_end;
-                if (TPC == 1) {
-                    slot_begin = 0;
-                    slot_end = 4 * min(kChunk, LP - chunk * kChunk);
-                    unguarded_end = slot_end;
-                } else {
-                    slot_begin = tl2 * 4 * LP;
-                    slot_end = slot_begin + 4 * LP;
-                    unguarded_end = slot_end - STEP + 1;
-                }
-                // this lane's piece of grad_out[b, q, h, :]
-                float go[NV][VEC];
-                const size_t obase = static_cast<size_t>(t0 + tl2) * D;
-#pragma unroll
-                for (int k = 0; k < NV; ++k) {
-                    if constexpr (!SCALAR) {
-                        const uint4 raw =
-                            *reinterpret_cast<const uint4*>(gout + obase + (j + k * LPR) * VEC);
-                        unpack16<T>(raw, go[k]);
-                    } else {
-                        const int c = j + k * 32;
-                        go[k][0] = (c < D) ? Elem<T>::to_f(gout[obase + c]) : 0.f;
-                    }
-                }
-                float gred[2][4];
-                if constexpr (SPLIT_RED) {
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        const T* src = gout + obase + (half * LPR + j) * 4;
-                        const uint2 raw = *reinterpret_cast<const uint2*>(src);
-                        const uint32_t wds[2] = {raw.x, raw.y};
-#pragma unroll
-                        for (int i = 0; i < 2; ++i) {
-                            const uint16_t l16 = static_cast<uint16_t>(wds[i] & 0xffffu);
-                            const uint16_t h16 = static_cast<uint16_t>(wds[i] >> 16);
-                            gred[half][2 * i] = Elem<T>::to_f(*reinterpret_cast<const T*>(&l16));
-                            gred[half][2 * i + 1] =
-                                Elem<T>::to_f(*reinterpret_cast<const T*>(&h16));
-                        }
-                    }
-                }
-
-                auto scatter_gather = [&](int base, auto unroll_tag, auto guarded_tag) {
-                    constexpr int U = decltype(unroll_tag)::value;   // rows in flight per lane
-                    constexpr bool GUARDED = decltype(guarded_tag)::value;
-                    const uint2* sp = s_slot + base + g;
-                    uint2 rec[U];
-                    float part[U];
-#pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        rec[u] = sp[u * RPI];
-                        if (GUARDED && base + u * RPI + g >= slot_end) rec[u].x = kNoRow;
-                        part[u] = 0.f;
-                    }
-                    if constexpr (!SCALAR) {
-                        // A missing corner loads row 0 instead of branching around the load;
-                        // it is skipped below, so it neither scatters nor contributes.
-                        uint4 raw[U][NV];
-#pragma unroll
-                        for (int u = 0; u < U; ++u) {
-                            const uint32_t off = (rec[u].x != kNoRow) ? rec[u].x : 0u;
-#pragma unroll
-                            for (int k = 0; k < NV; ++k)
-                                raw[u][k] =
-                                    ldg16(vlane + static_cast<size_t>(off) * 16 + k * (LPR * 16));
-                        }
-#pragma unroll
-                        for (int u = 0; u < U; ++u) {
-                            if (rec[u].x != kNoRow) {
-                                const float w = __uint_as_float(rec[u].y);
-                                if constexpr (SPLIT_RED) {
-                                    float* row = reinterpret_cast<float*>(
-                                        glane + static_cast<size_t>(rec[u].x) * 32);
-                                    red_add_f32x4(row, w * gred[0][0], w * gred[0][1],
-                                                  w * gred[0][2], w * gred[0][3]);
-                                    red_add_f32x4(row + LPR * 4, w * gred[1][0], w * gred[1][1],
-                                                  w * gred[1][2], w * gred[1][3]);
-                                } else {
-#pragma unroll
-                                    for (int k = 0; k < NV; ++k) {
-                                        float contrib[VEC];
-#pragma unroll
-                                        for (int e = 0; e < VEC; ++e) contrib[e] = w * go[k][e];
-                                        red_add_vec<TG, VEC>(
-                                            reinterpret_cast<TG*>(
-                                                glane + static_cast<size_t>(rec[u].x) * 16 +
-                                                k * (LPR * 16)),
-                                            contrib);
-                                    }
-                                }
-#pragma unroll
-                                for (int k = 0; k < NV; ++k) {
-                                    float f[VEC];
-                                    unpack16<T>(raw[u][k], f);
-#pragma unroll
-                                    for (int e = 0; e < VEC; ++e)
-                                        part[u] = fmaf(f[e], go[k][e], part[u]);
-                                }
-                            }
-                        }
-                    } else {
-#pragma unroll
-                        for (int u = 0; u < U; ++u) {
-                            const float w = __uint_as_float(rec[u].y);
-#pragma unroll
-                            for (int k = 0; k < NV; ++k) {
-                                const int c = j + k * 32;
-                                if (rec[u].x != kNoRow && c < D) {
-                                    const size_t idx = static_cast<size_t>(rec[u].x) + c;
-                                    const float v = Elem<T>::to_f(__ldg(value + idx));
-                                    red_add_scalar(gval + idx, w * go[k][0]);
-                                    part[u] = fmaf(v, go[k][0], part[u]);
-                                }
-                            }
-                        }
-                    }
-                    // fold to PART partials per slot, then park them in shared memory
-#pragma unroll
-                    for (int u = 0; u < U; ++u) {
-#pragma unroll
-                        for (int off = LPR / 2; off >= PART; off >>= 1)
-                            part[u] += __shfl_xor_sync(0xffffffffu, part[u], off);
-                        const int slot = base + u * RPI + g;
-                        if ((!GUARDED || slot < slot_end) && j < PART) {
-                            s_part[(slot >> 2) * SSTRIDE + (slot & 3) * PART + j] = part[u];
-                        }
-                    }
-                };
-
-                int base = slot_begin;
-#pragma unroll 1
-                for (; base < unguarded_end; base += STEP)
-                    scatter_gather(base, std::integral_constant<int, UNROLL>{}, std::false_type{});
-#pragma unroll 1
-                for (; base < slot_end; base += STEP)
-                    scatter_gather(base, std::integral_constant<int, UNROLL>{}, std::true_type{});
-            }
-            __syncwarp();
-
-            // ---- phase 3: lane = sample -----------------------------------------
-            if (active) {
-                float S[4];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    float acc = 0.f;
-#pragma unroll
-                    for (int q = 0; q < PART; ++q) acc += s_part[lane * SSTRIDE + c * PART + q];
-                    S[c] = acc;
-                }
-                float g_attn = 0.f, g_x = 0.f, g_y = 0.f;
-                if (geom.valid) {
-                    // a corner that does not exist left a zero partial sum behind
-                    const float lw = geom.lw, lh = geom.lh;
-                    const float hw = 1.f - lw, hh = 1.f - lh;
-                    g_attn = hh * hw * S[0] + hh * lw * S[1] + lh * hw * S[2] + lh * lw * S[3];
-                    g_x = geom.wf * geom.a * (hh * (S[1] - S[0]) + lh * (S[3] - S[2]));
-                    g_y = geom.hf * geom.a * (hw * (S[2] - S[0]) + lw * (S[3] - S[1]));
-                }
-                store_pair(gl + 2 * gi, g_x, g_y);
-                ga[gi] = Elem<T>::from_f(g_attn);
-            }
-            __syncwarp();
-        }
-    }
-}
 
 // fp32 accumulation buffer -> 16-bit grad_value
 template <typename T>
@@ -308,63 +41,13 @@ __global__ void __launch_bounds__(256) msda_downcast_kernel(const float* __restr
     }
 }
 
-// ---------------------------------------------------------------------------
-// host side
-// ---------------------------------------------------------------------------
-template <typename T, typename TG, int LPR, int NV, bool SCALAR>
-static cudaError_t launch_bwd_inst(const Params& p, const LaunchShape& ls, size_t smem,
-                                   cudaStream_t stream) {
-    auto kern = msda_bwd_kernel<T, TG, LPR, NV, SCALAR>;
-    if (smem > 48 * 1024) {
-        cudaError_t e =
-            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-    }
-    int grid = 0;
-    cudaError_t e = persistent_grid(reinterpret_cast<const void*>(kern), smem, ls, p, &grid);
-    if (e != cudaSuccess) return e;
-    kern<<<grid, kThreadsPerCta, smem, stream>>>(p);
-    return cudaGetLastError();
-}
-
-template <typename T, typename TG>
-static cudaError_t launch_bwd_typed(const Params& p, const RowPlan& rp, const LaunchShape& ls, size_t smem,
-                                    cudaStream_t stream) {
-    if (rp.scalar) return launch_bwd_inst<T, TG, 32, 8, true>(p, ls, smem, stream);
-    switch (rp.lpr * 100 + rp.nv) {
-        case 101: return launch_bwd_inst<T, TG, 1, 1, false>(p, ls, smem, stream);
-        case 201: return launch_bwd_inst<T, TG, 2, 1, false>(p, ls, smem, stream);
-        case 401: return launch_bwd_inst<T, TG, 4, 1, false>(p, ls, smem, stream);
-        case 801: return launch_bwd_inst<T, TG, 8, 1, false>(p, ls, smem, stream);
-        case 1601: return launch_bwd_inst<T, TG, 16, 1, false>(p, ls, smem, stream);
-        case 3201: return launch_bwd_inst<T, TG, 32, 1, false>(p, ls, smem, stream);
-        case 3202:
-            if constexpr (sizeof(T) == 4) {
-                return launch_bwd_inst<T, TG, 32, 2, false>(p, ls, smem, stream);
-            }
-            return cudaErrorInvalidValue;
-        default: return cudaErrorInvalidValue;
-    }
-}
-
 uint32_t bwd_warp_smem(int samples_per_item, size_t elem) {
     return warp_smem_bytes(samples_per_item, elem, kPartBytes);
 }
 
 cudaError_t launch_backward(const Params& p, int dtype, int acc_f32, const RowPlan& rp,
                             const LaunchShape& ls, cudaStream_t stream) {
-    const size_t smem = static_cast<size_t>(p.warp_smem) * kWarpsPerCta;
-    switch (dtype) {
-        case 0: return launch_bwd_typed<float, float>(p, rp, ls, smem, stream);
-        case 1:
-            return acc_f32 ? launch_bwd_typed<__half, float>(p, rp, ls, smem, stream)
-                           : launch_bwd_typed<__half, __half>(p, rp, ls, smem, stream);
-        case 2:
-            return acc_f32
-                       ? launch_bwd_typed<__nv_bfloat16, float>(p, rp, ls, smem, stream)
-                       : launch_bwd_typed<__nv_bfloat16, __nv_bfloat16>(p, rp, ls, smem, stream);
-        default: return cudaErrorInvalidValue;
-    }
+    return launch_backward_cps<4>(p, dtype, acc_f32, rp, ls, stream);
 }
 
 cudaError_t launch_downcast(const float* acc, void* out, long long n, int dtype,

@@ -168,10 +168,13 @@ int fill_common(Params& p, const DeviceInfo* dev, const void* value, const int32
 
 int backward_impl(const void* value, const int32_t* shapes, const int32_t* starts, const void* loc,
                   const void* attn, const void* grad_out, void* grad_value, void* grad_loc,
-                  void* grad_attn, void* workspace, size_t workspace_bytes, bool use_ws, int B,
-                  int K, int H, int D, int L, int Q, int P, int dtype, void* stream_v) {
-    if (!value || !shapes || !starts || !loc || !attn || !grad_out || !grad_value || !grad_loc ||
-        !grad_attn)
+                  void* grad_attn, void* workspace, size_t workspace_bytes, bool use_ws,
+                  bool nearest, int B, int K, int H, int D, int L, int Q, int P, int dtype,
+                  void* stream_v) {
+    // nearest == true: geometric kernel attention (one clamped integer pixel per sample, no
+    // location gradient); false: bilinear MSDA
+    if (!value || !shapes || !starts || !loc || !attn || !grad_out || !grad_value || !grad_attn ||
+        (!nearest && !grad_loc))
         return MSDA_ERR_NULL;
     int rc = check_dims(B, K, H, D, L, Q, P, dtype);
     if (rc != MSDA_OK) return rc;
@@ -185,7 +188,7 @@ int backward_impl(const void* value, const int32_t* shapes, const int32_t* start
     if (rc != MSDA_OK) return rc;
     const size_t e = elem_size(dtype);
     if (!aligned_to(grad_out, e) || !aligned_to(grad_value, e) || !aligned_to(grad_attn, e) ||
-        !aligned_to(grad_loc, 2 * e))
+        (!nearest && !aligned_to(grad_loc, 2 * e)))
         return MSDA_ERR_ALIGN;
 
     const long long nval = static_cast<long long>(B) * K * H * D;
@@ -213,8 +216,9 @@ int backward_impl(const void* value, const int32_t* shapes, const int32_t* start
     cudaError_t ce = cudaMemsetAsync(acc, 0, acc_bytes, stream);
     if (ce != cudaSuccess) return fail_cuda(ce);
     prof_record(2, stream);
-    ce = msda::launch_backward(p, dtype, acc_f32 ? 1 : 0, rp, msda::LaunchShape{dev->sm_count, g_tune_cps_bwd.load()},
-                               stream);
+    const msda::LaunchShape shape{dev->sm_count, g_tune_cps_bwd.load()};
+    ce = nearest ? msda::launch_gka_backward(p, dtype, acc_f32 ? 1 : 0, rp, shape, stream)
+                 : msda::launch_backward(p, dtype, acc_f32 ? 1 : 0, rp, shape, stream);
     prof_record(3, stream);
     if (ce != cudaSuccess) return fail_cuda(ce);
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -226,14 +230,10 @@ int backward_impl(const void* value, const int32_t* shapes, const int32_t* start
     return MSDA_OK;
 }
 
-}  // namespace
-
-extern "C" {
-
-int msda_sm100_forward(const void* value, const int32_t* spatial_shapes,
-                       const int32_t* level_start_index, const void* sampling_locations,
-                       const void* attention_weights, void* output, int B, int K, int H, int D,
-                       int L, int Q, int P, int dtype, void* stream_v) {
+int forward_impl(const void* value, const int32_t* spatial_shapes,
+                 const int32_t* level_start_index, const void* sampling_locations,
+                 const void* attention_weights, void* output, bool nearest, int B, int K, int H,
+                 int D, int L, int Q, int P, int dtype, void* stream_v) {
     if (!value || !spatial_shapes || !level_start_index || !sampling_locations ||
         !attention_weights || !output)
         return MSDA_ERR_NULL;
@@ -255,12 +255,45 @@ int msda_sm100_forward(const void* value, const int32_t* spatial_shapes,
     p.warp_smem = msda::fwd_warp_smem(p.tasks_per_item * p.LP, elem_size(dtype));
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     prof_record(0, stream);
-    cudaError_t ce =
-        msda::launch_forward(p, dtype, rp, msda::LaunchShape{dev->sm_count, g_tune_cps_fwd.load()}, stream);
+    const msda::LaunchShape shape{dev->sm_count, g_tune_cps_fwd.load()};
+    cudaError_t ce = nearest ? msda::launch_gka_forward(p, dtype, rp, shape, stream)
+                             : msda::launch_forward(p, dtype, rp, shape, stream);
     prof_record(1, stream);
     if (ce != cudaSuccess) return fail_cuda(ce);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return MSDA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int msda_sm100_forward(const void* value, const int32_t* spatial_shapes,
+                       const int32_t* level_start_index, const void* sampling_locations,
+                       const void* attention_weights, void* output, int B, int K, int H, int D,
+                       int L, int Q, int P, int dtype, void* stream) {
+    return forward_impl(value, spatial_shapes, level_start_index, sampling_locations,
+                        attention_weights, output, false, B, K, H, D, L, Q, P, dtype, stream);
+}
+
+int gka_sm100_forward(const void* value, const int32_t* spatial_shapes,
+                      const int32_t* level_start_index, const void* sampling_locations,
+                      const void* attention_weights, void* output, int B, int K, int H, int D,
+                      int L, int Q, int P, int dtype, void* stream) {
+    return forward_impl(value, spatial_shapes, level_start_index, sampling_locations,
+                        attention_weights, output, true, B, K, H, D, L, Q, P, dtype, stream);
+}
+
+int gka_sm100_backward_ws(const void* value, const int32_t* spatial_shapes,
+                          const int32_t* level_start_index, const void* sampling_locations,
+                          const void* attention_weights, const void* grad_output,
+                          void* grad_value, void* grad_attn_weight, void* workspace,
+                          size_t workspace_bytes, int B, int K, int H, int D, int L, int Q, int P,
+                          int dtype, void* stream) {
+    return backward_impl(value, spatial_shapes, level_start_index, sampling_locations,
+                         attention_weights, grad_output, grad_value, nullptr, grad_attn_weight,
+                         workspace, workspace_bytes, true, true, B, K, H, D, L, Q, P, dtype,
+                         stream);
 }
 
 int msda_sm100_backward(const void* value, const int32_t* spatial_shapes,
@@ -270,7 +303,7 @@ int msda_sm100_backward(const void* value, const int32_t* spatial_shapes,
                         int D, int L, int Q, int P, int dtype, void* stream) {
     return backward_impl(value, spatial_shapes, level_start_index, sampling_locations,
                          attention_weights, grad_output, grad_value, grad_sampling_loc,
-                         grad_attn_weight, nullptr, 0, false, B, K, H, D, L, Q, P, dtype, stream);
+                         grad_attn_weight, nullptr, 0, false, false, B, K, H, D, L, Q, P, dtype, stream);
 }
 
 size_t msda_sm100_backward_workspace_bytes(int B, int K, int H, int D, int dtype) {
@@ -286,8 +319,8 @@ int msda_sm100_backward_ws(const void* value, const int32_t* spatial_shapes,
                            int L, int Q, int P, int dtype, void* stream) {
     return backward_impl(value, spatial_shapes, level_start_index, sampling_locations,
                          attention_weights, grad_output, grad_value, grad_sampling_loc,
-                         grad_attn_weight, workspace, workspace_bytes, true, B, K, H, D, L, Q, P,
-                         dtype, stream);
+                         grad_attn_weight, workspace, workspace_bytes, true, false, B, K, H, D, L, Q,
+                         P, dtype, stream);
 }
 
 size_t msda_sm100_forward_bytes(int B, int K, int H, int D, int L, int Q, int P, int dtype) {

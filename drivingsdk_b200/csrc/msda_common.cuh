@@ -352,4 +352,26 @@ __device__ __forceinline__ void sample_setup(float lx, float ly, float a, int Wl
     g.valid = valid;
 }
 
+// Nearest-pixel variant (geometric kernel attention): the location holds pixel coordinates;
+// they are truncated to integers and clamped into the level
+// (kernels/geometric_kernel_attention/op_kernel/geometric_kernel_attention.cpp:123-159), so
+// every sample has exactly one row. rec.x/.y = {row offset, attention weight bits}.
+__device__ __forceinline__ void sample_setup_nearest(float lx, float ly, float a, int Wl, int Hl,
+                                                     uint32_t row_base, uint32_t H,
+                                                     uint32_t row_units, uint4& rec,
+                                                     SampleGeom& g) {
+    // __float2int_rz saturates and maps NaN to 0, so any input lands inside the level
+    int x = __float2int_rz(lx);
+    int y = __float2int_rz(ly);
+    x = min(max(x, 0), Wl - 1);
+    y = min(max(y, 0), Hl - 1);
+    rec.x = (row_base + static_cast<uint32_t>(y * Wl + x) * H) * row_units;
+    rec.y = __float_as_uint(a);
+    g.lw = g.lh = 0.f;
+    g.a = a;
+    g.wf = static_cast<float>(Wl);
+    g.hf = static_cast<float>(Hl);
+    g.valid = true;
+}
+
 }  // namespace msda

@@ -17,256 +17,9 @@
 //            writes the D outputs as 16-byte stores.
 // Rows whose byte length is not 16 * 2^k take the SCALAR instantiation: lane =
 // channel (mod 32), one row per instruction.
-#include <type_traits>
-
-#include "msda_launch.h"
-#include "msda_tile.cuh"
-
-// Compile-time tuning, chosen by measurement on B200 (BEVFormer / Deformable-DETR shapes):
-// four resident CTAs per SM (64 registers per thread, no spills) with four row loads in
-// flight per lane beat both deeper unrolling (spills) and more CTAs (fewer registers).
-#ifndef MSDA_FWD_MIN_CTAS
-#define MSDA_FWD_MIN_CTAS 4
-#endif
-#ifndef MSDA_FWD_UNROLL
-#define MSDA_FWD_UNROLL 4
-#endif
+#include "msda_fwd_kernel.cuh"
 
 namespace msda {
-
-template <typename T, int LPR, int NV, bool SCALAR>
-__global__ void __launch_bounds__(kThreadsPerCta, (SCALAR || NV > 1) ? 2 : MSDA_FWD_MIN_CTAS)
-msda_fwd_kernel(const __grid_constant__ Params p) {
-    constexpr int VEC = SCALAR ? 1 : Elem<T>::kVec;
-    constexpr int RPI = 32 / LPR;                  // rows per warp instruction
-    constexpr int UNROLL =
-        (RPI >= 16) ? 2 : ((NV > 2) ? 4 : MSDA_FWD_UNROLL);
-    constexpr int STEP = RPI * UNROLL;             // slots per trip of the gather loop
-    static_assert(kSlots % STEP == 0 && STEP <= kSlotPad, "slot loop must tile the slots");
-
-    extern __shared__ __align__(128) unsigned char smem[];
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-    const int g = lane / LPR;   // row slot within one instruction
-    const int j = lane % LPR;   // 16-byte piece (or channel mod 32) within the row
-
-    unsigned char* wb = smem + static_cast<size_t>(warp) * p.warp_smem;
-    uint2* s_slot = reinterpret_cast<uint2*>(wb);
-    WarpStage<T> st = warp_stage_init<T>(p, wb + kSlotBytes, lane);
-
-    const LaneLevels lv = load_lane_levels(p, lane);
-    const T* __restrict__ value = static_cast<const T*>(p.value);
-    const unsigned char* vlane = static_cast<const unsigned char*>(p.value) + j * 16;
-    T* __restrict__ out = static_cast<T*>(p.out);
-
-    const int TPC = p.tasks_per_item;
-    const int LP = p.LP;
-    const int D = p.D;
-    const int nchunks = (TPC == 1) ? (LP + kChunk - 1) / kChunk : 1;
-    ItemWalk walk = make_walk(p, warp);
-    auto full = [&](long long it) { return (it + 1) * TPC <= p.ntasks; };
-
-    if (st.ok && lane == 0 && walk.idx < walk.end && full(walk.item())) {
-        st.issue(p, walk.item(), 0);
-    }
-
-    for (int n = 0; walk.idx < walk.end; walk.idx += walk.stride, ++n) {
-        const int buf = n & 1;
-        const long long item = walk.item();
-        const T* sloc = nullptr;
-        const T* sattn = nullptr;
-        if (st.ok) {
-            const long long next = walk.item_at(walk.idx + walk.stride);
-            if (lane == 0 && walk.idx + walk.stride < walk.end && full(next)) {
-                st.issue(p, next, buf ^ 1);
-            }
-            if (full(item)) {
-                const bool arrived =
-                    __all_sync(0xffffffffu, mbar_wait(st.bar + buf, (n >> 1) & 1) ? 1 : 0) != 0;
-                if (arrived) {
-                    sloc = st.loc(p, buf);
-                    sattn = st.attn(p, buf);
-                } else {
-                    st.ok = false;
-                    if (lane == 0) atomicOr(p.status, kStatusStageTimeout);
-                }
-            }
-        }
-
-        const int t0 = static_cast<int>(item) * TPC;
-        const int ntask_here = min(TPC, static_cast<int>(p.ntasks - t0));
-        float acc[NV][VEC];
-
-        for (int chunk = 0; chunk < nchunks; ++chunk) {
-            // ---- phase 1: lane = sample -----------------------------------------
-            SampleGeom geom;
-            long long gi;
-            phase1<T>(p, lv, chunk, lane, item, ntask_here, sloc, sattn, s_slot, geom, gi);
-            __syncwarp();
-
-            // ---- phase 2: lane = (row slot, piece of row) -----------------------
-            for (int tl2 = 0; tl2 < ntask_here; ++tl2) {
-                int slot_begin, slot_end, unguarded_end;
-                if (TPC == 1) {
-                    // slots past the last sample hold "no row" records: no guard needed
-                    slot_begin = 0;
-                    slot_end = 4 * min(kChunk, LP - chunk * kChunk);
-                    unguarded_end = slot_end;
-                } else {
-                    // slots past slot_end belong to the next task: the last trip is guarded
-                    slot_begin = tl2 * 4 * LP;
-                    slot_end = slot_begin + 4 * LP;
-                    unguarded_end = slot_end - STEP + 1;
-                }
-                if (chunk == 0) {
-#pragma unroll
-                    for (int k = 0; k < NV; ++k)
-#pragma unroll
-                        for (int e = 0; e < VEC; ++e) acc[k][e] = 0.f;
-                }
-
-                auto gather = [&](int base, auto unroll_tag, auto guarded_tag) {
-                    constexpr int U = decltype(unroll_tag)::value;   // rows in flight per lane
-                    constexpr bool GUARDED = decltype(guarded_tag)::value;
-                    const uint2* sp = s_slot + base + g;
-                    uint2 rec[U];
-#pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        rec[u] = sp[u * RPI];
-                        if (GUARDED && base + u * RPI + g >= slot_end) rec[u].x = kNoRow;
-                    }
-                    if constexpr (!SCALAR) {
-                        // A missing corner loads nothing and reads as zeros (its weight is
-                        // zero as well, so it adds nothing — and no 0 * NaN can arise).
-                        uint4 raw[U][NV];
-#pragma unroll
-                        for (int u = 0; u < U; ++u) {
-#pragma unroll
-                            for (int k = 0; k < NV; ++k) {
-                                raw[u][k] = make_uint4(0u, 0u, 0u, 0u);
-                                if (rec[u].x != kNoRow)
-                                    raw[u][k] = ldg16(vlane + static_cast<size_t>(rec[u].x) * 16 +
-                                                      k * (LPR * 16));
-                            }
-                        }
-#pragma unroll
-                        for (int u = 0; u < U; ++u) {
-                            const float w = __uint_as_float(rec[u].y);
-#pragma unroll
-                            for (int k = 0; k < NV; ++k) {
-                                float f[VEC];
-                                unpack16<T>(raw[u][k], f);
-#pragma unroll
-                                for (int e = 0; e < VEC; ++e) acc[k][e] = fmaf(w, f[e], acc[k][e]);
-                            }
-                        }
-                    } else {
-                        float f[U][NV];
-#pragma unroll
-                        for (int u = 0; u < U; ++u) {
-#pragma unroll
-                            for (int k = 0; k < NV; ++k) {
-                                const int c = j + k * 32;
-                                f[u][k] = 0.f;
-                                if (rec[u].x != kNoRow && c < D) {
-                                    f[u][k] = Elem<T>::to_f(
-                                        __ldg(value + static_cast<size_t>(rec[u].x) + c));
-                                }
-                            }
-                        }
-#pragma unroll
-                        for (int u = 0; u < U; ++u) {
-                            const float w = __uint_as_float(rec[u].y);
-#pragma unroll
-                            for (int k = 0; k < NV; ++k) acc[k][0] = fmaf(w, f[u][k], acc[k][0]);
-                        }
-                    }
-                };
-
-                // full trips, then shorter ones, then single guarded instructions: a task with
-                // few slots (small L*P) does not pay for instructions that carry no row
-                int base = slot_begin;
-#pragma unroll 1
-                for (; base < unguarded_end; base += STEP)
-                    gather(base, std::integral_constant<int, UNROLL>{}, std::false_type{});
-                if constexpr (UNROLL > 2) {
-#pragma unroll 1
-                    for (; base + 2 * RPI <= slot_end; base += 2 * RPI)
-                        gather(base, std::integral_constant<int, 2>{}, std::false_type{});
-                }
-#pragma unroll 1
-                for (; base < slot_end; base += RPI)
-                    gather(base, std::integral_constant<int, 1>{}, std::true_type{});
-
-                // ---- epilogue ---------------------------------------------------
-                if (chunk == nchunks - 1) {
-                    const size_t obase = static_cast<size_t>(t0 + tl2) * D;
-#pragma unroll
-                    for (int k = 0; k < NV; ++k) {
-#pragma unroll
-                        for (int off = LPR; off < 32; off <<= 1) {
-#pragma unroll
-                            for (int e = 0; e < VEC; ++e)
-                                acc[k][e] += __shfl_xor_sync(0xffffffffu, acc[k][e], off);
-                        }
-                        if (g == 0) {
-                            if constexpr (!SCALAR) {
-                                float f[VEC];
-#pragma unroll
-                                for (int e = 0; e < VEC; ++e) f[e] = acc[k][e];
-                                *reinterpret_cast<uint4*>(out + obase + (j + k * LPR) * VEC) =
-                                    pack16<T>(f);
-                            } else {
-                                const int c = j + k * 32;
-                                if (c < D) out[obase + c] = Elem<T>::from_f(acc[k][0]);
-                            }
-                        }
-                    }
-                }
-            }
-            __syncwarp();
-        }
-    }
-}
-
-// ---------------------------------------------------------------------------
-// host side: instantiation table and launch
-// ---------------------------------------------------------------------------
-template <typename T, int LPR, int NV, bool SCALAR>
-static cudaError_t launch_fwd_inst(const Params& p, const LaunchShape& ls, size_t smem,
-                                   cudaStream_t stream) {
-    auto kern = msda_fwd_kernel<T, LPR, NV, SCALAR>;
-    if (smem > 48 * 1024) {
-        cudaError_t e =
-            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-    }
-    int grid = 0;
-    cudaError_t e = persistent_grid(reinterpret_cast<const void*>(kern), smem, ls, p, &grid);
-    if (e != cudaSuccess) return e;
-    kern<<<grid, kThreadsPerCta, smem, stream>>>(p);
-    return cudaGetLastError();
-}
-
-template <typename T>
-static cudaError_t launch_fwd_typed(const Params& p, const RowPlan& rp, const LaunchShape& ls, size_t smem,
-                                    cudaStream_t stream) {
-    if (rp.scalar) return launch_fwd_inst<T, 32, 8, true>(p, ls, smem, stream);
-    switch (rp.lpr * 100 + rp.nv) {
-        case 101: return launch_fwd_inst<T, 1, 1, false>(p, ls, smem, stream);
-        case 201: return launch_fwd_inst<T, 2, 1, false>(p, ls, smem, stream);
-        case 401: return launch_fwd_inst<T, 4, 1, false>(p, ls, smem, stream);
-        case 801: return launch_fwd_inst<T, 8, 1, false>(p, ls, smem, stream);
-        case 1601: return launch_fwd_inst<T, 16, 1, false>(p, ls, smem, stream);
-        case 3201: return launch_fwd_inst<T, 32, 1, false>(p, ls, smem, stream);
-        case 3202:
-            if constexpr (sizeof(T) == 4) {
-                return launch_fwd_inst<T, 32, 2, false>(p, ls, smem, stream);
-            }
-            return cudaErrorInvalidValue;
-        default: return cudaErrorInvalidValue;
-    }
-}
 
 uint32_t fwd_warp_smem(int samples_per_item, size_t elem) {
     return warp_smem_bytes(samples_per_item, elem, 0);
@@ -274,13 +27,7 @@ uint32_t fwd_warp_smem(int samples_per_item, size_t elem) {
 
 cudaError_t launch_forward(const Params& p, int dtype, const RowPlan& rp, const LaunchShape& ls,
                            cudaStream_t stream) {
-    const size_t smem = static_cast<size_t>(p.warp_smem) * kWarpsPerCta;
-    switch (dtype) {
-        case 0: return launch_fwd_typed<float>(p, rp, ls, smem, stream);
-        case 1: return launch_fwd_typed<__half>(p, rp, ls, smem, stream);
-        case 2: return launch_fwd_typed<__nv_bfloat16>(p, rp, ls, smem, stream);
-        default: return cudaErrorInvalidValue;
-    }
+    return launch_forward_cps<4>(p, dtype, rp, ls, stream);
 }
 
 }  // namespace msda

@@ -51,6 +51,12 @@ cudaError_t launch_backward(const Params& p, int dtype, int acc_f32, const RowPl
                             const LaunchShape& ls, cudaStream_t stream);
 uint32_t bwd_warp_smem(int samples_per_item, size_t elem);
 
+// Geometric kernel attention: same parameter block (grad_loc unused), one row per sample.
+cudaError_t launch_gka_forward(const Params& p, int dtype, const RowPlan& rp,
+                               const LaunchShape& ls, cudaStream_t stream);
+cudaError_t launch_gka_backward(const Params& p, int dtype, int acc_f32, const RowPlan& rp,
+                                const LaunchShape& ls, cudaStream_t stream);
+
 // out[i] = (T)acc[i] for n elements; dtype 1 = fp16, 2 = bf16.
 cudaError_t launch_downcast(const float* acc, void* out, long long n, int dtype,
                             cudaStream_t stream);

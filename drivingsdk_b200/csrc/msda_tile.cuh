@@ -154,10 +154,23 @@ __device__ __forceinline__ WarpStage<T> warp_stage_init(const Params& p, unsigne
     return st;
 }
 
+// With one record per sample (CPS == 1) a chunk writes only the first 32 slots; the gather
+// loop of a single-task item may read up to a full trip beyond its last sample, so the
+// other slots are set to "no row" once.
+template <int CPS>
+__device__ __forceinline__ void init_unused_slots(uint2* s_slot, int lane) {
+    if constexpr (CPS == 1) {
+#pragma unroll
+        for (int i = kChunk; i < kSlots + kSlotPad; i += 32) s_slot[i + lane] = make_uint2(kNoRow, 0u);
+        __syncwarp();
+    }
+}
+
 // Phase 1 of one chunk: lane = sample. Obtains (x, y, weight) — from the staged buffer or
-// directly — and leaves the four slot records of the sample in shared memory. Returns whether
-// this lane holds a sample; `gi` is its global sample index.
-template <typename T>
+// directly — and leaves the sample's slot records in shared memory: four (bilinear corners)
+// for CPS == 4, one (clamped integer pixel) for CPS == 1. Returns whether this lane holds a
+// sample; `gi` is its global sample index.
+template <typename T, int CPS>
 __device__ __forceinline__ bool phase1(const Params& p, const LaneLevels& lv, int chunk, int lane,
                                        long long item, int ntask_here, const T* sloc,
                                        const T* sattn, uint2* s_slot, SampleGeom& geom,
@@ -190,12 +203,21 @@ __device__ __forceinline__ bool phase1(const Params& p, const LaneLevels& lv, in
         const int c = (p.tasks_per_item == 1) ? chunk : 0;
         const uint32_t row_base =
             (b * static_cast<uint32_t>(p.K) + static_cast<uint32_t>(lv.start(c))) * p.H + h;
-        sample_setup(lx, ly, a, lv.w(c), lv.h(c), row_base, static_cast<uint32_t>(p.H),
-                     p.row_units, rec01, rec23, geom);
+        if constexpr (CPS == 4) {
+            sample_setup(lx, ly, a, lv.w(c), lv.h(c), row_base, static_cast<uint32_t>(p.H),
+                         p.row_units, rec01, rec23, geom);
+        } else {
+            sample_setup_nearest(lx, ly, a, lv.w(c), lv.h(c), row_base,
+                                 static_cast<uint32_t>(p.H), p.row_units, rec01, geom);
+        }
     }
-    uint4* dst = reinterpret_cast<uint4*>(s_slot) + 2 * lane;
-    dst[0] = rec01;
-    dst[1] = rec23;
+    if constexpr (CPS == 4) {
+        uint4* dst = reinterpret_cast<uint4*>(s_slot) + 2 * lane;
+        dst[0] = rec01;
+        dst[1] = rec23;
+    } else {
+        s_slot[lane] = make_uint2(rec01.x, rec01.y);
+    }
     return active;
 }
 

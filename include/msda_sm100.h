@@ -1,4 +1,5 @@
-/* C ABI of the sm_100a multi-scale deformable attention (MSDA) kernels.
+/* C ABI of the sm_100a multi-scale deformable attention (MSDA) kernels and of the
+ * geometric kernel attention kernels that share their machinery (gka_sm100_*).
  *
  * This library sits where the reference's generated operator API sat:
  * `aclnnMultiScaleDeformableAttn[GetWorkspaceSize]` and
@@ -127,6 +128,29 @@ int msda_sm100_backward_static(const void* value, const int32_t* spatial_shapes,
                                void* grad_value, void* grad_sampling_loc, void* grad_attn_weight,
                                int B, int K, int H, int D, int L, int Q, int P, int dtype,
                                void* stream);
+
+/* Geometric kernel attention (nearest-pixel sampling), forward. Replaces
+ * aclnnGeometricKernelAttention (mx_driving/csrc/GeometricKernelAttentionFunc.cpp:34-57;
+ * device kernel kernels/geometric_kernel_attention/op_kernel/geometric_kernel_attention.cpp).
+ * Same layouts as above, but sampling_locations holds PIXEL coordinates (x, y) of each
+ * level (in `dtype`), which are truncated to integers and clamped into the level:
+ *   output[b,q,h,:] = sum_{l,p} attention[b,q,h,l,p] * value[b, start_l + y*W_l + x, h, :]. */
+int gka_sm100_forward(const void* value, const int32_t* spatial_shapes,
+                      const int32_t* level_start_index, const void* sampling_locations,
+                      const void* attention_weights, void* output, int B, int K, int H, int D,
+                      int L, int Q, int P, int dtype, void* stream);
+
+/* Geometric kernel attention, backward. Replaces aclnnGeometricKernelAttnGrad
+ * (mx_driving/csrc/GeometricKernelAttentionFunc.cpp:59-118). grad_value is zero-filled here
+ * and accumulated in fp32 (in `workspace` for the 16-bit dtypes: same size rule as
+ * msda_sm100_backward_workspace_bytes; unused for MSDA_F32); grad_attn_weight is fully
+ * written; sampling locations have no gradient. */
+int gka_sm100_backward_ws(const void* value, const int32_t* spatial_shapes,
+                          const int32_t* level_start_index, const void* sampling_locations,
+                          const void* attention_weights, const void* grad_output,
+                          void* grad_value, void* grad_attn_weight, void* workspace,
+                          size_t workspace_bytes, int B, int K, int H, int D, int L, int Q, int P,
+                          int dtype, void* stream);
 
 /* Algorithmic (compulsory) bytes one call moves: every operand read once and
  * every result written once. Used by benchmarks for the bandwidth roofline. */

@@ -1,6 +1,8 @@
 """``mx_driving._C`` for this path: the two extension entry points
 (mx_driving/csrc/pybind.cpp:110-111)."""
 from drivingsdk_b200._C import (  # noqa: F401
+    geometric_kernel_attention_backward,
+    geometric_kernel_attention_forward,
     multi_scale_deformable_attn,
     multi_scale_deformable_attn_backward,
 )

@@ -237,3 +237,67 @@ void msda_oracle_kink_distance(const int* shapes, const float* loc, double* dist
                 if (!(dist[si] == dist[si])) dist[si] = 0.0; /* NaN: treat as on a kink */
             }
 }
+
+/* ---- geometric kernel attention (nearest-pixel sibling of MSDA) -----------------------
+ * Restates the reference's CPU golden (tests/torch/test_geometric_kernel_attention.py:44-103):
+ * sampling locations are integer pixel coordinates (x, y), clamped into [0, W-1] x [0, H-1]
+ * of their level (the golden converts them with .long(), i.e. truncation, first);
+ *   out[b,q,h,:]      = sum_{l,p} attn * value[b, start_l + y*W_l + x, h, :]
+ *   grad_value[row,:] += attn * grad_out[b,q,h,:]
+ *   grad_attn         = <value[row,:], grad_out[b,q,h,:]>.
+ * Pinned by tests/golden/gka_golden.npz (outputs of that golden). */
+static size_t gka_row(const float* loc, size_t si, int Hl, int Wl) {
+    long x = (long)loc[2 * si], y = (long)loc[2 * si + 1];
+    if (x < 0) x = 0;
+    if (x > Wl - 1) x = Wl - 1;
+    if (y < 0) y = 0;
+    if (y > Hl - 1) y = Hl - 1;
+    return (size_t)(y * Wl + x);
+}
+
+void gka_oracle_forward(const float* value, const int* shapes, const int* starts,
+                        const float* loc, const float* attn, double* out, int B, int K, int H,
+                        int D, int L, int Q, int P) {
+    const long ntask = (long)B * Q * H;
+    for (long t = 0; t < ntask; ++t) {
+        const int h = (int)(t % H);
+        const int b = (int)(t / ((long)Q * H));
+        double* o = out + (size_t)t * D;
+        for (int d = 0; d < D; ++d) o[d] = 0.0;
+        for (int l = 0; l < L; ++l)
+            for (int p = 0; p < P; ++p) {
+                const size_t si = ((size_t)t * L + l) * P + p;
+                const size_t row = gka_row(loc, si, shapes[2 * l], shapes[2 * l + 1]);
+                const float* v = value + (((size_t)b * K + starts[l] + row) * H + h) * (size_t)D;
+                const double a = (double)attn[si];
+                for (int d = 0; d < D; ++d) o[d] += a * (double)v[d];
+            }
+    }
+}
+
+void gka_oracle_backward(const float* value, const int* shapes, const int* starts,
+                         const float* loc, const float* attn, const float* grad_out,
+                         double* grad_value, double* grad_attn, int B, int K, int H, int D, int L,
+                         int Q, int P) {
+    const size_t nval = (size_t)B * K * H * D;
+    for (size_t i = 0; i < nval; ++i) grad_value[i] = 0.0;
+    const long ntask = (long)B * Q * H;
+    for (long t = 0; t < ntask; ++t) {
+        const int h = (int)(t % H);
+        const int b = (int)(t / ((long)Q * H));
+        const float* go = grad_out + (size_t)t * D;
+        for (int l = 0; l < L; ++l)
+            for (int p = 0; p < P; ++p) {
+                const size_t si = ((size_t)t * L + l) * P + p;
+                const size_t row = gka_row(loc, si, shapes[2 * l], shapes[2 * l + 1]);
+                const size_t off = (((size_t)b * K + starts[l] + row) * H + h) * (size_t)D;
+                const double a = (double)attn[si];
+                double s = 0.0;
+                for (int d = 0; d < D; ++d) {
+                    grad_value[off + d] += a * (double)go[d];
+                    s += (double)value[off + d] * (double)go[d];
+                }
+                grad_attn[si] = s;
+            }
+    }
+}

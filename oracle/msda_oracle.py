@@ -40,6 +40,10 @@ def _load():
         lib.msda_oracle_forward.restype = None
         lib.msda_oracle_backward.argtypes = [f32, i32, i32, f32, f32, f32, f64, f64, f64] + dims
         lib.msda_oracle_backward.restype = None
+        lib.gka_oracle_forward.argtypes = [f32, i32, i32, f32, f32, f64] + dims
+        lib.gka_oracle_forward.restype = None
+        lib.gka_oracle_backward.argtypes = [f32, i32, i32, f32, f32, f32, f64, f64] + dims
+        lib.gka_oracle_backward.restype = None
         lib.msda_oracle_kink_distance.argtypes = [i32, f32, f64] + [ctypes.c_int] * 5
         lib.msda_oracle_kink_distance.restype = None
         lib.msda_oracle_set_threads.argtypes = [ctypes.c_int]
@@ -100,3 +104,23 @@ def kink_distance(shapes, loc):
     dist = np.empty((B, Q, H, L, P), dtype=np.float64)
     _load().msda_oracle_kink_distance(shapes, loc, dist, B, H, L, Q, P)
     return dist
+
+
+def gka_forward(value, shapes, starts, loc, attn):
+    """Geometric kernel attention, output[B, Q, H*D] in float64 (loc = pixel coordinates)."""
+    value, shapes, starts, loc, attn, dims = _prep(value, shapes, starts, loc, attn)
+    B, K, H, D, L, Q, P = dims
+    out = np.empty((B, Q, H * D), dtype=np.float64)
+    _load().gka_oracle_forward(value, shapes, starts, loc, attn, out, *dims)
+    return out
+
+
+def gka_backward(value, shapes, starts, loc, attn, grad_out):
+    """(grad_value, grad_attn) in float64."""
+    value, shapes, starts, loc, attn, dims = _prep(value, shapes, starts, loc, attn)
+    B, K, H, D, L, Q, P = dims
+    grad_out = np.ascontiguousarray(grad_out, dtype=np.float32).reshape(B, Q, H * D)
+    gv = np.empty(value.shape, dtype=np.float64)
+    ga = np.empty(attn.shape, dtype=np.float64)
+    _load().gka_oracle_backward(value, shapes, starts, loc, attn, grad_out, gv, ga, *dims)
+    return gv, ga
