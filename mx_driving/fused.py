@@ -1,0 +1,14 @@
+"""Deprecated import path kept by the reference (mx_driving/fused.py:7-9): re-exports the
+MSDA operator names. The other operators that module re-exports are not part of this tree."""
+import warnings
+
+from drivingsdk_b200.ops.multi_scale_deformable_attn import (  # noqa: F401
+    MultiScaleDeformableAttnFunction,
+    multi_scale_deformable_attn,
+    npu_multi_scale_deformable_attn_function,
+)
+
+warnings.warn(
+    "This package is deprecated and will be removed in future. Please use `mx_driving` instead.",
+    DeprecationWarning,
+)
