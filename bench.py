@@ -376,13 +376,13 @@ def run_e2e(sdk, host_sets, shapes_i32, starts_i32, dev, dtype, world, query_sha
     """Public API, host operands. Every step copies value / locations / weights / grad_output
     from pinned host memory to the device, runs forward and backward through the autograd
     function, and copies output and all three gradients back to pinned host memory — all
-    inside the timed region. The three stages run on three streams with two buffer slots, so
+    inside the timed region. The three stages run on three streams with three buffer slots, so
     the upload of step i+1 and the download of step i-1 overlap the kernels of step i (PCIe
     is full duplex); per step the same bytes move as without the overlap."""
     import torch
     import torch.distributed as dist
     h0 = host_sets[0]
-    NSLOT = 2
+    NSLOT = 3
     s_comp = torch.cuda.current_stream()
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     d_in = [{k: torch.empty_like(v, device=dev) for k, v in h0.items()} for _ in range(NSLOT)]
@@ -453,7 +453,7 @@ def run_e2e(sdk, host_sets, shapes_i32, starts_i32, dev, dtype, world, query_sha
     d2h = sum(h.numel() * h.element_size() for h in h_out[0])
     return {"value": global_samples / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms,
             "steps": steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "overlap": "3 streams, 2 slots: upload, kernels and download of neighbouring steps overlap"}
+            "overlap": "3 streams, 3 slots: upload, kernels and download of neighbouring steps overlap"}
 
 
 def main():
