@@ -98,7 +98,6 @@ class ClockSampler:
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -294,10 +293,23 @@ def run_native(args):
         for e in quad:
             e.record(stream)  # materialise the underlying cudaEvent_t
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # The timed region is short (K steps of ~0.5 ms), so the clock sampler would mostly see an
+    # idle GPU. Untimed steps of the same work run for ~0.4 s before and ~0.2 s after the timed
+    # region while the sampler is on, so that its samples are taken under this load.
+    def busy(seconds):
+        t_end = time.perf_counter() + seconds
+        i = 0
+        while time.perf_counter() < t_end:
+            step_c_abi(sets[i % NSETS])
+            i += 1
+            if i % 16 == 0:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-        time.sleep(0.25)
+    busy(0.4)
     launches0 = lib.msda_sm100_launch_count()
     barrier()
     ev0.record(stream)
@@ -309,6 +321,7 @@ def run_native(args):
     barrier()
     total_ms = ev0.elapsed_time(ev1)
     launches = lib.msda_sm100_launch_count() - launches0
+    busy(0.2)
     clocks = sampler.stop() if rank == 0 else None
     fwd_ms = sum(q[0].elapsed_time(q[1]) for q in kev) / K_steps
     bwd_ms = sum(q[2].elapsed_time(q[3]) for q in kev) / K_steps
