@@ -11,6 +11,9 @@ Public surface, same names as the reference package exports for this path
     geometric_kernel_attention(value, spatial_shapes, level_start_index, sampling_locations,
                                attention_weights) -> Tensor   (nearest-pixel sibling operator,
                                mx_driving/ops/geometric_kernel_attention.py:27-54)
+    deformable_aggregation / npu_deformable_aggregation(mc_ms_feat, spatial_shape,
+                               scale_start_index, sampling_location, weights) -> Tensor
+                               (mx_driving/ops/npu_deformable_aggregation.py:9-88)
 
 The operator names are resolved on first use, so that the patcher (pure Python)
 can be imported on a machine without the compiled extension. Using an operator
@@ -26,8 +29,10 @@ _OP_NAMES = (
     "npu_multi_scale_deformable_attn_function",
 )
 _GKA_NAMES = ("geometric_kernel_attention", "GeometricKernelAttentionFunc")
+_DA_NAMES = ("npu_deformable_aggregation", "deformable_aggregation", "AdsDeformableAggregation")
 
-__all__ = list(_OP_NAMES) + list(_GKA_NAMES) + ["patcher", "default_patcher", "dist"]
+__all__ = (list(_OP_NAMES) + list(_GKA_NAMES) + list(_DA_NAMES)
+           + ["patcher", "default_patcher", "dist"])
 
 
 def __getattr__(name):
@@ -36,6 +41,9 @@ def __getattr__(name):
         return getattr(mod, name)
     if name in _GKA_NAMES:
         mod = importlib.import_module(__name__ + ".ops.geometric_kernel_attention")
+        return getattr(mod, name)
+    if name in _DA_NAMES:
+        mod = importlib.import_module(__name__ + ".ops.npu_deformable_aggregation")
         return getattr(mod, name)
     if name == "_C":
         return importlib.import_module(__name__ + "._C")

@@ -26,6 +26,9 @@ SIGNATURES = {
     "gka_sm100_forward": (_i, [_vp, _ip, _ip, _vp, _vp, _vp] + _DIMS7 + [_i, _vp]),
     "gka_sm100_backward_ws": (_i, [_vp, _ip, _ip, _vp, _vp, _vp, _vp, _vp, _vp, _sz] + _DIMS7
                               + [_i, _vp]),
+    "da_sm100_forward": (_i, [_vp, _ip, _ip, _vp, _vp, _vp] + [_i] * 8 + [_vp]),
+    "da_sm100_backward": (_i, [_vp, _ip, _ip, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 8 + [_vp]),
+    "da_sm100_last_cuda_error": (_i, []),
     "msda_sm100_static_scratch_bytes": (_sz, []),
     "msda_sm100_backward_static": (_i, [_vp, _ip, _ip, _vp, _vp, _vp, _vp, _vp, _vp] + _DIMS7
                                    + [_i, _vp]),

@@ -296,6 +296,115 @@ std::tuple<at::Tensor, at::Tensor> geometric_kernel_attention_backward(
     return std::make_tuple(grad_value, grad_attn);
 }
 
+// ---------------------------------------------------------------------------
+// deformable aggregation (mx_driving/csrc/DeformableAggregation.cpp:20-76,
+// pybind.cpp:121-122). The kernels are fp32; 16-bit tensors are converted on the way in
+// and out, as the reference binding does for its other 16-bit paths.
+// ---------------------------------------------------------------------------
+namespace {
+
+struct DaDims {
+    int B, F, C, A, Pts, cams, scales, G;
+};
+
+DaDims check_da_inputs(const at::Tensor& feat, const at::Tensor& shape, const at::Tensor& start,
+                       const at::Tensor& loc, const at::Tensor& wts) {
+    TORCH_CHECK(feat.is_cuda() && loc.is_cuda() && wts.is_cuda(),
+                "deformable_aggregation: mc_ms_feat, sampling_location and weights must be CUDA "
+                "tensors (this build has no CPU path)");
+    TORCH_CHECK(feat.dim() == 3, "mc_ms_feat.dim() must be 3, but got: ", feat.dim());
+    TORCH_CHECK(shape.dim() == 3, "spatial_shape.dim() must be 3, but got: ", shape.dim());
+    TORCH_CHECK(start.dim() == 2, "scale_start_index.dim() must be 2, but got: ", start.dim());
+    TORCH_CHECK(loc.dim() == 5, "sampling_location.dim() must be 5, but got: ", loc.dim());
+    TORCH_CHECK(wts.dim() == 6, "weights.dim() must be 6, but got: ", wts.dim());
+    TORCH_CHECK(wts.size(5) % 8 == 0, "weights.sizes()[5] must be multiple of 8, but got: ",
+                wts.size(5));
+    TORCH_CHECK(is_float_kind(feat.scalar_type()) && is_float_kind(loc.scalar_type()) &&
+                    is_float_kind(wts.scalar_type()),
+                "deformable_aggregation: float16, bfloat16 or float32 tensors expected");
+    TORCH_CHECK(shape.scalar_type() == at::kInt && start.scalar_type() == at::kInt,
+                "spatial_shape and scale_start_index must be int32 tensors");
+    DaDims d;
+    d.B = static_cast<int>(feat.size(0));
+    d.F = static_cast<int>(feat.size(1));
+    d.C = static_cast<int>(feat.size(2));
+    d.A = static_cast<int>(wts.size(1));
+    d.Pts = static_cast<int>(wts.size(2));
+    d.cams = static_cast<int>(wts.size(3));
+    d.scales = static_cast<int>(wts.size(4));
+    d.G = static_cast<int>(wts.size(5));
+    TORCH_CHECK(wts.size(0) == d.B && loc.size(0) == d.B && loc.size(1) == d.A &&
+                    loc.size(2) == d.Pts && loc.size(3) == d.cams && loc.size(4) == 2,
+                "sampling_location / weights shapes do not match");
+    TORCH_CHECK(shape.size(0) == d.cams && shape.size(1) == d.scales && shape.size(2) == 2 &&
+                    start.size(0) == d.cams && start.size(1) == d.scales,
+                "spatial_shape must be [cams, scales, 2] and scale_start_index [cams, scales]");
+    TORCH_CHECK(d.C % d.G == 0, "the number of channels must be a multiple of the groups");
+    return d;
+}
+
+void raise_on_da_error(int rc, const char* what) {
+    if (rc == MSDA_OK) return;
+    if (rc == MSDA_ERR_CUDA) {
+        const auto ce = static_cast<cudaError_t>(da_sm100_last_cuda_error());
+        TORCH_CHECK(false, what, ": CUDA error: ", cudaGetErrorString(ce));
+    }
+    TORCH_CHECK(false, what, ": ", msda_sm100_strerror(rc));
+}
+
+}  // namespace
+
+at::Tensor deformable_aggregation(const at::Tensor& feat_in, const at::Tensor& shape_in,
+                                  const at::Tensor& start_in, const at::Tensor& loc_in,
+                                  const at::Tensor& wts_in) {
+    const DaDims d = check_da_inputs(feat_in, shape_in, start_in, loc_in, wts_in);
+    const c10::cuda::CUDAGuard guard(feat_in.device());
+    const at::Tensor feat = feat_in.to(at::kFloat).contiguous();
+    const at::Tensor loc = loc_in.to(at::kFloat).contiguous();
+    const at::Tensor wts = wts_in.to(at::kFloat).contiguous();
+    const at::Tensor shape = shape_in.contiguous();
+    const at::Tensor start = start_in.contiguous();
+    at::Tensor out = at::empty({d.B, d.A, d.C}, feat.options());
+    if (out.numel() == 0) return out.to(feat_in.scalar_type());
+    const int rc = da_sm100_forward(feat.data_ptr(), shape.data_ptr<int32_t>(),
+                                    start.data_ptr<int32_t>(), loc.data_ptr(), wts.data_ptr(),
+                                    out.data_ptr(), d.B, d.F, d.C, d.A, d.Pts, d.cams, d.scales,
+                                    d.G, at::cuda::getCurrentCUDAStream().stream());
+    raise_on_da_error(rc, "npu_deformable_aggregation");
+    return out.to(feat_in.scalar_type());
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> deformable_aggregation_backward(
+    const at::Tensor& feat_in, const at::Tensor& shape_in, const at::Tensor& start_in,
+    const at::Tensor& loc_in, const at::Tensor& wts_in, const at::Tensor& grad_out_in,
+    const at::Tensor& grad_feat_in, const at::Tensor& grad_loc_in, const at::Tensor& grad_wts_in) {
+    // the three gradient tensors are accepted for call compatibility with the reference
+    // (it fills tensors the caller zeroed); results are returned as new tensors
+    (void)grad_feat_in; (void)grad_loc_in; (void)grad_wts_in;
+    const DaDims d = check_da_inputs(feat_in, shape_in, start_in, loc_in, wts_in);
+    TORCH_CHECK(grad_out_in.is_cuda() && is_float_kind(grad_out_in.scalar_type()) &&
+                    grad_out_in.numel() == static_cast<int64_t>(d.B) * d.A * d.C,
+                "grad_output must be a CUDA tensor [bs, anchors, channels]");
+    const c10::cuda::CUDAGuard guard(feat_in.device());
+    const at::Tensor feat = feat_in.to(at::kFloat).contiguous();
+    const at::Tensor loc = loc_in.to(at::kFloat).contiguous();
+    const at::Tensor wts = wts_in.to(at::kFloat).contiguous();
+    const at::Tensor shape = shape_in.contiguous();
+    const at::Tensor start = start_in.contiguous();
+    const at::Tensor grad_out = grad_out_in.to(at::kFloat).contiguous();
+    at::Tensor grad_feat = at::empty_like(feat);
+    at::Tensor grad_loc = at::empty_like(loc);
+    at::Tensor grad_wts = at::empty_like(wts);
+    const int rc = da_sm100_backward(
+        feat.data_ptr(), shape.data_ptr<int32_t>(), start.data_ptr<int32_t>(), loc.data_ptr(),
+        wts.data_ptr(), grad_out.data_ptr(), grad_feat.data_ptr(), grad_loc.data_ptr(),
+        grad_wts.data_ptr(), d.B, d.F, d.C, d.A, d.Pts, d.cams, d.scales, d.G,
+        at::cuda::getCurrentCUDAStream().stream());
+    raise_on_da_error(rc, "npu_deformable_aggregation_backward");
+    return std::make_tuple(grad_feat.to(feat_in.scalar_type()), grad_loc.to(loc_in.scalar_type()),
+                           grad_wts.to(wts_in.scalar_type()));
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "sm_100a multi-scale deformable attention (drop-in for mx_driving._C on this path)";
     m.def("multi_scale_deformable_attn", &multi_scale_deformable_attn,
@@ -311,4 +420,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("geometric_kernel_attention_backward", &geometric_kernel_attention_backward,
           "GKA backward: (value, spatial_shapes, level_start_index, sampling_locations, "
           "attention_weights, grad_output) -> (grad_value, grad_attn_weights)");
+    m.def("npu_deformable_aggregation", &deformable_aggregation,
+          "deformable aggregation forward: (mc_ms_feat, spatial_shape, scale_start_index, "
+          "sampling_location, weights) -> output");
+    m.def("npu_deformable_aggregation_backward", &deformable_aggregation_backward,
+          "deformable aggregation backward -> (grad_mc_ms_feat, grad_sampling_location, "
+          "grad_weights)");
 }

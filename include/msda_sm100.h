@@ -152,6 +152,25 @@ int gka_sm100_backward_ws(const void* value, const int32_t* spatial_shapes,
                           size_t workspace_bytes, int B, int K, int H, int D, int L, int Q, int P,
                           int dtype, void* stream);
 
+/* Deformable aggregation (multi-camera, multi-scale feature sampling with per-group
+ * weights), fp32. Replaces aclnnDeformableAggregation / aclnnDeformableAggregationGrad
+ * (mx_driving/csrc/DeformableAggregation.cpp:49-50, 72-74; device kernels
+ * kernels/deformable_aggregation/op_kernel/deformable_aggregation{,_grad}.cpp).
+ *   feat [B, F, C]; spatial_shape [cams, scales, 2] (h, w) and scale_start [cams, scales]
+ *   (int32, host or device); sampling_location [B, A, Pts, cams, 2] (w, h) in (0, 1);
+ *   weights [B, A, Pts, cams, scales, G]; out / grad_out [B, A, C].
+ * A sample counts only if 0 < w < 1 and 0 < h < 1. Limits: C <= 256, C % G == 0, G <= 32,
+ * scales <= 32, cams * scales <= 64. Backward zero-fills grad_feat on `stream` and fully
+ * writes grad_sampling_location and grad_weights. */
+int da_sm100_forward(const void* feat, const int32_t* spatial_shape, const int32_t* scale_start,
+                     const void* sampling_location, const void* weights, void* out, int B, int F,
+                     int C, int A, int Pts, int cams, int scales, int G, void* stream);
+int da_sm100_backward(const void* feat, const int32_t* spatial_shape, const int32_t* scale_start,
+                      const void* sampling_location, const void* weights, const void* grad_out,
+                      void* grad_feat, void* grad_sampling_location, void* grad_weights, int B,
+                      int F, int C, int A, int Pts, int cams, int scales, int G, void* stream);
+int da_sm100_last_cuda_error(void);
+
 /* Algorithmic (compulsory) bytes one call moves: every operand read once and
  * every result written once. Used by benchmarks for the bandwidth roofline. */
 size_t msda_sm100_forward_bytes(int B, int K, int H, int D, int L, int Q, int P, int dtype);

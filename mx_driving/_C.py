@@ -4,5 +4,7 @@ from drivingsdk_b200._C import (  # noqa: F401
     geometric_kernel_attention_backward,
     geometric_kernel_attention_forward,
     multi_scale_deformable_attn,
+    npu_deformable_aggregation,
+    npu_deformable_aggregation_backward,
     multi_scale_deformable_attn_backward,
 )

@@ -43,3 +43,27 @@ def msda_forward_backward(value, shapes, loc, attn, grad_out):
     out = msda_forward(value, shapes, loc, attn)
     out.backward(grad_out)
     return out.detach(), value.grad, loc.grad, attn.grad
+
+
+def da_forward(feat, shapes, starts, loc, wts):
+    """Deformable aggregation restated with grid_sample, independent of the C oracle; used to
+    cross-check the oracle's backward through autograd.
+    feat [B,F,C]; shapes [cams,scales,2] (h,w); starts [cams,scales]; loc [B,A,Pts,cams,2] (w,h)
+    in (0,1); wts [B,A,Pts,cams,scales,G] -> out [B,A,C]."""
+    B, Fk, C = feat.shape
+    _, A, Pts, cams, scales, G = wts.shape
+    inside = ((loc > 0) & (loc < 1)).all(-1)                      # [B,A,Pts,cams]
+    out = feat.new_zeros(B, A, C)
+    for cam in range(cams):
+        grid = (2.0 * loc[:, :, :, cam] - 1.0)                     # [B,A,Pts,2]
+        for sc in range(scales):
+            h, w = int(shapes[cam, sc, 0]), int(shapes[cam, sc, 1])
+            st = int(starts[cam, sc])
+            img = feat[:, st:st + h * w].reshape(B, h, w, C).permute(0, 3, 1, 2)
+            val = F.grid_sample(img, grid, mode="bilinear", padding_mode="zeros",
+                                align_corners=False)                # [B,C,A,Pts]
+            wt = wts[:, :, :, cam, sc]                              # [B,A,Pts,G]
+            wt = wt.repeat_interleave(C // G, dim=-1).permute(0, 3, 1, 2)
+            mask = inside[:, :, :, cam].unsqueeze(1).to(val.dtype)
+            out = out + (val * wt * mask).sum(-1).transpose(1, 2)
+    return out

@@ -301,3 +301,93 @@ void gka_oracle_backward(const float* value, const int* shapes, const int* start
             }
     }
 }
+
+/* ---- deformable aggregation ------------------------------------------------------------
+ * Restates the reference's numpy golden of the forward
+ * (tests/torch/test_deformable_aggregation.py:33-125): for every (batch, anchor, point, cam,
+ * scale) a sample at loc = (w, h), skipped unless 0 < w < 1 and 0 < h < 1; pixel
+ * coordinates loc * size - 0.5; bilinear corners that fall outside the map read as zero; the
+ * interpolated C-vector is multiplied group-wise by weights[..., group] and summed into
+ * out[b, anchor, :]. The backward is the derivative of that expression (the reference has no
+ * CPU golden for it): grad_feat scatter, grad_weights[..., g] = <interpolated group g,
+ * grad_out group g>, grad_loc from the bilinear slopes, summed over scales and channels.
+ * Forward pinned by tests/golden/da_golden.npz (outputs of the reference golden); backward
+ * cross-checked against autograd of an independent PyTorch restatement in the tests.
+ * feat [B,F,C]; shapes [cams,scales,2] (h,w); starts [cams,scales]; loc [B,A,Pts,cams,2]
+ * (w,h); wts [B,A,Pts,cams,scales,G]. */
+static void da_sample(const float* feat, const int* shapes, const int* starts, const float* loc,
+                      const float* wts, const float* grad_out, double* out, double* grad_feat,
+                      double* grad_loc, double* grad_wts, int b, int a, int pt, int cam, int sc,
+                      int F, int C, int A, int Pts, int cams, int scales, int G) {
+    const size_t pc = (((size_t)b * A + a) * Pts + pt) * cams + cam;
+    const size_t wi = (pc * scales + sc) * G;
+    const double lw_n = (double)loc[2 * pc], lh_n = (double)loc[2 * pc + 1];
+    const int cpg = C / G;
+    if (grad_wts)
+        for (int g = 0; g < G; ++g) grad_wts[wi + g] = 0.0;
+    if (!(lw_n > 0.0 && lw_n < 1.0 && lh_n > 0.0 && lh_n < 1.0)) return;
+    const int map = cam * scales + sc;
+    const int Hm = shapes[2 * map], Wm = shapes[2 * map + 1];
+    corners_t c;
+    corners(lw_n, lh_n, Hm, Wm, &c);
+    if (!c.valid) return;
+    const float* rows[4] = {0, 0, 0, 0};
+    double* grows[4] = {0, 0, 0, 0};
+    for (int k = 0; k < 4; ++k)
+        if (c.ok[k]) {
+            const size_t off = ((size_t)b * F + starts[map] + c.row[k]) * (size_t)C;
+            rows[k] = feat + off;
+            if (grad_feat) grows[k] = grad_feat + off;
+        }
+    const double hw = 1.0 - c.lw, hh = 1.0 - c.lh;
+    double gx = 0.0, gy = 0.0;
+    for (int ch = 0; ch < C; ++ch) {
+        const int g = ch / cpg;
+        const double wt = (double)wts[wi + g];
+        double v[4];
+        for (int k = 0; k < 4; ++k) v[k] = rows[k] ? (double)rows[k][ch] : 0.0;
+        const double val = c.w[0] * v[0] + c.w[1] * v[1] + c.w[2] * v[2] + c.w[3] * v[3];
+        if (out) out[((size_t)b * A + a) * C + ch] += val * wt;
+        if (grad_out) {
+            const double go = (double)grad_out[((size_t)b * A + a) * C + ch];
+            for (int k = 0; k < 4; ++k)
+                if (grows[k]) grows[k][ch] += c.w[k] * wt * go;
+            grad_wts[wi + g] += val * go;
+            gx += go * wt * (double)Wm * (hh * (v[1] - v[0]) + c.lh * (v[3] - v[2]));
+            gy += go * wt * (double)Hm * (hw * (v[2] - v[0]) + c.lw * (v[3] - v[1]));
+        }
+    }
+    if (grad_loc) {
+        grad_loc[2 * pc] += gx;
+        grad_loc[2 * pc + 1] += gy;
+    }
+}
+
+void da_oracle_forward(const float* feat, const int* shapes, const int* starts, const float* loc,
+                       const float* wts, double* out, int B, int F, int C, int A, int Pts,
+                       int cams, int scales, int G) {
+    for (size_t i = 0; i < (size_t)B * A * C; ++i) out[i] = 0.0;
+    for (int b = 0; b < B; ++b)
+        for (int a = 0; a < A; ++a)
+            for (int pt = 0; pt < Pts; ++pt)
+                for (int cam = 0; cam < cams; ++cam)
+                    for (int sc = 0; sc < scales; ++sc)
+                        da_sample(feat, shapes, starts, loc, wts, 0, out, 0, 0, 0, b, a, pt, cam,
+                                  sc, F, C, A, Pts, cams, scales, G);
+}
+
+void da_oracle_backward(const float* feat, const int* shapes, const int* starts,
+                        const float* loc, const float* wts, const float* grad_out,
+                        double* grad_feat, double* grad_loc, double* grad_wts, int B, int F,
+                        int C, int A, int Pts, int cams, int scales, int G) {
+    for (size_t i = 0; i < (size_t)B * F * C; ++i) grad_feat[i] = 0.0;
+    for (size_t i = 0; i < (size_t)B * A * Pts * cams * 2; ++i) grad_loc[i] = 0.0;
+    for (int b = 0; b < B; ++b)
+        for (int a = 0; a < A; ++a)
+            for (int pt = 0; pt < Pts; ++pt)
+                for (int cam = 0; cam < cams; ++cam)
+                    for (int sc = 0; sc < scales; ++sc)
+                        da_sample(feat, shapes, starts, loc, wts, grad_out, 0, grad_feat,
+                                  grad_loc, grad_wts, b, a, pt, cam, sc, F, C, A, Pts, cams,
+                                  scales, G);
+}

@@ -44,6 +44,11 @@ def _load():
         lib.gka_oracle_forward.restype = None
         lib.gka_oracle_backward.argtypes = [f32, i32, i32, f32, f32, f32, f64, f64] + dims
         lib.gka_oracle_backward.restype = None
+        d8 = [ctypes.c_int] * 8
+        lib.da_oracle_forward.argtypes = [f32, i32, i32, f32, f32, f64] + d8
+        lib.da_oracle_forward.restype = None
+        lib.da_oracle_backward.argtypes = [f32, i32, i32, f32, f32, f32, f64, f64, f64] + d8
+        lib.da_oracle_backward.restype = None
         lib.msda_oracle_kink_distance.argtypes = [i32, f32, f64] + [ctypes.c_int] * 5
         lib.msda_oracle_kink_distance.restype = None
         lib.msda_oracle_set_threads.argtypes = [ctypes.c_int]
@@ -124,3 +129,36 @@ def gka_backward(value, shapes, starts, loc, attn, grad_out):
     ga = np.empty(attn.shape, dtype=np.float64)
     _load().gka_oracle_backward(value, shapes, starts, loc, attn, grad_out, gv, ga, *dims)
     return gv, ga
+
+
+def _da_prep(feat, shapes, starts, loc, wts):
+    feat = np.ascontiguousarray(feat, dtype=np.float32)
+    loc = np.ascontiguousarray(loc, dtype=np.float32)
+    wts = np.ascontiguousarray(wts, dtype=np.float32)
+    shapes = np.ascontiguousarray(shapes, dtype=np.int32)
+    starts = np.ascontiguousarray(starts, dtype=np.int32)
+    B, F, C = feat.shape
+    _, A, Pts, cams, scales, G = wts.shape
+    if loc.shape != (B, A, Pts, cams, 2) or shapes.shape != (cams, scales, 2) or \
+            starts.shape != (cams, scales) or C % G != 0:
+        raise ValueError("inconsistent deformable-aggregation operand shapes")
+    return feat, shapes, starts, loc, wts, (B, F, C, A, Pts, cams, scales, G)
+
+
+def da_forward(feat, shapes, starts, loc, wts):
+    """Deformable aggregation, out[B, A, C] in float64."""
+    feat, shapes, starts, loc, wts, dims = _da_prep(feat, shapes, starts, loc, wts)
+    out = np.empty((dims[0], dims[3], dims[2]), dtype=np.float64)
+    _load().da_oracle_forward(feat, shapes, starts, loc, wts, out, *dims)
+    return out
+
+
+def da_backward(feat, shapes, starts, loc, wts, grad_out):
+    """(grad_feat, grad_loc, grad_wts) in float64."""
+    feat, shapes, starts, loc, wts, dims = _da_prep(feat, shapes, starts, loc, wts)
+    grad_out = np.ascontiguousarray(grad_out, dtype=np.float32).reshape(dims[0], dims[3], dims[2])
+    gf = np.empty(feat.shape, dtype=np.float64)
+    gl = np.empty(loc.shape, dtype=np.float64)
+    gw = np.empty(wts.shape, dtype=np.float64)
+    _load().da_oracle_backward(feat, shapes, starts, loc, wts, grad_out, gf, gl, gw, *dims)
+    return gf, gl, gw

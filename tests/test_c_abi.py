@@ -13,7 +13,7 @@ HEADER = os.path.join(ROOT, "include", "msda_sm100.h")
 def declared_functions():
     text = open(HEADER).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b((?:msda|gka)_sm100_\w+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b((?:msda|gka|da)_sm100_\w+)\s*\(", text)))
 
 
 def test_every_declared_symbol_is_exported():
