@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--op", default="msda", choices=["msda", "gka", "da"],
+                    help="msda (the headline path, default); gka / da: the sibling operators "
+                         "geometric kernel attention / deformable aggregation on one GPU")
     ap.add_argument("--workload", default="bevformer_sca")
     ap.add_argument("--dtype", default="float32", choices=["float32", "float16", "bfloat16"])
     ap.add_argument("--shard", default="batch", choices=["batch", "query"])
@@ -469,9 +472,149 @@ def run_e2e(sdk, host_sets, shapes_i32, starts_i32, dev, dtype, world, query_sha
             "overlap": "3 streams, 3 slots: upload, kernels and download of neighbouring steps overlap"}
 
 
+# --------------------------------------------------------------------------- sibling operators
+def run_sibling(args):
+    """One-GPU fwd+bwd timing of geometric kernel attention (--op gka) or deformable
+    aggregation (--op da) through the C ABI, operands in HBM, with the same roofline
+    accounting (every operand once, every result once) and a CPU-oracle baseline."""
+    import numpy as np
+    import torch
+    from drivingsdk_b200 import capi
+    from oracle import msda_oracle
+
+    lib = capi.load()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(4321)
+    stream = torch.cuda.current_stream()
+    if args.op == "gka":
+        # MapTR-style call of the reference's unit test (tests/torch/
+        # test_geometric_kernel_attention.py:109): 24 views, 7156 queries, 4 heads x 64
+        # channels, one 15x25 level, 15 points per query
+        B, Q, H, D, L, P, hw = 24, 7156, 4, 64, 1, 15, (15, 25)
+        K = hw[0] * hw[1] * L
+        value = (torch.rand(B, K, H, D, generator=g) * 3).to(dev)
+        loc = torch.empty(B, Q, H, L, P, 2)
+        loc[..., 0] = torch.randint(-3, hw[1] + 3, (B, Q, H, L, P), generator=g).float()
+        loc[..., 1] = torch.randint(-3, hw[0] + 3, (B, Q, H, L, P), generator=g).float()
+        loc = loc.to(dev)
+        attn = torch.rand(B, Q, H, L, P, generator=g).to(dev)
+        go = (torch.rand(B, Q, H * D, generator=g) * 10).to(dev)
+        shapes = torch.tensor([list(hw)] * L, dtype=torch.int32, device=dev)
+        starts = torch.arange(L, dtype=torch.int32, device=dev) * (hw[0] * hw[1])
+        out = torch.empty(B, Q, H * D, device=dev)
+        gv, ga = torch.empty_like(value), torch.empty_like(attn)
+        dims = (B, K, H, D, L, Q, P)
+        samples = B
+        nv, ns, no = value.numel(), attn.numel(), out.numel()
+        fwd_bytes, bwd_bytes = 4 * (nv + 3 * ns + no), 4 * (2 * nv + 4 * ns + no)
+
+        def fwd():
+            capi.check(lib.gka_sm100_forward(value.data_ptr(), shapes.data_ptr(), starts.data_ptr(),
+                                             loc.data_ptr(), attn.data_ptr(), out.data_ptr(), *dims,
+                                             capi.F32, stream.cuda_stream), "gka fwd")
+
+        def bwd():
+            capi.check(lib.gka_sm100_backward_ws(
+                value.data_ptr(), shapes.data_ptr(), starts.data_ptr(), loc.data_ptr(),
+                attn.data_ptr(), go.data_ptr(), gv.data_ptr(), ga.data_ptr(), None, 0, *dims,
+                capi.F32, stream.cuda_stream), "gka bwd")
+
+        def cpu_once(nb):
+            n = lambda t: t[:nb].cpu().numpy()
+            msda_oracle.gka_forward(n(value), shapes.cpu().numpy(), starts.cpu().numpy(), n(loc), n(attn))
+            msda_oracle.gka_backward(n(value), shapes.cpu().numpy(), starts.cpu().numpy(), n(loc),
+                                     n(attn), n(go))
+        config = {"workload": "gka_maptr_test_shape", "B": B, "Q": Q, "H": H, "D": D, "K": K,
+                  "L": L, "P": P}
+    else:
+        # Sparse4D-style call: 6 cameras x 4 scales (64x176 ... 8x22), 256 channels in 8 groups,
+        # 900 anchors x 13 points, batch 6; locations uniform in (0, 1): every sample counts
+        B, C, A, Pts, G = 6, 256, 900, 13, 8
+        maps = [[(64, 176), (32, 88), (16, 44), (8, 22)]] * 6
+        cams, scales = len(maps), len(maps[0])
+        shapes_np = np.array(maps, dtype=np.int32).reshape(cams, scales, 2)
+        sizes = (shapes_np[..., 0] * shapes_np[..., 1]).reshape(-1)
+        starts_np = np.concatenate([[0], np.cumsum(sizes)[:-1]]).astype(np.int32).reshape(cams, scales)
+        F = int(sizes.sum())
+        feat = torch.randn(B, F, C, generator=g).to(dev)
+        loc = torch.rand(B, A, Pts, cams, 2, generator=g).clamp_(1e-4, 1 - 1e-4).to(dev)
+        wts = torch.rand(B, A, Pts, cams, scales, G, generator=g).to(dev)
+        go = torch.randn(B, A, C, generator=g).to(dev)
+        shapes = torch.from_numpy(shapes_np).to(dev)
+        starts = torch.from_numpy(starts_np).to(dev)
+        out = torch.empty(B, A, C, device=dev)
+        gf, gl, gw = torch.empty_like(feat), torch.empty_like(loc), torch.empty_like(wts)
+        dims = (B, F, C, A, Pts, cams, scales, G)
+        samples = B
+        nf, nl, nw, no = feat.numel(), loc.numel(), wts.numel(), out.numel()
+        fwd_bytes, bwd_bytes = 4 * (nf + nl + nw + no), 4 * (2 * nf + 2 * nl + 2 * nw + no)
+
+        def fwd():
+            capi.check(lib.da_sm100_forward(feat.data_ptr(), shapes.data_ptr(), starts.data_ptr(),
+                                            loc.data_ptr(), wts.data_ptr(), out.data_ptr(), *dims,
+                                            stream.cuda_stream), "da fwd")
+
+        def bwd():
+            capi.check(lib.da_sm100_backward(feat.data_ptr(), shapes.data_ptr(), starts.data_ptr(),
+                                             loc.data_ptr(), wts.data_ptr(), go.data_ptr(),
+                                             gf.data_ptr(), gl.data_ptr(), gw.data_ptr(), *dims,
+                                             stream.cuda_stream), "da bwd")
+
+        def cpu_once(nb):
+            n = lambda t: t[:nb].cpu().numpy()
+            msda_oracle.da_forward(n(feat), shapes_np, starts_np, n(loc), n(wts))
+            msda_oracle.da_backward(n(feat), shapes_np, starts_np, n(loc), n(wts), n(go))
+        config = {"workload": "da_sparse4d_shape", "B": B, "C": C, "anchors": A, "pts": Pts,
+                  "cams": cams, "scales": scales, "groups": G, "F": F}
+
+    for _ in range(max(3, args.warmup)):
+        fwd(); bwd()
+    torch.cuda.synchronize()
+    K_steps = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K_steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = lib.msda_sm100_launch_count()
+    e0.record(stream)
+    for i in range(K_steps):
+        ev[i][0].record(stream); fwd(); ev[i][1].record(stream); bwd(); ev[i][2].record(stream)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / K_steps
+    fwd_ms = sum(q[0].elapsed_time(q[1]) for q in ev) / K_steps
+    bwd_ms = sum(q[1].elapsed_time(q[2]) for q in ev) / K_steps
+    peak, peak_kind = load_peaks()
+    line = {
+        "metric": f"{args.op}_fwd_bwd_samples_per_s", "value": samples / (ms * 1e-3), "unit": UNIT,
+        "n_gpus": 1, "steps": K_steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": config,
+        "roofline": {"bound": "hbm", "kernel": f"{args.op} backward call (zero-fill + kernel)",
+                     "achieved": bwd_bytes / (bwd_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": bwd_bytes / (bwd_ms * 1e-3) / 1e9 / peak, "traffic": None,
+                     "peak_kind": peak_kind, "algorithmic_bytes": bwd_bytes, "kernel_ms": bwd_ms,
+                     "forward": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
+                                 "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak,
+                                 "algorithmic_bytes": fwd_bytes, "kernel_ms": fwd_ms},
+                     "step": {"frac": (fwd_bytes + bwd_bytes) / (ms * 1e-3) / 1e9 / peak,
+                              "algorithmic_bytes": fwd_bytes + bwd_bytes}},
+        "gpu_launches": int(lib.msda_sm100_launch_count() - launches0),
+    }
+    if not args.no_cpu_baseline:
+        msda_oracle.set_threads(os.cpu_count() or 1)
+        t0 = time.perf_counter()
+        cpu_once(1)
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": 1.0 / dt, "unit": UNIT, "cores": 1, "kind": "port",
+                                "sample": "1 batch entry, fwd+bwd, C oracle (float64, one thread)"}
+    print(json.dumps(line))
+
+
 def main():
     args = parse_args()
-    if args.impl == "reference":
+    if args.op != "msda":
+        run_sibling(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_native(args)

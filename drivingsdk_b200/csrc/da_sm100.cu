@@ -26,6 +26,7 @@
 
 #include "../../include/msda_sm100.h"
 #include "msda_common.cuh"
+#include "msda_launch.h"
 
 namespace msda {
 
@@ -453,6 +454,7 @@ int da_sm100_forward(const void* feat, const int32_t* spatial_shape, const int32
         t_da_cuda_error = static_cast<int>(e);
         return MSDA_ERR_CUDA;
     }
+    msda::count_launches(1);
     return MSDA_OK;
 }
 
@@ -481,6 +483,7 @@ int da_sm100_backward(const void* feat, const int32_t* spatial_shape, const int3
         t_da_cuda_error = static_cast<int>(e);
         return MSDA_ERR_CUDA;
     }
+    msda::count_launches(1);
     return MSDA_OK;
 }
 

@@ -266,6 +266,10 @@ int forward_impl(const void* value, const int32_t* spatial_shapes,
 
 }  // namespace
 
+namespace msda {
+void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+}  // namespace msda
+
 extern "C" {
 
 int msda_sm100_forward(const void* value, const int32_t* spatial_shapes,

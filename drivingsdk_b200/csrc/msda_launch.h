@@ -57,6 +57,9 @@ cudaError_t launch_gka_forward(const Params& p, int dtype, const RowPlan& rp,
 cudaError_t launch_gka_backward(const Params& p, int dtype, int acc_f32, const RowPlan& rp,
                                 const LaunchShape& ls, cudaStream_t stream);
 
+// Adds to the library-wide kernel launch counter (msda_sm100_launch_count).
+void count_launches(int n);
+
 // out[i] = (T)acc[i] for n elements; dtype 1 = fp16, 2 = bf16.
 cudaError_t launch_downcast(const float* acc, void* out, long long n, int dtype,
                             cudaStream_t stream);
