@@ -384,7 +384,7 @@ def run_native(args):
 
 # ncu dram__bytes_read.sum + dram__bytes_write.sum of one backward-kernel launch, per
 # (workload, dtype); from the captures summarised under profiles/.
-TRAFFIC_BYTES = {("bevformer_sca", "float32"): 620_674_304}
+TRAFFIC_BYTES = {("bevformer_sca", "float32"): 626_346_752}
 
 
 def run_e2e(sdk, host_sets, shapes_i32, starts_i32, dev, dtype, world, query_shard, steps,
