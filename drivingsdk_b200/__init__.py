@@ -11,6 +11,9 @@ Public surface, same names as the reference package exports for this path
     geometric_kernel_attention(value, spatial_shapes, level_start_index, sampling_locations,
                                attention_weights) -> Tensor   (nearest-pixel sibling operator,
                                mx_driving/ops/geometric_kernel_attention.py:27-54)
+    multi_scale_deformable_attn_fused(value, shapes, level_start, reference_points,
+                               sampling_offsets, attention_logits) -> Tensor   (extension: the
+                               operator with its callers' softmax and location arithmetic inside)
     deformable_aggregation / npu_deformable_aggregation(mc_ms_feat, spatial_shape,
                                scale_start_index, sampling_location, weights) -> Tensor
                                (mx_driving/ops/npu_deformable_aggregation.py:9-88)
@@ -29,9 +32,10 @@ _OP_NAMES = (
     "npu_multi_scale_deformable_attn_function",
 )
 _GKA_NAMES = ("geometric_kernel_attention", "GeometricKernelAttentionFunc")
+_FUSED_NAMES = ("multi_scale_deformable_attn_fused", "MultiScaleDeformableAttnFusedFunction")
 _DA_NAMES = ("npu_deformable_aggregation", "deformable_aggregation", "AdsDeformableAggregation")
 
-__all__ = (list(_OP_NAMES) + list(_GKA_NAMES) + list(_DA_NAMES)
+__all__ = (list(_OP_NAMES) + list(_FUSED_NAMES) + list(_GKA_NAMES) + list(_DA_NAMES)
            + ["patcher", "default_patcher", "dist"])
 
 
@@ -41,6 +45,9 @@ def __getattr__(name):
         return getattr(mod, name)
     if name in _GKA_NAMES:
         mod = importlib.import_module(__name__ + ".ops.geometric_kernel_attention")
+        return getattr(mod, name)
+    if name in _FUSED_NAMES:
+        mod = importlib.import_module(__name__ + ".ops.msda_fused")
         return getattr(mod, name)
     if name in _DA_NAMES:
         mod = importlib.import_module(__name__ + ".ops.npu_deformable_aggregation")

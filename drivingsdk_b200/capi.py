@@ -23,6 +23,9 @@ SIGNATURES = {
     "msda_sm100_backward_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "msda_sm100_backward_ws": (_i, [_vp, _ip, _ip, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz]
                                + _DIMS7 + [_i, _vp]),
+    "msda_sm100_fused_forward": (_i, [_vp, _ip, _ip, _vp, _vp, _vp, _vp] + _DIMS7 + [_i, _vp]),
+    "msda_sm100_fused_backward_ws": (_i, [_vp, _ip, _ip, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                         _vp, _sz] + _DIMS7 + [_i, _vp]),
     "gka_sm100_forward": (_i, [_vp, _ip, _ip, _vp, _vp, _vp] + _DIMS7 + [_i, _vp]),
     "gka_sm100_backward_ws": (_i, [_vp, _ip, _ip, _vp, _vp, _vp, _vp, _vp, _vp, _sz] + _DIMS7
                               + [_i, _vp]),

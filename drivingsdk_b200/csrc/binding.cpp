@@ -405,6 +405,88 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> deformable_aggregation_backward(
                            grad_wts.to(wts_in.scalar_type()));
 }
 
+// ---------------------------------------------------------------------------
+// fused MSDA: reference points + sampling offsets + attention logits in, output out; the
+// location arithmetic and the softmax of mmcv's MultiScaleDeformableAttention.forward happen
+// inside the kernels. No counterpart in the reference's extension.
+// ---------------------------------------------------------------------------
+namespace {
+
+Dims check_fused_inputs(const at::Tensor& value, const at::Tensor& shapes,
+                        const at::Tensor& starts, const at::Tensor& ref, const at::Tensor& off,
+                        const at::Tensor& logits) {
+    const Dims d = check_inputs(value, shapes, starts, off, logits);
+    TORCH_CHECK(ref.is_cuda() && ref.scalar_type() == value.scalar_type(),
+                "reference_points must be a CUDA tensor of value's dtype");
+    TORCH_CHECK(ref.dim() == 4 && ref.size(0) == d.B && ref.size(1) == d.Q && ref.size(2) == d.L &&
+                    ref.size(3) == 2,
+                "reference_points must be [bs, num_queries, num_levels, 2]");
+    TORCH_CHECK(static_cast<int64_t>(d.L) * d.P <= 32,
+                "the fused operator needs num_levels * num_points <= 32");
+    return d;
+}
+
+}  // namespace
+
+at::Tensor msda_fused_forward(const at::Tensor& value_in, const at::Tensor& shapes_in,
+                              const at::Tensor& starts_in, const at::Tensor& ref_in,
+                              const at::Tensor& off_in, const at::Tensor& logits_in) {
+    const Dims d = check_fused_inputs(value_in, shapes_in, starts_in, ref_in, off_in, logits_in);
+    const c10::cuda::CUDAGuard guard(value_in.device());
+    const at::Tensor value = value_in.contiguous();
+    const at::Tensor ref = ref_in.contiguous();
+    const at::Tensor off = off_in.contiguous();
+    const at::Tensor logits = logits_in.contiguous();
+    const at::Tensor shapes = shapes_in.contiguous();
+    const at::Tensor starts = starts_in.contiguous();
+    at::Tensor out = at::empty({d.B, d.Q, static_cast<int64_t>(d.H) * d.D}, value.options());
+    if (out.numel() == 0) return out;
+    const int rc = msda_sm100_fused_forward(
+        value.data_ptr(), shapes.data_ptr<int32_t>(), starts.data_ptr<int32_t>(), ref.data_ptr(),
+        off.data_ptr(), logits.data_ptr(), out.data_ptr(), d.B, d.K, d.H, d.D, d.L, d.Q, d.P,
+        dtype_code(value.scalar_type()), at::cuda::getCurrentCUDAStream().stream());
+    raise_on_error(rc, "msda_fused_forward");
+    return out;
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> msda_fused_backward(
+    const at::Tensor& value_in, const at::Tensor& shapes_in, const at::Tensor& starts_in,
+    const at::Tensor& ref_in, const at::Tensor& off_in, const at::Tensor& logits_in,
+    const at::Tensor& grad_out_in) {
+    const Dims d = check_fused_inputs(value_in, shapes_in, starts_in, ref_in, off_in, logits_in);
+    TORCH_CHECK(grad_out_in.is_cuda() && is_float_kind(grad_out_in.scalar_type()) &&
+                    grad_out_in.numel() == static_cast<int64_t>(d.B) * d.Q * d.H * d.D,
+                "grad_output must be a CUDA tensor [bs, num_queries, num_heads * embed_dims]");
+    const c10::cuda::CUDAGuard guard(value_in.device());
+    const at::Tensor value = value_in.contiguous();
+    const at::Tensor ref = ref_in.contiguous();
+    const at::Tensor off = off_in.contiguous();
+    const at::Tensor logits = logits_in.contiguous();
+    const at::Tensor shapes = shapes_in.contiguous();
+    const at::Tensor starts = starts_in.contiguous();
+    const at::Tensor grad_out = grad_out_in.to(value.scalar_type()).contiguous();
+    at::Tensor grad_value = at::empty_like(value);
+    at::Tensor grad_off = at::empty_like(off);
+    at::Tensor grad_logits = at::empty_like(logits);
+    at::Tensor grad_ref = at::empty(ref.sizes(), ref.options().dtype(at::kFloat));
+    const int dt = dtype_code(value.scalar_type());
+    at::Tensor workspace;
+    void* ws_ptr = nullptr;
+    const size_t ws_bytes = msda_sm100_backward_workspace_bytes(d.B, d.K, d.H, d.D, dt);
+    if (ws_bytes > 0) {
+        workspace = at::empty({static_cast<int64_t>(ws_bytes / sizeof(float))},
+                              value.options().dtype(at::kFloat));
+        ws_ptr = workspace.data_ptr();
+    }
+    const int rc = msda_sm100_fused_backward_ws(
+        value.data_ptr(), shapes.data_ptr<int32_t>(), starts.data_ptr<int32_t>(), ref.data_ptr(),
+        off.data_ptr(), logits.data_ptr(), grad_out.data_ptr(), grad_value.data_ptr(),
+        grad_ref.data_ptr<float>(), grad_off.data_ptr(), grad_logits.data_ptr(), ws_ptr, ws_bytes,
+        d.B, d.K, d.H, d.D, d.L, d.Q, d.P, dt, at::cuda::getCurrentCUDAStream().stream());
+    raise_on_error(rc, "msda_fused_backward");
+    return std::make_tuple(grad_value, grad_ref.to(ref.scalar_type()), grad_off, grad_logits);
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "sm_100a multi-scale deformable attention (drop-in for mx_driving._C on this path)";
     m.def("multi_scale_deformable_attn", &multi_scale_deformable_attn,
@@ -420,6 +502,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("geometric_kernel_attention_backward", &geometric_kernel_attention_backward,
           "GKA backward: (value, spatial_shapes, level_start_index, sampling_locations, "
           "attention_weights, grad_output) -> (grad_value, grad_attn_weights)");
+    m.def("msda_fused_forward", &msda_fused_forward,
+          "fused MSDA forward: (value, spatial_shapes, level_start_index, reference_points, "
+          "sampling_offsets, attention_logits) -> output");
+    m.def("msda_fused_backward", &msda_fused_backward,
+          "fused MSDA backward -> (grad_value, grad_reference_points, grad_sampling_offsets, "
+          "grad_attention_logits)");
     m.def("npu_deformable_aggregation", &deformable_aggregation,
           "deformable aggregation forward: (mc_ms_feat, spatial_shape, scale_start_index, "
           "sampling_location, weights) -> output");

@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, 2) da_kernel(const __grid_cons
             uint4 rec01 = make_uint4(kNoRow, 0u, kNoRow, 0u);
             uint4 rec23 = rec01;
             SampleGeom geom;
-            geom.lw = geom.lh = geom.a = geom.wf = geom.hf = 0.f;
+            geom.lw = geom.lh = geom.a = geom.wf = geom.hf = geom.prob = 0.f;
             geom.valid = false;
             int pc = 0, scale = 0;
             if (active) {

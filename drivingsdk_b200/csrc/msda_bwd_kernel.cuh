@@ -23,9 +23,11 @@ constexpr int kPartBytes = ((kChunk * (4 * kPartMax + 1) * 4 + 15) / 16) * 16;
 #define MSDA_BWD_UNROLL 4
 #endif
 
-template <typename T, typename TG, int LPR, int NV, bool SCALAR, int CPS>
+template <typename T, typename TG, int LPR, int NV, bool SCALAR, int MODE>
 __global__ void __launch_bounds__(kThreadsPerCta, (SCALAR || NV > 1) ? 2 : MSDA_BWD_MIN_CTAS)
 msda_bwd_kernel(const __grid_constant__ Params p) {
+    constexpr int CPS = (MODE == kModeFused) ? 4 : MODE;   // rows (corners) per sample
+    constexpr bool FUSED = MODE == kModeFused;
     constexpr int VEC = SCALAR ? 1 : Elem<T>::kVec;
     constexpr int RPI = 32 / LPR;
     constexpr int PART = (LPR < kPartMax) ? LPR : kPartMax;  // partials per slot
@@ -105,7 +107,8 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
             SampleGeom geom;
             long long gi;
             const bool active =
-                phase1<T, CPS>(p, lv, chunk, lane, item, ntask_here, sloc, sattn, s_slot, geom, gi);
+                phase1<T, CPS, FUSED>(p, lv, chunk, lane, item, ntask_here, sloc, sattn, s_slot,
+                                      geom, gi);
             __syncwarp();
 
             // ---- phase 2: lane = (row slot, piece of row) -----------------------
@@ -250,32 +253,84 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
             __syncwarp();
 
             // ---- phase 3: lane = sample -----------------------------------------
-            if (active) {
-                float S[CPS];
+            if constexpr (!FUSED) {
+                if (active) {
+                    float S[CPS];
 #pragma unroll
-                for (int c = 0; c < CPS; ++c) {
-                    float acc = 0.f;
+                    for (int c = 0; c < CPS; ++c) {
+                        float acc = 0.f;
 #pragma unroll
-                    for (int q = 0; q < PART; ++q) acc += s_part[lane * SSTRIDE + c * PART + q];
-                    S[c] = acc;
-                }
-                if constexpr (CPS == 4) {
-                    float g_attn = 0.f, g_x = 0.f, g_y = 0.f;
-                    if (geom.valid) {
-                        // a corner that does not exist left a zero partial sum behind
-                        const float lw = geom.lw, lh = geom.lh;
-                        const float hw = 1.f - lw, hh = 1.f - lh;
-                        g_attn =
-                            hh * hw * S[0] + hh * lw * S[1] + lh * hw * S[2] + lh * lw * S[3];
-                        g_x = geom.wf * geom.a * (hh * (S[1] - S[0]) + lh * (S[3] - S[2]));
-                        g_y = geom.hf * geom.a * (hw * (S[2] - S[0]) + lw * (S[3] - S[1]));
+                        for (int q = 0; q < PART; ++q)
+                            acc += s_part[lane * SSTRIDE + c * PART + q];
+                        S[c] = acc;
                     }
-                    store_pair(static_cast<T*>(p.grad_loc) + 2 * gi, g_x, g_y);
-                    static_cast<T*>(p.grad_attn)[gi] = Elem<T>::from_f(g_attn);
-                } else {
-                    // nearest-pixel operator: d out / d attention = <value row, grad_out>;
-                    // the integer locations have no gradient
-                    static_cast<T*>(p.grad_attn)[gi] = Elem<T>::from_f(S[0]);
+                    if constexpr (CPS == 4) {
+                        float g_attn = 0.f, g_x = 0.f, g_y = 0.f;
+                        if (geom.valid) {
+                            // a corner that does not exist left a zero partial sum behind
+                            const float lw = geom.lw, lh = geom.lh;
+                            const float hw = 1.f - lw, hh = 1.f - lh;
+                            g_attn = hh * hw * S[0] + hh * lw * S[1] + lh * hw * S[2] +
+                                     lh * lw * S[3];
+                            g_x = geom.wf * geom.a * (hh * (S[1] - S[0]) + lh * (S[3] - S[2]));
+                            g_y = geom.hf * geom.a * (hw * (S[2] - S[0]) + lw * (S[3] - S[1]));
+                        }
+                        store_pair(static_cast<T*>(p.grad_loc) + 2 * gi, g_x, g_y);
+                        static_cast<T*>(p.grad_attn)[gi] = Elem<T>::from_f(g_attn);
+                    } else {
+                        // nearest-pixel operator: d out / d attention = <value row, grad_out>;
+                        // the integer locations have no gradient
+                        static_cast<T*>(p.grad_attn)[gi] = Elem<T>::from_f(S[0]);
+                    }
+                }
+            } else {
+                // Fused variant: chain the sample gradients through
+                //   location = reference point + offset / (W, H)   and   weight = softmax(logits).
+                float g_attn = 0.f, g_x = 0.f, g_y = 0.f;
+                if (active && geom.valid) {
+                    float S[4];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float acc = 0.f;
+#pragma unroll
+                        for (int q = 0; q < PART; ++q)
+                            acc += s_part[lane * SSTRIDE + c * PART + q];
+                        S[c] = acc;
+                    }
+                    const float lw = geom.lw, lh = geom.lh;
+                    const float hw = 1.f - lw, hh = 1.f - lh;
+                    g_attn = hh * hw * S[0] + hh * lw * S[1] + lh * hw * S[2] + lh * lw * S[3];
+                    g_x = geom.wf * geom.a * (hh * (S[1] - S[0]) + lh * (S[3] - S[2]));
+                    g_y = geom.hf * geom.a * (hw * (S[2] - S[0]) + lw * (S[3] - S[1]));
+                }
+                int tl, s;
+                lane_sample_index(p, chunk, lane, tl, s);
+                float* scratch = fused_scratch(s_slot);
+                const float prob = active ? geom.prob : 0.f;
+                // softmax backward: d logit_s = p_s * (d a_s - sum_j p_j * d a_j)
+                const float dot = task_sum(p, prob * g_attn, lane, tl, scratch);
+                __syncwarp();
+                scratch[32 + lane] = g_x;
+                scratch[64 + lane] = g_y;
+                __syncwarp();
+                if (active) {
+                    store_pair(static_cast<T*>(p.grad_loc) + 2 * gi, g_x / geom.wf,
+                               g_y / geom.hf);
+                    static_cast<T*>(p.grad_attn)[gi] = Elem<T>::from_f(prob * (g_attn - dot));
+                    if (s % p.P == 0) {
+                        // first point of a level: the reference point of (b, q, level) gets
+                        // the sum over this head's points (heads meet in the atomic)
+                        float sx = 0.f, sy = 0.f;
+                        for (int i = 0; i < p.P; ++i) {
+                            sx += scratch[32 + lane + i];
+                            sy += scratch[64 + lane + i];
+                        }
+                        const uint32_t t = static_cast<uint32_t>(item) * TPC + tl;
+                        const uint32_t bq = fd_div(t, p.fd_h);
+                        float* gr = p.grad_ref + (static_cast<size_t>(bq) * p.L + lv.level0) * 2;
+                        atomicAdd(gr, sx);
+                        atomicAdd(gr + 1, sy);
+                    }
                 }
             }
             __syncwarp();
@@ -286,10 +341,10 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
 // ---------------------------------------------------------------------------
 // launch table
 // ---------------------------------------------------------------------------
-template <typename T, typename TG, int LPR, int NV, bool SCALAR, int CPS>
+template <typename T, typename TG, int LPR, int NV, bool SCALAR, int MODE>
 static cudaError_t launch_bwd_inst(const Params& p, const LaunchShape& ls, size_t smem,
                                    cudaStream_t stream) {
-    auto kern = msda_bwd_kernel<T, TG, LPR, NV, SCALAR, CPS>;
+    auto kern = msda_bwd_kernel<T, TG, LPR, NV, SCALAR, MODE>;
     if (smem > 48 * 1024) {
         cudaError_t e =
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -302,39 +357,39 @@ static cudaError_t launch_bwd_inst(const Params& p, const LaunchShape& ls, size_
     return cudaGetLastError();
 }
 
-template <typename T, typename TG, int CPS>
+template <typename T, typename TG, int MODE>
 static cudaError_t launch_bwd_typed(const Params& p, const RowPlan& rp, const LaunchShape& ls, size_t smem,
                                     cudaStream_t stream) {
-    if (rp.scalar) return launch_bwd_inst<T, TG, 32, 8, true, CPS>(p, ls, smem, stream);
+    if (rp.scalar) return launch_bwd_inst<T, TG, 32, 8, true, MODE>(p, ls, smem, stream);
     switch (rp.lpr * 100 + rp.nv) {
-        case 101: return launch_bwd_inst<T, TG, 1, 1, false, CPS>(p, ls, smem, stream);
-        case 201: return launch_bwd_inst<T, TG, 2, 1, false, CPS>(p, ls, smem, stream);
-        case 401: return launch_bwd_inst<T, TG, 4, 1, false, CPS>(p, ls, smem, stream);
-        case 801: return launch_bwd_inst<T, TG, 8, 1, false, CPS>(p, ls, smem, stream);
-        case 1601: return launch_bwd_inst<T, TG, 16, 1, false, CPS>(p, ls, smem, stream);
-        case 3201: return launch_bwd_inst<T, TG, 32, 1, false, CPS>(p, ls, smem, stream);
+        case 101: return launch_bwd_inst<T, TG, 1, 1, false, MODE>(p, ls, smem, stream);
+        case 201: return launch_bwd_inst<T, TG, 2, 1, false, MODE>(p, ls, smem, stream);
+        case 401: return launch_bwd_inst<T, TG, 4, 1, false, MODE>(p, ls, smem, stream);
+        case 801: return launch_bwd_inst<T, TG, 8, 1, false, MODE>(p, ls, smem, stream);
+        case 1601: return launch_bwd_inst<T, TG, 16, 1, false, MODE>(p, ls, smem, stream);
+        case 3201: return launch_bwd_inst<T, TG, 32, 1, false, MODE>(p, ls, smem, stream);
         case 3202:
             if constexpr (sizeof(T) == 4) {
-                return launch_bwd_inst<T, TG, 32, 2, false, CPS>(p, ls, smem, stream);
+                return launch_bwd_inst<T, TG, 32, 2, false, MODE>(p, ls, smem, stream);
             }
             return cudaErrorInvalidValue;
         default: return cudaErrorInvalidValue;
     }
 }
 
-template <int CPS>
+template <int MODE>
 static cudaError_t launch_backward_cps(const Params& p, int dtype, int acc_f32, const RowPlan& rp,
                                        const LaunchShape& ls, cudaStream_t stream) {
     const size_t smem = static_cast<size_t>(p.warp_smem) * kWarpsPerCta;
     switch (dtype) {
-        case 0: return launch_bwd_typed<float, float, CPS>(p, rp, ls, smem, stream);
+        case 0: return launch_bwd_typed<float, float, MODE>(p, rp, ls, smem, stream);
         case 1:
-            return acc_f32 ? launch_bwd_typed<__half, float, CPS>(p, rp, ls, smem, stream)
-                           : launch_bwd_typed<__half, __half, CPS>(p, rp, ls, smem, stream);
+            return acc_f32 ? launch_bwd_typed<__half, float, MODE>(p, rp, ls, smem, stream)
+                           : launch_bwd_typed<__half, __half, MODE>(p, rp, ls, smem, stream);
         case 2:
             return acc_f32
-                       ? launch_bwd_typed<__nv_bfloat16, float, CPS>(p, rp, ls, smem, stream)
-                       : launch_bwd_typed<__nv_bfloat16, __nv_bfloat16, CPS>(p, rp, ls, smem,
+                       ? launch_bwd_typed<__nv_bfloat16, float, MODE>(p, rp, ls, smem, stream)
+                       : launch_bwd_typed<__nv_bfloat16, __nv_bfloat16, MODE>(p, rp, ls, smem,
                                                                              stream);
         default: return cudaErrorInvalidValue;
     }

@@ -15,6 +15,7 @@ using msda::Params;
 using msda::RowPlan;
 
 constexpr int kAbiVersion = 1;
+constexpr int kBilinear = 0, kNearest = 1, kFused = 2;
 constexpr int kMaxDevices = 64;
 
 __device__ int g_status_word;
@@ -168,14 +169,17 @@ int fill_common(Params& p, const DeviceInfo* dev, const void* value, const int32
 
 int backward_impl(const void* value, const int32_t* shapes, const int32_t* starts, const void* loc,
                   const void* attn, const void* grad_out, void* grad_value, void* grad_loc,
-                  void* grad_attn, void* workspace, size_t workspace_bytes, bool use_ws,
-                  bool nearest, int B, int K, int H, int D, int L, int Q, int P, int dtype,
-                  void* stream_v) {
-    // nearest == true: geometric kernel attention (one clamped integer pixel per sample, no
-    // location gradient); false: bilinear MSDA
+                  void* grad_attn, void* workspace, size_t workspace_bytes, bool use_ws, int mode,
+                  const void* ref, float* grad_ref, int B, int K, int H, int D, int L, int Q,
+                  int P, int dtype, void* stream_v) {
+    // mode: kBilinear = MSDA; kNearest = geometric kernel attention (one clamped integer pixel
+    // per sample, no location gradient); kFused = MSDA fed by reference points, offsets (in
+    // `loc`) and logits (in `attn`)
+    const bool nearest = mode == kNearest;
     if (!value || !shapes || !starts || !loc || !attn || !grad_out || !grad_value || !grad_attn ||
-        (!nearest && !grad_loc))
+        (!nearest && !grad_loc) || (mode == kFused && (!ref || !grad_ref)))
         return MSDA_ERR_NULL;
+    if (mode == kFused && static_cast<long long>(L) * P > 32) return MSDA_ERR_LIMIT;
     int rc = check_dims(B, K, H, D, L, Q, P, dtype);
     if (rc != MSDA_OK) return rc;
     const DeviceInfo* dev = nullptr;
@@ -217,8 +221,18 @@ int backward_impl(const void* value, const int32_t* shapes, const int32_t* start
     if (ce != cudaSuccess) return fail_cuda(ce);
     prof_record(2, stream);
     const msda::LaunchShape shape{dev->sm_count, g_tune_cps_bwd.load()};
-    ce = nearest ? msda::launch_gka_backward(p, dtype, acc_f32 ? 1 : 0, rp, shape, stream)
-                 : msda::launch_backward(p, dtype, acc_f32 ? 1 : 0, rp, shape, stream);
+    if (mode == kFused) {
+        p.ref = ref;
+        p.grad_ref = grad_ref;
+        ce = cudaMemsetAsync(grad_ref, 0, static_cast<size_t>(B) * Q * L * 2 * sizeof(float),
+                             stream);
+        if (ce != cudaSuccess) return fail_cuda(ce);
+        ce = msda::launch_fused_backward(p, dtype, acc_f32 ? 1 : 0, rp, shape, stream);
+    } else if (nearest) {
+        ce = msda::launch_gka_backward(p, dtype, acc_f32 ? 1 : 0, rp, shape, stream);
+    } else {
+        ce = msda::launch_backward(p, dtype, acc_f32 ? 1 : 0, rp, shape, stream);
+    }
     prof_record(3, stream);
     if (ce != cudaSuccess) return fail_cuda(ce);
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -232,8 +246,10 @@ int backward_impl(const void* value, const int32_t* shapes, const int32_t* start
 
 int forward_impl(const void* value, const int32_t* spatial_shapes,
                  const int32_t* level_start_index, const void* sampling_locations,
-                 const void* attention_weights, void* output, bool nearest, int B, int K, int H,
-                 int D, int L, int Q, int P, int dtype, void* stream_v) {
+                 const void* attention_weights, void* output, int mode, const void* ref, int B,
+                 int K, int H, int D, int L, int Q, int P, int dtype, void* stream_v) {
+    if (mode == kFused && (!ref || static_cast<long long>(L) * P > 32))
+        return ref ? MSDA_ERR_LIMIT : MSDA_ERR_NULL;
     if (!value || !spatial_shapes || !level_start_index || !sampling_locations ||
         !attention_weights || !output)
         return MSDA_ERR_NULL;
@@ -256,8 +272,10 @@ int forward_impl(const void* value, const int32_t* spatial_shapes,
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     prof_record(0, stream);
     const msda::LaunchShape shape{dev->sm_count, g_tune_cps_fwd.load()};
-    cudaError_t ce = nearest ? msda::launch_gka_forward(p, dtype, rp, shape, stream)
-                             : msda::launch_forward(p, dtype, rp, shape, stream);
+    p.ref = ref;
+    cudaError_t ce = mode == kFused     ? msda::launch_fused_forward(p, dtype, rp, shape, stream)
+                     : mode == kNearest ? msda::launch_gka_forward(p, dtype, rp, shape, stream)
+                                        : msda::launch_forward(p, dtype, rp, shape, stream);
     prof_record(1, stream);
     if (ce != cudaSuccess) return fail_cuda(ce);
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -277,7 +295,8 @@ int msda_sm100_forward(const void* value, const int32_t* spatial_shapes,
                        const void* attention_weights, void* output, int B, int K, int H, int D,
                        int L, int Q, int P, int dtype, void* stream) {
     return forward_impl(value, spatial_shapes, level_start_index, sampling_locations,
-                        attention_weights, output, false, B, K, H, D, L, Q, P, dtype, stream);
+                        attention_weights, output, kBilinear, nullptr, B, K, H, D, L, Q, P, dtype,
+                        stream);
 }
 
 int gka_sm100_forward(const void* value, const int32_t* spatial_shapes,
@@ -285,7 +304,33 @@ int gka_sm100_forward(const void* value, const int32_t* spatial_shapes,
                       const void* attention_weights, void* output, int B, int K, int H, int D,
                       int L, int Q, int P, int dtype, void* stream) {
     return forward_impl(value, spatial_shapes, level_start_index, sampling_locations,
-                        attention_weights, output, true, B, K, H, D, L, Q, P, dtype, stream);
+                        attention_weights, output, kNearest, nullptr, B, K, H, D, L, Q, P, dtype,
+                        stream);
+}
+
+int msda_sm100_fused_forward(const void* value, const int32_t* spatial_shapes,
+                             const int32_t* level_start_index, const void* reference_points,
+                             const void* sampling_offsets, const void* attention_logits,
+                             void* output, int B, int K, int H, int D, int L, int Q, int P,
+                             int dtype, void* stream) {
+    return forward_impl(value, spatial_shapes, level_start_index, sampling_offsets,
+                        attention_logits, output, kFused, reference_points, B, K, H, D, L, Q, P,
+                        dtype, stream);
+}
+
+int msda_sm100_fused_backward_ws(const void* value, const int32_t* spatial_shapes,
+                                 const int32_t* level_start_index, const void* reference_points,
+                                 const void* sampling_offsets, const void* attention_logits,
+                                 const void* grad_output, void* grad_value,
+                                 float* grad_reference_points, void* grad_sampling_offsets,
+                                 void* grad_attention_logits, void* workspace,
+                                 size_t workspace_bytes, int B, int K, int H, int D, int L, int Q,
+                                 int P, int dtype, void* stream) {
+    return backward_impl(value, spatial_shapes, level_start_index, sampling_offsets,
+                         attention_logits, grad_output, grad_value, grad_sampling_offsets,
+                         grad_attention_logits, workspace, workspace_bytes, true, kFused,
+                         reference_points, grad_reference_points, B, K, H, D, L, Q, P, dtype,
+                         stream);
 }
 
 int gka_sm100_backward_ws(const void* value, const int32_t* spatial_shapes,
@@ -296,8 +341,8 @@ int gka_sm100_backward_ws(const void* value, const int32_t* spatial_shapes,
                           int dtype, void* stream) {
     return backward_impl(value, spatial_shapes, level_start_index, sampling_locations,
                          attention_weights, grad_output, grad_value, nullptr, grad_attn_weight,
-                         workspace, workspace_bytes, true, true, B, K, H, D, L, Q, P, dtype,
-                         stream);
+                         workspace, workspace_bytes, true, kNearest, nullptr, nullptr, B, K, H, D,
+                         L, Q, P, dtype, stream);
 }
 
 int msda_sm100_backward(const void* value, const int32_t* spatial_shapes,
@@ -307,7 +352,8 @@ int msda_sm100_backward(const void* value, const int32_t* spatial_shapes,
                         int D, int L, int Q, int P, int dtype, void* stream) {
     return backward_impl(value, spatial_shapes, level_start_index, sampling_locations,
                          attention_weights, grad_output, grad_value, grad_sampling_loc,
-                         grad_attn_weight, nullptr, 0, false, false, B, K, H, D, L, Q, P, dtype, stream);
+                         grad_attn_weight, nullptr, 0, false, kBilinear, nullptr, nullptr, B, K, H, D, L,
+                         Q, P, dtype, stream);
 }
 
 size_t msda_sm100_backward_workspace_bytes(int B, int K, int H, int D, int dtype) {
@@ -323,8 +369,8 @@ int msda_sm100_backward_ws(const void* value, const int32_t* spatial_shapes,
                            int L, int Q, int P, int dtype, void* stream) {
     return backward_impl(value, spatial_shapes, level_start_index, sampling_locations,
                          attention_weights, grad_output, grad_value, grad_sampling_loc,
-                         grad_attn_weight, workspace, workspace_bytes, true, false, B, K, H, D, L, Q,
-                         P, dtype, stream);
+                         grad_attn_weight, workspace, workspace_bytes, true, kBilinear, nullptr, nullptr,
+                         B, K, H, D, L, Q, P, dtype, stream);
 }
 
 size_t msda_sm100_forward_bytes(int B, int K, int H, int D, int L, int Q, int P, int dtype) {

@@ -52,6 +52,12 @@ __device__ __forceinline__ uint32_t fd_div(uint32_t n, const FastDiv& f) {
     return static_cast<uint32_t>((static_cast<uint64_t>(n) * f.mul) >> f.shift);
 }
 
+// Kernel modes (template parameter): rows per sample, or the fused bilinear variant whose
+// phase 1 builds locations and weights from reference points, offsets and logits.
+constexpr int kModeBilinear = 4;
+constexpr int kModeNearest = 1;
+constexpr int kModeFused = 5;
+
 constexpr uint32_t kNoRow = 0xffffffffu;  // slot record of a corner that does not exist
 
 // Level geometry by value. A launch that received the shapes on the host puts
@@ -70,6 +76,10 @@ struct Params {
     const void* loc;     // [B, Q, H, L, P, 2]  (x, y) in [0, 1]
     const void* attn;    // [B, Q, H, L, P]
     void* out;           // [B, Q, H*D]
+    // fused variant: loc holds sampling offsets [B,Q,H,L,P,2], attn holds logits [B,Q,H,L,P],
+    // grad_loc / grad_attn receive their gradients, and
+    const void* ref;     // reference points [B, Q, L, 2]
+    float* grad_ref;     // [B, Q, L, 2] fp32, zero-filled by the caller of the kernel
     // backward operands
     const void* grad_out;  // [B, Q, H*D]
     void* grad_value;      // [B, K, H, D]; accumulation target (may be fp32 scratch)
@@ -295,6 +305,7 @@ struct SampleGeom {
     float lw, lh;  // fractional offsets inside the cell
     float a;       // attention weight (0 when the sample is dropped)
     float wf, hf;  // level width / height as floats
+    float prob;    // fused variant: the sample's softmax probability, kept for dropped samples too
     bool valid;
 };
 
@@ -347,6 +358,7 @@ __device__ __forceinline__ void sample_setup(float lx, float ly, float a, int Wl
     g.lw = valid ? lw : 0.f;
     g.lh = valid ? lh : 0.f;
     g.a = aa;
+    g.prob = a;
     g.wf = wf;
     g.hf = hf;
     g.valid = valid;
@@ -369,6 +381,7 @@ __device__ __forceinline__ void sample_setup_nearest(float lx, float ly, float a
     rec.y = __float_as_uint(a);
     g.lw = g.lh = 0.f;
     g.a = a;
+    g.prob = a;
     g.wf = static_cast<float>(Wl);
     g.hf = static_cast<float>(Hl);
     g.valid = true;

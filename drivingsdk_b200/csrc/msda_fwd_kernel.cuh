@@ -21,9 +21,11 @@
 
 namespace msda {
 
-template <typename T, int LPR, int NV, bool SCALAR, int CPS>
+template <typename T, int LPR, int NV, bool SCALAR, int MODE>
 __global__ void __launch_bounds__(kThreadsPerCta, (SCALAR || NV > 1) ? 2 : MSDA_FWD_MIN_CTAS)
 msda_fwd_kernel(const __grid_constant__ Params p) {
+    constexpr int CPS = (MODE == kModeFused) ? 4 : MODE;   // rows (corners) per sample
+    constexpr bool FUSED = MODE == kModeFused;
     constexpr int VEC = SCALAR ? 1 : Elem<T>::kVec;
     constexpr int RPI = 32 / LPR;                  // rows per warp instruction
     constexpr int UNROLL =
@@ -89,7 +91,8 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
             // ---- phase 1: lane = sample -----------------------------------------
             SampleGeom geom;
             long long gi;
-            phase1<T, CPS>(p, lv, chunk, lane, item, ntask_here, sloc, sattn, s_slot, geom, gi);
+            phase1<T, CPS, FUSED>(p, lv, chunk, lane, item, ntask_here, sloc, sattn, s_slot, geom,
+                                  gi);
             __syncwarp();
 
             // ---- phase 2: lane = (row slot, piece of row) -----------------------
@@ -220,10 +223,10 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
 // ---------------------------------------------------------------------------
 // launch table
 // ---------------------------------------------------------------------------
-template <typename T, int LPR, int NV, bool SCALAR, int CPS>
+template <typename T, int LPR, int NV, bool SCALAR, int MODE>
 static cudaError_t launch_fwd_inst(const Params& p, const LaunchShape& ls, size_t smem,
                                    cudaStream_t stream) {
-    auto kern = msda_fwd_kernel<T, LPR, NV, SCALAR, CPS>;
+    auto kern = msda_fwd_kernel<T, LPR, NV, SCALAR, MODE>;
     if (smem > 48 * 1024) {
         cudaError_t e =
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -236,34 +239,34 @@ static cudaError_t launch_fwd_inst(const Params& p, const LaunchShape& ls, size_
     return cudaGetLastError();
 }
 
-template <typename T, int CPS>
+template <typename T, int MODE>
 static cudaError_t launch_fwd_typed(const Params& p, const RowPlan& rp, const LaunchShape& ls, size_t smem,
                                     cudaStream_t stream) {
-    if (rp.scalar) return launch_fwd_inst<T, 32, 8, true, CPS>(p, ls, smem, stream);
+    if (rp.scalar) return launch_fwd_inst<T, 32, 8, true, MODE>(p, ls, smem, stream);
     switch (rp.lpr * 100 + rp.nv) {
-        case 101: return launch_fwd_inst<T, 1, 1, false, CPS>(p, ls, smem, stream);
-        case 201: return launch_fwd_inst<T, 2, 1, false, CPS>(p, ls, smem, stream);
-        case 401: return launch_fwd_inst<T, 4, 1, false, CPS>(p, ls, smem, stream);
-        case 801: return launch_fwd_inst<T, 8, 1, false, CPS>(p, ls, smem, stream);
-        case 1601: return launch_fwd_inst<T, 16, 1, false, CPS>(p, ls, smem, stream);
-        case 3201: return launch_fwd_inst<T, 32, 1, false, CPS>(p, ls, smem, stream);
+        case 101: return launch_fwd_inst<T, 1, 1, false, MODE>(p, ls, smem, stream);
+        case 201: return launch_fwd_inst<T, 2, 1, false, MODE>(p, ls, smem, stream);
+        case 401: return launch_fwd_inst<T, 4, 1, false, MODE>(p, ls, smem, stream);
+        case 801: return launch_fwd_inst<T, 8, 1, false, MODE>(p, ls, smem, stream);
+        case 1601: return launch_fwd_inst<T, 16, 1, false, MODE>(p, ls, smem, stream);
+        case 3201: return launch_fwd_inst<T, 32, 1, false, MODE>(p, ls, smem, stream);
         case 3202:
             if constexpr (sizeof(T) == 4) {
-                return launch_fwd_inst<T, 32, 2, false, CPS>(p, ls, smem, stream);
+                return launch_fwd_inst<T, 32, 2, false, MODE>(p, ls, smem, stream);
             }
             return cudaErrorInvalidValue;
         default: return cudaErrorInvalidValue;
     }
 }
 
-template <int CPS>
+template <int MODE>
 static cudaError_t launch_forward_cps(const Params& p, int dtype, const RowPlan& rp,
                                       const LaunchShape& ls, cudaStream_t stream) {
     const size_t smem = static_cast<size_t>(p.warp_smem) * kWarpsPerCta;
     switch (dtype) {
-        case 0: return launch_fwd_typed<float, CPS>(p, rp, ls, smem, stream);
-        case 1: return launch_fwd_typed<__half, CPS>(p, rp, ls, smem, stream);
-        case 2: return launch_fwd_typed<__nv_bfloat16, CPS>(p, rp, ls, smem, stream);
+        case 0: return launch_fwd_typed<float, MODE>(p, rp, ls, smem, stream);
+        case 1: return launch_fwd_typed<__half, MODE>(p, rp, ls, smem, stream);
+        case 2: return launch_fwd_typed<__nv_bfloat16, MODE>(p, rp, ls, smem, stream);
         default: return cudaErrorInvalidValue;
     }
 }

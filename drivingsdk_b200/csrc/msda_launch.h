@@ -57,6 +57,12 @@ cudaError_t launch_gka_forward(const Params& p, int dtype, const RowPlan& rp,
 cudaError_t launch_gka_backward(const Params& p, int dtype, int acc_f32, const RowPlan& rp,
                                 const LaunchShape& ls, cudaStream_t stream);
 
+// Fused variant (reference points + offsets + logits instead of locations + weights).
+cudaError_t launch_fused_forward(const Params& p, int dtype, const RowPlan& rp,
+                                 const LaunchShape& ls, cudaStream_t stream);
+cudaError_t launch_fused_backward(const Params& p, int dtype, int acc_f32, const RowPlan& rp,
+                                  const LaunchShape& ls, cudaStream_t stream);
+
 // Adds to the library-wide kernel launch counter (msda_sm100_launch_count).
 void count_launches(int n);
 

@@ -29,6 +29,7 @@ namespace msda {
 struct LaneLevels {
     int w0, h0, start0;  // chunk 0 (samples 0..31, or the only chunk)
     int w1, h1, start1;  // chunk 1 (samples 32..63)
+    int level0;          // level index of the lane's chunk-0 sample (fused variant)
     __device__ __forceinline__ int w(int c) const { return c ? w1 : w0; }
     __device__ __forceinline__ int h(int c) const { return c ? h1 : h0; }
     __device__ __forceinline__ int start(int c) const { return c ? start1 : start0; }
@@ -66,6 +67,7 @@ __device__ __forceinline__ LaneLevels load_lane_levels(const Params& p, int lane
         }
         if (c == 0) {
             lv.h0 = hh; lv.w0 = ww; lv.start0 = ss;
+            lv.level0 = l;
         } else {
             lv.h1 = hh; lv.w1 = ww; lv.start1 = ss;
         }
@@ -166,11 +168,55 @@ __device__ __forceinline__ void init_unused_slots(uint2* s_slot, int lane) {
     }
 }
 
+// Sum / maximum over the samples of this lane's task. With one task per item that is the whole
+// warp (inactive lanes must hold the neutral element); with several tasks per item the
+// values go through `scratch` (32 floats of the warp's shared memory) and every lane walks
+// its own task's segment.
+__device__ __forceinline__ float task_sum(const Params& p, float v, int lane, int tl,
+                                          float* scratch) {
+    if (p.tasks_per_item == 1) {
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        return v;
+    }
+    __syncwarp();
+    scratch[lane] = v;
+    __syncwarp();
+    float acc = 0.f;
+    const int begin = min(tl, p.tasks_per_item - 1) * p.LP;
+    for (int i = 0; i < p.LP; ++i) acc += scratch[begin + i];
+    return acc;
+}
+__device__ __forceinline__ float task_max(const Params& p, float v, int lane, int tl,
+                                          float* scratch) {
+    if (p.tasks_per_item == 1) {
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1)
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+        return v;
+    }
+    __syncwarp();
+    scratch[lane] = v;
+    __syncwarp();
+    float acc = -INFINITY;
+    const int begin = min(tl, p.tasks_per_item - 1) * p.LP;
+    for (int i = 0; i < p.LP; ++i) acc = fmaxf(acc, scratch[begin + i]);
+    return acc;
+}
+// The 64 padding records behind the slot array double as 128 floats of per-warp scratch for
+// the fused variant (the gather loop may read them as records, but never uses what it reads).
+__device__ __forceinline__ float* fused_scratch(uint2* s_slot) {
+    return reinterpret_cast<float*>(s_slot + kSlots);
+}
+
 // Phase 1 of one chunk: lane = sample. Obtains (x, y, weight) — from the staged buffer or
 // directly — and leaves the sample's slot records in shared memory: four (bilinear corners)
 // for CPS == 4, one (clamped integer pixel) for CPS == 1. Returns whether this lane holds a
-// sample; `gi` is its global sample index.
-template <typename T, int CPS>
+// sample; `gi` is its global sample index. FUSED: the staged/loaded pair is a sampling
+// offset and the scalar a logit; the location is reference point + offset / (W, H) of the
+// level and the weight the softmax of the task's logits (what the callers of MSDA compute
+// in separate kernels: mmcv's MultiScaleDeformableAttention.forward).
+template <typename T, int CPS, bool FUSED>
 __device__ __forceinline__ bool phase1(const Params& p, const LaneLevels& lv, int chunk, int lane,
                                        long long item, int ntask_here, const T* sloc,
                                        const T* sattn, uint2* s_slot, SampleGeom& geom,
@@ -180,13 +226,14 @@ __device__ __forceinline__ bool phase1(const Params& p, const LaneLevels& lv, in
     const bool active = (tl < ntask_here) && (s < p.LP);
     uint4 rec01 = make_uint4(kNoRow, 0u, kNoRow, 0u);
     uint4 rec23 = rec01;
-    geom.lw = geom.lh = geom.a = geom.wf = geom.hf = 0.f;
+    geom.lw = geom.lh = geom.a = geom.wf = geom.hf = geom.prob = 0.f;
     geom.valid = false;
     gi = 0;
+    float lx = 0.f, ly = 0.f, a = FUSED ? -INFINITY : 0.f;
+    uint32_t t = 0;
     if (active) {
-        const uint32_t t = static_cast<uint32_t>(item) * p.tasks_per_item + tl;
+        t = static_cast<uint32_t>(item) * p.tasks_per_item + tl;
         gi = static_cast<long long>(t) * p.LP + s;
-        float lx, ly, a;
         if (sloc != nullptr) {
             const int li = tl * p.LP + s;
             lx = Elem<T>::to_f(sloc[2 * li]);
@@ -198,9 +245,26 @@ __device__ __forceinline__ bool phase1(const Params& p, const LaneLevels& lv, in
             ly = Elem<T>::to_f(gl[2 * gi + 1]);
             a = Elem<T>::to_f(static_cast<const T*>(p.attn)[gi]);
         }
+    }
+    if constexpr (FUSED) {
+        // softmax over the task's L*P logits (all lanes take part in the reductions)
+        float* scratch = fused_scratch(s_slot);
+        const float m = task_max(p, a, lane, tl, scratch);
+        const float e = active ? __expf(a - m) : 0.f;
+        const float sum = task_sum(p, e, lane, tl, scratch);
+        a = active ? e / sum : 0.f;
+    }
+    if (active) {
         const uint32_t b = fd_div(t, p.fd_qh);
-        const uint32_t h = t - fd_div(t, p.fd_h) * p.H;
+        const uint32_t bq = fd_div(t, p.fd_h);          // b * Q + q
+        const uint32_t h = t - bq * p.H;
         const int c = (p.tasks_per_item == 1) ? chunk : 0;
+        if constexpr (FUSED) {
+            const T* ref = static_cast<const T*>(p.ref) +
+                           (static_cast<size_t>(bq) * p.L + lv.level0) * 2;
+            lx = Elem<T>::to_f(ref[0]) + lx / static_cast<float>(lv.w(c));
+            ly = Elem<T>::to_f(ref[1]) + ly / static_cast<float>(lv.h(c));
+        }
         const uint32_t row_base =
             (b * static_cast<uint32_t>(p.K) + static_cast<uint32_t>(lv.start(c))) * p.H + h;
         if constexpr (CPS == 4) {

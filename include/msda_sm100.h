@@ -129,6 +129,30 @@ int msda_sm100_backward_static(const void* value, const int32_t* spatial_shapes,
                                int B, int K, int H, int D, int L, int Q, int P, int dtype,
                                void* stream);
 
+/* Fused MSDA: the operator together with the arithmetic its callers run around it
+ * (mmcv's MultiScaleDeformableAttention.forward): sampling location = reference point +
+ * offset / (W, H) of the level, attention weight = softmax of the logits over levels*points.
+ * No counterpart in the reference library (its models call the plain operator); it removes
+ * the softmax and location kernels and the two intermediate tensors between them.
+ *   reference_points [B, Q, L, 2] (x, y) in [0, 1]; sampling_offsets [B, Q, H, L, P, 2] in
+ *   pixels; attention_logits [B, Q, H, L, P]; all in `dtype`. Limit: L * P <= 32.
+ * Backward: grad_value as msda_sm100_backward_ws (same workspace rule); grad_sampling_offsets
+ * and grad_attention_logits in `dtype`, fully written; grad_reference_points [B, Q, L, 2] in
+ * FLOAT32 (summed over heads and points with atomics; zero-filled by the call). */
+int msda_sm100_fused_forward(const void* value, const int32_t* spatial_shapes,
+                             const int32_t* level_start_index, const void* reference_points,
+                             const void* sampling_offsets, const void* attention_logits,
+                             void* output, int B, int K, int H, int D, int L, int Q, int P,
+                             int dtype, void* stream);
+int msda_sm100_fused_backward_ws(const void* value, const int32_t* spatial_shapes,
+                                 const int32_t* level_start_index, const void* reference_points,
+                                 const void* sampling_offsets, const void* attention_logits,
+                                 const void* grad_output, void* grad_value,
+                                 float* grad_reference_points, void* grad_sampling_offsets,
+                                 void* grad_attention_logits, void* workspace,
+                                 size_t workspace_bytes, int B, int K, int H, int D, int L, int Q,
+                                 int P, int dtype, void* stream);
+
 /* Geometric kernel attention (nearest-pixel sampling), forward. Replaces
  * aclnnGeometricKernelAttention (mx_driving/csrc/GeometricKernelAttentionFunc.cpp:34-57;
  * device kernel kernels/geometric_kernel_attention/op_kernel/geometric_kernel_attention.cpp).
