@@ -46,9 +46,10 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--op", default="msda", choices=["msda", "gka", "da"],
-                    help="msda (the headline path, default); gka / da: the sibling operators "
-                         "geometric kernel attention / deformable aggregation on one GPU")
+    ap.add_argument("--op", default="msda", choices=["msda", "fused", "gka", "da"],
+                    help="msda (the headline path, default); fused: MSDA with its callers' softmax and "
+                         "location arithmetic inside; gka / da: the sibling operators geometric "
+                         "kernel attention / deformable aggregation; these three on one GPU")
     ap.add_argument("--workload", default="bevformer_sca")
     ap.add_argument("--dtype", default="float32", choices=["float32", "float16", "bfloat16"])
     ap.add_argument("--shard", default="batch", choices=["batch", "query"])
@@ -526,6 +527,49 @@ def run_sibling(args):
             msda_oracle.gka_backward(n(value), shapes.cpu().numpy(), starts.cpu().numpy(), n(loc),
                                      n(attn), n(go))
         config = {"workload": "gka_maptr_test_shape", "B": B, "Q": Q, "H": H, "D": D, "K": K,
+                  "L": L, "P": P}
+    elif args.op == "fused":
+        # BEVFormer-base shape, fed by reference points, offsets (pixels) and logits
+        from drivingsdk_b200 import workloads
+        w = workloads.WORKLOADS["bevformer_sca"]
+        B, Q, H, D, L, P, K = w.B, w.Q, w.H, w.D, w.L, w.P, w.K
+        shapes64, starts64 = workloads.level_tensors(w.levels)
+        shapes, starts = shapes64.int().to(dev), starts64.int().to(dev)
+        value = torch.randn(B, K, H, D, generator=g).to(dev)
+        ref = torch.rand(B, Q, L, 2, generator=g).to(dev)
+        off = (torch.randn(B, Q, H, L, P, 2, generator=g) * 20).to(dev)
+        logits = torch.randn(B, Q, H, L, P, generator=g).to(dev)
+        go = torch.randn(B, Q, H * D, generator=g).to(dev)
+        out = torch.empty(B, Q, H * D, device=dev)
+        gv, goff, glog = torch.empty_like(value), torch.empty_like(off), torch.empty_like(logits)
+        gref = torch.empty(B, Q, L, 2, device=dev)
+        dims = (B, K, H, D, L, Q, P)
+        samples = B
+        nv, ns, no, nr = value.numel(), logits.numel(), out.numel(), ref.numel()
+        fwd_bytes = 4 * (nv + 3 * ns + nr + no)
+        bwd_bytes = 4 * (2 * nv + 6 * ns + 2 * nr + no)
+
+        def fwd():
+            capi.check(lib.msda_sm100_fused_forward(
+                value.data_ptr(), shapes.data_ptr(), starts.data_ptr(), ref.data_ptr(),
+                off.data_ptr(), logits.data_ptr(), out.data_ptr(), *dims, capi.F32,
+                stream.cuda_stream), "fused fwd")
+
+        def bwd():
+            capi.check(lib.msda_sm100_fused_backward_ws(
+                value.data_ptr(), shapes.data_ptr(), starts.data_ptr(), ref.data_ptr(),
+                off.data_ptr(), logits.data_ptr(), go.data_ptr(), gv.data_ptr(), gref.data_ptr(),
+                goff.data_ptr(), glog.data_ptr(), None, 0, *dims, capi.F32, stream.cuda_stream),
+                "fused bwd")
+
+        def cpu_once(nb):
+            from drivingsdk_b200.ops.msda_fused import compose_unfused
+            loc, attn = compose_unfused(ref[:nb].cpu(), off[:nb].cpu(), logits[:nb].cpu(), shapes64)
+            n = lambda t: t[:nb].cpu().numpy()
+            msda_oracle.forward(n(value), shapes64.numpy(), starts64.numpy(), loc.numpy(), attn.numpy())
+            msda_oracle.backward(n(value), shapes64.numpy(), starts64.numpy(), loc.numpy(),
+                                 attn.numpy(), n(go))
+        config = {"workload": "bevformer_sca_fused", "B": B, "Q": Q, "H": H, "D": D, "K": K,
                   "L": L, "P": P}
     else:
         # Sparse4D-style call: 6 cameras x 4 scales (64x176 ... 8x22), 256 channels in 8 groups,
