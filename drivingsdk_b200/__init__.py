@@ -17,6 +17,8 @@ Public surface, same names as the reference package exports for this path
     deformable_aggregation / npu_deformable_aggregation(mc_ms_feat, spatial_shape,
                                scale_start_index, sampling_location, weights) -> Tensor
                                (mx_driving/ops/npu_deformable_aggregation.py:9-88)
+    npu_add_relu(x, y) -> x = relu(x + y)      (mx_driving/ops/npu_add_relu.py:19-37)
+    npu_max_pool2d(x, 3, 2, 1) -> Tensor       (mx_driving/ops/npu_max_pool2d.py:13-19)
 
 The operator names are resolved on first use, so that the patcher (pure Python)
 can be imported on a machine without the compiled extension. Using an operator
@@ -34,9 +36,14 @@ _OP_NAMES = (
 _GKA_NAMES = ("geometric_kernel_attention", "GeometricKernelAttentionFunc")
 _FUSED_NAMES = ("multi_scale_deformable_attn_fused", "MultiScaleDeformableAttnFusedFunction")
 _DA_NAMES = ("npu_deformable_aggregation", "deformable_aggregation", "AdsDeformableAggregation")
+# operators behind the other default patches: name -> module under .ops
+_CONV_SIDE = {
+    "npu_add_relu": "npu_add_relu",
+    "npu_max_pool2d": "npu_max_pool2d",
+}
 
 __all__ = (list(_OP_NAMES) + list(_FUSED_NAMES) + list(_GKA_NAMES) + list(_DA_NAMES)
-           + ["patcher", "default_patcher", "dist"])
+           + list(_CONV_SIDE) + ["patcher", "default_patcher", "dist"])
 
 
 def __getattr__(name):
@@ -51,6 +58,9 @@ def __getattr__(name):
         return getattr(mod, name)
     if name in _DA_NAMES:
         mod = importlib.import_module(__name__ + ".ops.npu_deformable_aggregation")
+        return getattr(mod, name)
+    if name in _CONV_SIDE:
+        mod = importlib.import_module(__name__ + ".ops." + _CONV_SIDE[name])
         return getattr(mod, name)
     if name == "_C":
         return importlib.import_module(__name__ + "._C")

@@ -21,7 +21,7 @@ EXT = os.path.join(PKG, "_C.so")
 
 CUDA_SOURCES = ["msda_capi.cu", "msda_fwd_sm100.cu", "msda_bwd_sm100.cu", "gka_fwd_sm100.cu",
                 "gka_bwd_sm100.cu", "msda_fused_fwd_sm100.cu", "msda_fused_bwd_sm100.cu", "da_sm100.cu",
-                "msda_static_scratch.cu"]
+                "msda_static_scratch.cu", "resnet_ops_sm100.cu"]
 CUDA_HEADERS = ["msda_common.cuh", "msda_tile.cuh", "msda_launch.h", "msda_fwd_kernel.cuh",
                 "msda_bwd_kernel.cuh"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -1,4 +1,5 @@
-"""ctypes view of the C-ABI library (``libmsda_sm100.so``, include/msda_sm100.h).
+"""ctypes view of the C-ABI library (``libmsda_sm100.so``, include/msda_sm100.h and
+include/conv_ops_sm100.h).
 
 This is the same boundary a non-Python host would bind. The torch extension
 ``_C`` links against the library directly; this module exists for callers that
@@ -14,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libmsda_sm100.so")
 F32, F16, BF16 = 0, 1, 2
 TUNE_STAGE, TUNE_CTAS_PER_SM, TUNE_CTAS_PER_SM_BWD = 0, 1, 2
 
-# name -> (restype, argtypes); kept in step with include/msda_sm100.h
+# name -> (restype, argtypes); kept in step with the headers under include/
 _vp, _ip, _i, _sz = ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
 _DIMS7 = [_i] * 7
 SIGNATURES = {
@@ -35,6 +36,9 @@ SIGNATURES = {
     "msda_sm100_static_scratch_bytes": (_sz, []),
     "msda_sm100_backward_static": (_i, [_vp, _ip, _ip, _vp, _vp, _vp, _vp, _vp, _vp] + _DIMS7
                                    + [_i, _vp]),
+    "addrelu_sm100_forward": (_i, [_vp, _vp, _sz, _i, _vp]),
+    "addrelu_sm100_backward": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
+    "maxpool_sm100_forward": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "msda_sm100_forward_bytes": (_sz, _DIMS7 + [_i]),
     "msda_sm100_backward_bytes": (_sz, _DIMS7 + [_i]),
     "msda_sm100_device_status": (_i, [_i]),

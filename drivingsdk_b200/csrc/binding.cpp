@@ -24,6 +24,7 @@
 
 #include <tuple>
 
+#include "../../include/conv_ops_sm100.h"
 #include "../../include/msda_sm100.h"
 
 namespace {
@@ -487,6 +488,68 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> msda_fused_backward(
     return std::make_tuple(grad_value, grad_ref.to(ref.scalar_type()), grad_off, grad_logits);
 }
 
+// ---------------------------------------------------------------------------
+// add + ReLU and ResNet-stem max pooling (mx_driving/csrc/pybind.cpp: npu_add_relu,
+// npu_add_relu_grad, npu_max_pool2d; bindings mx_driving/csrc/AddRelu.cpp:20-32,
+// mx_driving/csrc/MaxPool2d.cpp:25-100)
+// ---------------------------------------------------------------------------
+at::Tensor npu_add_relu(at::Tensor& x, const at::Tensor& y_in) {
+    TORCH_CHECK(x.is_cuda() && y_in.is_cuda(),
+                "npu_add_relu: x and y must be CUDA tensors (this build has no CPU path)");
+    TORCH_CHECK(is_float_kind(x.scalar_type()) && x.scalar_type() == y_in.scalar_type(),
+                "npu_add_relu: x and y must share a dtype of float16, bfloat16 or float32");
+    TORCH_CHECK(x.sizes() == y_in.sizes(), "npu_add_relu: x and y must have the same shape");
+    TORCH_CHECK(x.is_contiguous(), "npu_add_relu: x is updated in place and must be contiguous");
+    const c10::cuda::CUDAGuard guard(x.device());
+    const at::Tensor y = y_in.contiguous();
+    const int rc = addrelu_sm100_forward(x.data_ptr(), y.data_ptr(),
+                                         static_cast<size_t>(x.numel()),
+                                         dtype_code(x.scalar_type()),
+                                         at::cuda::getCurrentCUDAStream().stream());
+    raise_on_error(rc, "npu_add_relu");
+    return x;
+}
+
+at::Tensor npu_add_relu_grad(const at::Tensor& self_in, const at::Tensor& grad_output_in) {
+    TORCH_CHECK(self_in.is_cuda() && grad_output_in.is_cuda(),
+                "npu_add_relu_grad: CUDA tensors expected (this build has no CPU path)");
+    TORCH_CHECK(is_float_kind(self_in.scalar_type()), "npu_add_relu_grad: floating tensors expected");
+    TORCH_CHECK(self_in.numel() == grad_output_in.numel(),
+                "npu_add_relu_grad: self and grad_output must have the same number of elements");
+    const c10::cuda::CUDAGuard guard(self_in.device());
+    const at::Tensor self = self_in.contiguous();
+    const at::Tensor grad_output = grad_output_in.to(self.scalar_type()).contiguous();
+    at::Tensor result = at::empty_like(self);
+    const int rc = addrelu_sm100_backward(self.data_ptr(), grad_output.data_ptr(), result.data_ptr(),
+                                          static_cast<size_t>(self.numel()),
+                                          dtype_code(self.scalar_type()),
+                                          at::cuda::getCurrentCUDAStream().stream());
+    raise_on_error(rc, "npu_add_relu_grad");
+    return result;
+}
+
+at::Tensor npu_max_pool2d(const at::Tensor& x_in, int kernel_size, int stride, int padding) {
+    TORCH_CHECK(x_in.is_cuda(), "npu_max_pool2d: x must be a CUDA tensor (this build has no CPU path)");
+    TORCH_CHECK(is_float_kind(x_in.scalar_type()),
+                "x: float32 or float16 tensor expected but got a tensor with dtype: ",
+                x_in.scalar_type());
+    TORCH_CHECK(kernel_size == 3, "kernel_size: expected 3 but got: ", kernel_size);
+    TORCH_CHECK(stride == 2, "stride: expected 2 but got: ", stride);
+    TORCH_CHECK(padding == 1, "padding: expected 1 but got: ", padding);
+    TORCH_CHECK(x_in.dim() == 4, "x_trans.dim() must be 4, but got: ", x_in.dim());
+    const c10::cuda::CUDAGuard guard(x_in.device());
+    const at::Tensor x = x_in.contiguous();
+    const int64_t N = x.size(0), C = x.size(1), H = x.size(2), W = x.size(3);
+    at::Tensor y = at::empty({N, C, (H + 1) / 2, (W + 1) / 2}, x.options());
+    if (y.numel() == 0) return y;
+    const int rc = maxpool_sm100_forward(x.data_ptr(), y.data_ptr(), static_cast<int>(N),
+                                         static_cast<int>(C), static_cast<int>(H),
+                                         static_cast<int>(W), dtype_code(x.scalar_type()),
+                                         at::cuda::getCurrentCUDAStream().stream());
+    raise_on_error(rc, "npu_max_pool2d");
+    return y;
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "sm_100a multi-scale deformable attention (drop-in for mx_driving._C on this path)";
     m.def("multi_scale_deformable_attn", &multi_scale_deformable_attn,
@@ -511,6 +574,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("npu_deformable_aggregation", &deformable_aggregation,
           "deformable aggregation forward: (mc_ms_feat, spatial_shape, scale_start_index, "
           "sampling_location, weights) -> output");
+    m.def("npu_add_relu", &npu_add_relu, "x = relu(x + y) in place; returns x");
+    m.def("npu_add_relu_grad", &npu_add_relu_grad, "(out, grad_output) -> grad of either addend");
+    m.def("npu_max_pool2d", &npu_max_pool2d, "(x, 3, 2, 1) -> max pooled x (inference only)");
     m.def("npu_deformable_aggregation_backward", &deformable_aggregation_backward,
           "deformable aggregation backward -> (grad_mc_ms_feat, grad_sampling_location, "
           "grad_weights)");

@@ -286,6 +286,7 @@ int forward_impl(const void* value, const int32_t* spatial_shapes,
 
 namespace msda {
 void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+int note_cuda_error(cudaError_t e) { return fail_cuda(e); }
 }  // namespace msda
 
 extern "C" {

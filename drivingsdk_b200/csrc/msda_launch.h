@@ -66,6 +66,10 @@ cudaError_t launch_fused_backward(const Params& p, int dtype, int acc_f32, const
 // Adds to the library-wide kernel launch counter (msda_sm100_launch_count).
 void count_launches(int n);
 
+// Records `e` as the calling thread's last CUDA error (msda_sm100_last_cuda_error) and
+// returns MSDA_ERR_CUDA.
+int note_cuda_error(cudaError_t e);
+
 // out[i] = (T)acc[i] for n elements; dtype 1 = fp16, 2 = bf16.
 cudaError_t launch_downcast(const float* acc, void* out, long long n, int dtype,
                             cudaStream_t stream);

@@ -5,11 +5,11 @@
 
 Same surface as the reference's patcher for this path (mx_driving/patcher/__init__.py):
 ``Patcher``, ``Patch``, ``AtomicPatch``, ``BasePatch``, ``PatchStatus``, ``PatchResult``,
-``MultiScaleDeformableAttention`` (alias ``MSDA``), ``default_patcher``, the legacy
-function ``msda(module, options)``, ``configure_patcher_logging`` and
-``set_patcher_log_level``. The reference's other predefined patches (deformable
-convolution, sparse convolution, dataset and optimizer shims, ...) belong to other
-operators and are not part of this package.
+``MultiScaleDeformableAttention`` (alias ``MSDA``), ``ResNetAddRelu``, ``ResNetMaxPool``,
+``default_patcher``, the legacy functions ``msda(module, options)``, ``resnet_add_relu``,
+``resnet_maxpool``, ``configure_patcher_logging`` and ``set_patcher_log_level``. The
+reference's other predefined patches (sparse convolution, dataset and optimizer shims, ...)
+belong to operators that are not part of this package.
 """
 from typing import Dict, List, Type
 
@@ -18,11 +18,20 @@ from .reporting import PatchResult, PatchStatus
 from .patch import AtomicPatch, BasePatch, Patch
 from .patcher import Patcher, replace_with
 from .mmcv_patch import MultiScaleDeformableAttention
+from .mmdet_patch import ResNetAddRelu, ResNetMaxPool
 
 MSDA = MultiScaleDeformableAttention  # alias
 
-_ALL_PATCH_CLASSES: List[Type[Patch]] = [MultiScaleDeformableAttention]
-_DEFAULT_PATCH_CLASSES: List[Type[Patch]] = [MultiScaleDeformableAttention]
+# same order as the reference's registry (mx_driving/patcher/__init__.py:116-149), restricted
+# to the patches whose operators exist in this package
+_ALL_PATCH_CLASSES: List[Type[Patch]] = [
+    MultiScaleDeformableAttention,
+    ResNetAddRelu, ResNetMaxPool,
+]
+_DEFAULT_PATCH_CLASSES: List[Type[Patch]] = [
+    MultiScaleDeformableAttention,
+    ResNetAddRelu, ResNetMaxPool,
+]
 
 
 def _create_default_patcher() -> Patcher:
@@ -48,11 +57,14 @@ def _create_legacy_patch_func(patch_cls: Type[Patch]):
 
 
 msda = _create_legacy_patch_func(MultiScaleDeformableAttention)
+resnet_add_relu = _create_legacy_patch_func(ResNetAddRelu)
+resnet_maxpool = _create_legacy_patch_func(ResNetMaxPool)
 
 __all__ = [
     "Patcher", "BasePatch", "Patch", "AtomicPatch", "replace_with",
     "patcher_logger", "configure_patcher_logging", "set_patcher_log_level",
     "PatchStatus", "PatchResult",
     "default_patcher", "MultiScaleDeformableAttention", "MSDA", "msda",
+    "ResNetAddRelu", "ResNetMaxPool", "resnet_add_relu", "resnet_maxpool",
     "_ALL_PATCH_CLASSES", "_DEFAULT_PATCH_CLASSES", "_LEGACY_NAME_TO_CLASS",
 ]

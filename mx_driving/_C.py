@@ -4,6 +4,9 @@ from drivingsdk_b200._C import (  # noqa: F401
     geometric_kernel_attention_backward,
     geometric_kernel_attention_forward,
     multi_scale_deformable_attn,
+    npu_add_relu,
+    npu_add_relu_grad,
+    npu_max_pool2d,
     npu_deformable_aggregation,
     npu_deformable_aggregation_backward,
     multi_scale_deformable_attn_backward,

@@ -7,13 +7,18 @@ import re
 from drivingsdk_b200 import capi
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-HEADER = os.path.join(ROOT, "include", "msda_sm100.h")
+INCLUDE = os.path.join(ROOT, "include")
 
 
 def declared_functions():
-    text = open(HEADER).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b((?:msda|gka|da)_sm100_\w+)\s*\(", text)))
+    names = set()
+    for header in sorted(os.listdir(INCLUDE)):
+        if not header.endswith(".h"):
+            continue
+        text = open(os.path.join(INCLUDE, header)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names.update(re.findall(r"\b([a-z]+_sm100_\w+)\s*\(", text))
+    return sorted(names)
 
 
 def test_every_declared_symbol_is_exported():
@@ -21,7 +26,7 @@ def test_every_declared_symbol_is_exported():
     names = declared_functions()
     assert len(names) >= 12
     for n in names:
-        assert hasattr(lib, n), f"{n} is declared in include/msda_sm100.h but not exported"
+        assert hasattr(lib, n), f"{n} is declared under include/ but not exported"
 
 
 def test_python_signature_table_matches_header():
