@@ -19,6 +19,11 @@ Public surface, same names as the reference package exports for this path
                                (mx_driving/ops/npu_deformable_aggregation.py:9-88)
     npu_add_relu(x, y) -> x = relu(x + y)      (mx_driving/ops/npu_add_relu.py:19-37)
     npu_max_pool2d(x, 3, 2, 1) -> Tensor       (mx_driving/ops/npu_max_pool2d.py:13-19)
+    deform_conv2d(x, offset, weight, stride, padding, dilation, groups, deformable_groups)
+                               DeformConv2dFunction   (mx_driving/ops/deform_conv2d.py:19-121)
+    modulated_deform_conv2d(x, offset, mask, weight, bias, stride, padding, dilation, groups,
+                               deformable_groups)   ModulatedDeformConv2dFunction
+                               (mx_driving/ops/modulated_deform_conv2d.py:24-132)
 
 The operator names are resolved on first use, so that the patcher (pure Python)
 can be imported on a machine without the compiled extension. Using an operator
@@ -40,6 +45,10 @@ _DA_NAMES = ("npu_deformable_aggregation", "deformable_aggregation", "AdsDeforma
 _CONV_SIDE = {
     "npu_add_relu": "npu_add_relu",
     "npu_max_pool2d": "npu_max_pool2d",
+    "deform_conv2d": "deform_conv2d",
+    "DeformConv2dFunction": "deform_conv2d",
+    "modulated_deform_conv2d": "modulated_deform_conv2d",
+    "ModulatedDeformConv2dFunction": "modulated_deform_conv2d",
 }
 
 __all__ = (list(_OP_NAMES) + list(_FUSED_NAMES) + list(_GKA_NAMES) + list(_DA_NAMES)

@@ -21,9 +21,10 @@ EXT = os.path.join(PKG, "_C.so")
 
 CUDA_SOURCES = ["msda_capi.cu", "msda_fwd_sm100.cu", "msda_bwd_sm100.cu", "gka_fwd_sm100.cu",
                 "gka_bwd_sm100.cu", "msda_fused_fwd_sm100.cu", "msda_fused_bwd_sm100.cu", "da_sm100.cu",
-                "msda_static_scratch.cu", "resnet_ops_sm100.cu"]
+                "msda_static_scratch.cu", "resnet_ops_sm100.cu", "dcn_sm100.cu",
+                "gemm_simt_sm100.cu", "gemm_tc_sm100.cu"]
 CUDA_HEADERS = ["msda_common.cuh", "msda_tile.cuh", "msda_launch.h", "msda_fwd_kernel.cuh",
-                "msda_bwd_kernel.cuh"]
+                "msda_bwd_kernel.cuh", "gemm_sm100.h"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 OBJ_DIR = os.path.join(PKG, "build")
@@ -55,7 +56,8 @@ def build_library(force=False, verbose_ptxas=False) -> str:
     from concurrent.futures import ThreadPoolExecutor
     srcs = [os.path.join(CSRC, s) for s in CUDA_SOURCES]
     deps = srcs + [os.path.join(CSRC, h) for h in CUDA_HEADERS] + [
-        os.path.join(ROOT, "include", "msda_sm100.h")]
+        os.path.join(ROOT, "include", "msda_sm100.h"),
+        os.path.join(ROOT, "include", "conv_ops_sm100.h")]
     if not (force or _stale(LIB, deps)):
         return LIB
     os.makedirs(OBJ_DIR, exist_ok=True)
@@ -77,7 +79,8 @@ def build_library(force=False, verbose_ptxas=False) -> str:
 
 def build_extension(force=False) -> str:
     src = os.path.join(CSRC, "binding.cpp")
-    deps = [src, os.path.join(ROOT, "include", "msda_sm100.h"), LIB]
+    deps = [src, os.path.join(ROOT, "include", "msda_sm100.h"),
+            os.path.join(ROOT, "include", "conv_ops_sm100.h"), LIB]
     if not (force or _stale(EXT, deps)):
         return EXT
     import torch

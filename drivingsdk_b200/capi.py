@@ -39,6 +39,13 @@ SIGNATURES = {
     "addrelu_sm100_forward": (_i, [_vp, _vp, _sz, _i, _vp]),
     "addrelu_sm100_backward": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
     "maxpool_sm100_forward": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "dcn_sm100_columns_bytes": (_sz, [_vp]),
+    "dcn_sm100_backward_workspace_bytes": (_sz, [_vp]),
+    "dcn_sm100_forward": (_i, [_vp] * 7 + [_vp, _vp]),
+    "dcn_sm100_backward": (_i, [_vp] * 11 + [_vp, _sz, _vp, _vp]),
+    "dcn_sm100_use_tensor_cores": (_i, [_i]),
+    "gemm_nt_sm100_f32": (_i, [_vp, ctypes.c_longlong, _vp, ctypes.c_longlong, _vp,
+                               ctypes.c_longlong, _vp, _i, _i, _i, _i, _vp]),
     "msda_sm100_forward_bytes": (_sz, _DIMS7 + [_i]),
     "msda_sm100_backward_bytes": (_sz, _DIMS7 + [_i]),
     "msda_sm100_device_status": (_i, [_i]),
@@ -49,6 +56,15 @@ SIGNATURES = {
     "msda_sm100_last_cuda_error": (_i, []),
     "msda_sm100_abi_version": (_i, []),
 }
+
+
+
+class DcnShape(ctypes.Structure):
+    """``dcn_shape`` of include/conv_ops_sm100.h."""
+    _fields_ = [(n, ctypes.c_int) for n in (
+        "N", "H", "W", "C", "Ho", "Wo", "Co", "kh", "kw", "stride_h", "stride_w", "pad_h",
+        "pad_w", "dil_h", "dil_w", "groups", "deform_groups")]
+
 
 _lib = None
 

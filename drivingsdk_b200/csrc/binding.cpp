@@ -550,6 +550,210 @@ at::Tensor npu_max_pool2d(const at::Tensor& x_in, int kernel_size, int stride, i
     return y;
 }
 
+// ---------------------------------------------------------------------------
+// deformable / modulated deformable convolution (mx_driving/csrc/pybind.cpp: deformable_conv2d,
+// deformable_conv2d_backward, modulated_deformable_conv2d, modulated_deformable_conv2d_backward;
+// bindings mx_driving/csrc/DeformableConv2d.cpp:21-101, ModulatedDeformableConv2d.cpp:26-140).
+// Tensors are channels-last as in the reference: x [n, h, w, c], offset [n, ho, wo, dg*2*kh*kw],
+// mask [n, ho, wo, dg*kh*kw], weight [co, kh, kw, c/groups]; grad_out is taken as
+// [n, ho, wo, co] by both backward functions. Arithmetic is fp32; 16-bit inputs are converted.
+// ---------------------------------------------------------------------------
+namespace {
+
+struct DcnCall {
+    dcn_shape s;
+    at::Tensor x, offset, mask, weight;
+};
+
+DcnCall check_dcn(const at::Tensor& input, const at::Tensor& offset, const at::Tensor& mask,
+                  const at::Tensor& weight, at::IntArrayRef kernel_size, at::IntArrayRef stride,
+                  at::IntArrayRef padding, at::IntArrayRef dilation, int64_t groups,
+                  int64_t deformable_groups) {
+    TORCH_CHECK(input.is_cuda() && offset.is_cuda() && weight.is_cuda(),
+                "deformable_conv2d: CUDA tensors expected (this build has no CPU path)");
+    TORCH_CHECK(input.dim() == 4, "input must to be a 4D Tensor, but got: ", input.dim());
+    TORCH_CHECK(offset.dim() == 4, "offset has to be a 4D Tensor, but got: ", offset.dim());
+    TORCH_CHECK(weight.dim() == 4, "weight has to be a 4D Tensor, but got: ", weight.dim());
+    TORCH_CHECK(kernel_size.size() == 2 && stride.size() == 2 && padding.size() == 2 &&
+                    dilation.size() == 2,
+                "kernel_size, stride, padding and dilation must have two entries");
+    TORCH_CHECK(stride[0] > 0 && stride[1] > 0, "stride must be greater than 0");
+    TORCH_CHECK(kernel_size[0] > 0 && kernel_size[1] > 0, "kernel_size must be greater than 0");
+    TORCH_CHECK(dilation[0] > 0 && dilation[1] > 0, "dilation must be greater than 0");
+    TORCH_CHECK(weight.size(1) == kernel_size[0] && weight.size(2) == kernel_size[1],
+                "kernel size mismatch");
+    TORCH_CHECK(groups > 0, "groups must be greater than 0");
+    TORCH_CHECK(deformable_groups > 0, "deformable_groups must be greater than 0");
+    TORCH_CHECK(weight.size(0) % groups == 0, "weight's out channel should be divided by groups");
+    TORCH_CHECK(input.size(3) % groups == 0, "input's channel should be divided by groups");
+    TORCH_CHECK(weight.size(3) == input.size(3) / groups,
+                "weight must be [c_out, kh, kw, c_in / groups]");
+    const int64_t taps = kernel_size[0] * kernel_size[1];
+    TORCH_CHECK(offset.size(0) == input.size(0) && offset.size(3) == deformable_groups * 2 * taps,
+                "offset must be [n, h_out, w_out, deformable_groups * 2 * kh * kw]");
+    if (mask.defined()) {
+        TORCH_CHECK(mask.is_cuda() && mask.dim() == 4, "mask has to be a 4D Tensor, but got: ", mask.dim());
+        TORCH_CHECK(mask.size(0) == offset.size(0) && mask.size(1) == offset.size(1) &&
+                        mask.size(2) == offset.size(2) && mask.size(3) == deformable_groups * taps,
+                    "The shape of the mask is invalid");
+    }
+    DcnCall c;
+    c.s.N = static_cast<int>(input.size(0));
+    c.s.H = static_cast<int>(input.size(1));
+    c.s.W = static_cast<int>(input.size(2));
+    c.s.C = static_cast<int>(input.size(3));
+    c.s.Ho = static_cast<int>(offset.size(1));
+    c.s.Wo = static_cast<int>(offset.size(2));
+    c.s.Co = static_cast<int>(weight.size(0));
+    c.s.kh = static_cast<int>(kernel_size[0]);
+    c.s.kw = static_cast<int>(kernel_size[1]);
+    c.s.stride_h = static_cast<int>(stride[0]);
+    c.s.stride_w = static_cast<int>(stride[1]);
+    c.s.pad_h = static_cast<int>(padding[0]);
+    c.s.pad_w = static_cast<int>(padding[1]);
+    c.s.dil_h = static_cast<int>(dilation[0]);
+    c.s.dil_w = static_cast<int>(dilation[1]);
+    c.s.groups = static_cast<int>(groups);
+    c.s.deform_groups = static_cast<int>(deformable_groups);
+    c.x = input.to(at::kFloat).contiguous();
+    c.offset = offset.to(at::kFloat).contiguous();
+    c.weight = weight.to(at::kFloat).contiguous();
+    if (mask.defined()) c.mask = mask.to(at::kFloat).contiguous();
+    return c;
+}
+
+std::tuple<at::Tensor, at::Tensor> dcn_forward(const char* what, const at::Tensor& input,
+                                               const at::Tensor& offset, const at::Tensor& mask,
+                                               const at::Tensor& weight, const at::Tensor& bias,
+                                               at::IntArrayRef kernel_size, at::IntArrayRef stride,
+                                               at::IntArrayRef padding, at::IntArrayRef dilation,
+                                               int64_t groups, int64_t deformable_groups) {
+    DcnCall c = check_dcn(input, offset, mask, weight, kernel_size, stride, padding, dilation,
+                          groups, deformable_groups);
+    const c10::cuda::CUDAGuard guard(input.device());
+    const dcn_shape& s = c.s;
+    at::Tensor out = at::empty({s.N, s.Ho, s.Wo, s.Co}, c.x.options());
+    at::Tensor columns = at::empty({s.N, static_cast<int64_t>(s.Ho) * s.Wo, s.groups,
+                                    static_cast<int64_t>(s.kh) * s.kw, s.C / s.groups}, c.x.options());
+    at::Tensor bias_f;
+    if (bias.defined()) {
+        TORCH_CHECK(bias.is_cuda() && bias.numel() == s.Co, "bias must be a CUDA tensor [c_out]");
+        bias_f = bias.to(at::kFloat).contiguous();
+    }
+    if (out.numel() > 0) {
+        const int rc = dcn_sm100_forward(
+            c.x.data_ptr<float>(), c.offset.data_ptr<float>(),
+            c.mask.defined() ? c.mask.data_ptr<float>() : nullptr, c.weight.data_ptr<float>(),
+            bias_f.defined() ? bias_f.data_ptr<float>() : nullptr, out.data_ptr<float>(),
+            columns.data_ptr<float>(), &s, at::cuda::getCurrentCUDAStream().stream());
+        raise_on_error(rc, what);
+    }
+    return std::make_tuple(out.permute({0, 3, 1, 2}).to(input.scalar_type()), columns);
+}
+
+struct DcnGrads {
+    at::Tensor x, offset, mask, weight, bias;
+};
+
+DcnGrads dcn_backward(const char* what, const at::Tensor& input, const at::Tensor& offset,
+                      const at::Tensor& mask, const at::Tensor& weight, bool want_bias,
+                      const at::Tensor& columns, const at::Tensor& grad_y,
+                      at::IntArrayRef kernel_size, at::IntArrayRef stride, at::IntArrayRef padding,
+                      at::IntArrayRef dilation, int64_t groups, int64_t deformable_groups) {
+    DcnCall c = check_dcn(input, offset, mask, weight, kernel_size, stride, padding, dilation,
+                          groups, deformable_groups);
+    const dcn_shape& s = c.s;
+    TORCH_CHECK(grad_y.is_cuda() && grad_y.dim() == 4 && grad_y.size(0) == s.N && grad_y.size(1) == s.Ho &&
+                    grad_y.size(2) == s.Wo && grad_y.size(3) == s.Co,
+                "grad_y must be a CUDA tensor [n, h_out, w_out, c_out]");
+    const c10::cuda::CUDAGuard guard(input.device());
+    const at::Tensor go = grad_y.to(at::kFloat).contiguous();
+    const size_t col_bytes = dcn_sm100_columns_bytes(&s);
+    at::Tensor cols = columns;
+    if (!cols.defined() || static_cast<size_t>(cols.numel()) * 4 != col_bytes || !cols.is_cuda()) {
+        // the caller did not keep the forward's columns: compute them again
+        at::Tensor out;
+        std::tie(out, cols) = dcn_forward(what, input, offset, mask, weight, at::Tensor(),
+                                          kernel_size, stride, padding, dilation, groups,
+                                          deformable_groups);
+    }
+    cols = cols.to(at::kFloat).contiguous();
+    DcnGrads g;
+    g.x = at::empty_like(c.x);
+    g.offset = at::empty_like(c.offset);
+    g.weight = at::empty_like(c.weight);
+    if (c.mask.defined()) g.mask = at::empty_like(c.mask);
+    if (want_bias) g.bias = at::empty({s.Co}, c.x.options());
+    const size_t ws_bytes = dcn_sm100_backward_workspace_bytes(&s);
+    at::Tensor ws = at::empty({static_cast<int64_t>(ws_bytes / 4) + 4}, c.x.options());
+    if (g.x.numel() > 0 && go.numel() > 0) {
+        const int rc = dcn_sm100_backward(
+            c.x.data_ptr<float>(), c.offset.data_ptr<float>(),
+            c.mask.defined() ? c.mask.data_ptr<float>() : nullptr, c.weight.data_ptr<float>(),
+            cols.data_ptr<float>(), go.data_ptr<float>(), g.x.data_ptr<float>(),
+            g.offset.data_ptr<float>(), g.mask.defined() ? g.mask.data_ptr<float>() : nullptr,
+            g.weight.data_ptr<float>(), g.bias.defined() ? g.bias.data_ptr<float>() : nullptr,
+            ws.data_ptr(), ws_bytes, &s, at::cuda::getCurrentCUDAStream().stream());
+        raise_on_error(rc, what);
+    }
+    return g;
+}
+
+}  // namespace
+
+std::tuple<at::Tensor, at::Tensor> deformable_conv2d(
+    const at::Tensor& input, const at::Tensor& offset, const at::Tensor& weight,
+    at::IntArrayRef kernel_size, at::IntArrayRef stride, at::IntArrayRef padding,
+    at::IntArrayRef dilation, int64_t groups, int64_t deformable_groups) {
+    return dcn_forward("deformable_conv2d", input, offset, at::Tensor(), weight, at::Tensor(),
+                       kernel_size, stride, padding, dilation, groups, deformable_groups);
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> deformable_conv2d_backward(
+    const at::Tensor& input, const at::Tensor& weight, const at::Tensor& offset,
+    const at::Tensor& offset_output, const at::Tensor& grad_y, at::IntArrayRef kernel_size,
+    at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation, int64_t groups,
+    int64_t deformable_groups) {
+    DcnGrads g = dcn_backward("deformable_conv2d_backward", input, offset, at::Tensor(), weight,
+                              false, offset_output, grad_y, kernel_size, stride, padding,
+                              dilation, groups, deformable_groups);
+    return std::make_tuple(g.x.permute({0, 3, 1, 2}).to(input.scalar_type()),
+                           g.weight.permute({0, 3, 1, 2}).to(weight.scalar_type()),
+                           g.offset.permute({0, 3, 1, 2}).to(offset.scalar_type()));
+}
+
+std::tuple<at::Tensor, at::Tensor> modulated_deformable_conv2d(
+    const at::Tensor& input, const at::Tensor& offset, const at::Tensor& mask,
+    const at::Tensor& weight, const c10::optional<at::Tensor>& bias_opt,
+    at::IntArrayRef kernel_size, at::IntArrayRef stride, at::IntArrayRef padding,
+    at::IntArrayRef dilation, int64_t groups, int64_t deformable_groups, int64_t with_bias) {
+    TORCH_CHECK(mask.defined(), "mask has to be a 4D Tensor");
+    const at::Tensor bias = (with_bias != 0 && bias_opt.has_value()) ? *bias_opt : at::Tensor();
+    return dcn_forward("modulated_deformable_conv2d", input, offset, mask, weight, bias,
+                       kernel_size, stride, padding, dilation, groups, deformable_groups);
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor>
+modulated_deformable_conv2d_backward(
+    const at::Tensor& input, const at::Tensor& offset, const at::Tensor& mask,
+    const at::Tensor& weight, const c10::optional<at::Tensor>& bias_opt,
+    const at::Tensor& offset_output, const at::Tensor& grad_y, at::IntArrayRef kernel_size,
+    at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation, int64_t groups,
+    int64_t deformable_groups, int64_t with_bias) {
+    TORCH_CHECK(mask.defined(), "mask has to be a 4D Tensor");
+    const bool want_bias = with_bias != 0 && bias_opt.has_value();
+    DcnGrads g = dcn_backward("modulated_deformable_conv2d_backward", input, offset, mask, weight,
+                              want_bias, offset_output, grad_y, kernel_size, stride, padding,
+                              dilation, groups, deformable_groups);
+    return std::make_tuple(g.x.permute({0, 3, 1, 2}).to(input.scalar_type()),
+                           g.weight.permute({0, 3, 1, 2}).to(weight.scalar_type()),
+                           want_bias ? g.bias.to(bias_opt->scalar_type()) : at::Tensor(),
+                           g.offset.permute({0, 3, 1, 2}).to(offset.scalar_type()),
+                           g.mask.permute({0, 3, 1, 2}).to(mask.scalar_type()));
+}
+
+int64_t dcn_use_tensor_cores(int64_t on) { return dcn_sm100_use_tensor_cores(static_cast<int>(on)); }
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "sm_100a multi-scale deformable attention (drop-in for mx_driving._C on this path)";
     m.def("multi_scale_deformable_attn", &multi_scale_deformable_attn,
@@ -574,6 +778,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("npu_deformable_aggregation", &deformable_aggregation,
           "deformable aggregation forward: (mc_ms_feat, spatial_shape, scale_start_index, "
           "sampling_location, weights) -> output");
+    m.def("deformable_conv2d", &deformable_conv2d,
+          "(x_nhwc, offset_nhwc, weight_ohwi, kernel_size, stride, padding, dilation, groups, "
+          "deformable_groups) -> (out [n, c_out, h_out, w_out] view, offset_output)");
+    m.def("deformable_conv2d_backward", &deformable_conv2d_backward,
+          "(x_nhwc, weight_ohwi, offset_nhwc, offset_output, grad_y_nhwc, kernel_size, stride, "
+          "padding, dilation, groups, deformable_groups) -> (grad_x, grad_weight, grad_offset), "
+          "each shaped like the NCHW-style original of its tensor");
+    m.def("modulated_deformable_conv2d", &modulated_deformable_conv2d,
+          "(x_nhwc, offset_nhwc, mask_nhwc, weight_ohwi, bias, kernel_size, stride, padding, "
+          "dilation, groups, deformable_groups, with_bias) -> (out, offset_output)");
+    m.def("modulated_deformable_conv2d_backward", &modulated_deformable_conv2d_backward,
+          "-> (grad_x, grad_weight, grad_bias, grad_offset, grad_mask)");
+    m.def("dcn_use_tensor_cores", &dcn_use_tensor_cores,
+          "1 / 0 selects the tcgen05 / fp32 FMA product kernels; returns the previous setting");
     m.def("npu_add_relu", &npu_add_relu, "x = relu(x + y) in place; returns x");
     m.def("npu_add_relu_grad", &npu_add_relu_grad, "(out, grad_output) -> grad of either addend");
     m.def("npu_max_pool2d", &npu_max_pool2d, "(x, 3, 2, 1) -> max pooled x (inference only)");

@@ -1,0 +1,431 @@
+// C[M, N] = sum_k A[m, k] * B[n, k] on the sm_100a tensor cores with fp32 accuracy.
+//
+// Operands are fp32 in global memory with k contiguous. A TF32 tensor-core product keeps only
+// 10 mantissa bits of each operand, which is not enough for a convolution whose results are
+// compared with an fp32 implementation at 1e-4, so every operand is split in two TF32-exact
+// parts, v = hi + lo with hi = v rounded towards zero to TF32 and lo = v - hi (exact in fp32),
+// and three products are accumulated per tile: lo*hi + hi*lo + hi*hi (lo*lo is below fp32
+// resolution). Accumulation is fp32, in tensor memory.
+//
+// One CTA computes one 128 x BN tile of C (BN = 64, 128 or 256) over its share of K, in steps
+// of 32 k (one 128-byte swizzled row per operand row):
+//   warp 0        producer: one lane issues the two TMA tile loads of a stage
+//   warps 2..5    splitters: turn the raw tile in shared memory into its hi part (in place)
+//                 and its lo part (second buffer at the same offsets, so the swizzle pattern
+//                 does not matter), then hand the stage to the MMA warp; afterwards they are
+//                 the epilogue: tcgen05.ld of the accumulator (warp q reads lanes 32q..32q+31),
+//                 bias, stores (or reductions when K is cut across CTAs)
+//   warp 1        MMA: one lane issues 4 k-slices x 3 products of tcgen05.mma per stage and
+//                 commits the stage's "empty" barrier; owns the tensor-memory allocation
+// Out-of-range parts of a tile (M, N or K tails) are zero-filled by TMA and masked in the
+// epilogue. Every barrier wait is bounded: on a timeout the CTA raises the library's sticky
+// status word, stops issuing work, waits (bounded) for its own copies, frees its tensor memory
+// and returns.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+
+#include "gemm_sm100.h"
+#include "msda_common.cuh"
+
+namespace msda {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 32;                      // fp32 elements = one 128-byte swizzle row
+constexpr int kGemmThreads = 192;
+constexpr int kTileABytes = BM * BK * 4;    // 16 KiB
+constexpr int kStatusGemmTimeout = 2;       // bit in the sticky status word
+constexpr int kWaitLimit = 1 << 22;
+
+template <int BN>
+struct Tile {
+    static constexpr int kTileBBytes = BN * BK * 4;
+    static constexpr int kStageBytes = 2 * kTileABytes + 2 * kTileBBytes;
+    static constexpr int kStages = (BN == 256) ? 2 : (BN == 128 ? 3 : 4);
+    // + barriers and the tensor-memory address, + slack to align the tiles to 1 KiB
+    static constexpr int kSmemBytes = kStages * kStageBytes + 256 + 1024;
+};
+
+__device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (int spin = 0; spin < kWaitLimit; ++spin) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (spin > 1024) __nanosleep(64);
+    }
+    return false;
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// 2-D tiled TMA load into this CTA's shared memory; coordinates are (k, row).
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1,
+                                            uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Shared-memory operand descriptor: k-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);   // start address
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;                // stride between 8-row groups
+    d |= 1ull << 46;                                            // descriptor version (sm_100)
+    d |= 2ull << 61;                                            // 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor: TF32 x TF32 -> fp32, both operands k-major, M = 128, N = BN.
+template <int BN>
+__device__ __forceinline__ uint32_t instr_desc() {
+    return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+           (static_cast<uint32_t>(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc,
+                                         uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::
+                     "r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct TcParams {
+    float* C;
+    long long ldc;
+    const float* bias;
+    int M, N, K;
+    int kb_per_split;   // k-blocks (of BK) per CTA along gridDim.z
+    int reduce;         // add into C with reductions (K is cut across CTAs)
+    int* status;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const TcParams p) {
+    using T = Tile<BN>;
+    constexpr int kStages = T::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base_u32 = smem_u32(smem_raw);
+    uint8_t* tiles = smem_raw + ((1024u - (base_u32 & 1023u)) & 1023u);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + kStages * T::kStageBytes);
+    uint64_t* full_raw = bars;                  // TMA landed
+    uint64_t* full_split = bars + kStages;      // hi/lo parts written
+    uint64_t* empty = bars + 2 * kStages;       // the MMAs that read the stage have finished
+    uint64_t* accum_full = bars + 3 * kStages;  // every MMA of the tile has finished
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    const int kb_total = (p.K + BK - 1) / BK;
+    const int kb_begin = blockIdx.z * p.kb_per_split;
+    const int kb_end = min(kb_total, kb_begin + p.kb_per_split);
+    const int num_kb = kb_end - kb_begin;
+    if (num_kb <= 0) return;   // uniform over the CTA
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_raw[s], 1);
+            mbar_init(&full_split[s], 4);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(accum_full, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::
+                         "r"(smem_u32(tmem_slot)), "r"(static_cast<uint32_t>(BN))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    auto stage_ptr = [&](int s) { return tiles + s * T::kStageBytes; };
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < num_kb && !*abort_flag; ++i) {
+                const int s = i % kStages;
+                const uint32_t round = static_cast<uint32_t>(i / kStages);
+                if (!gemm_wait(&empty[s], (round & 1u) ^ 1u)) {
+                    atomicOr(p.status, kStatusGemmTimeout);
+                    *abort_flag = 1;
+                    break;
+                }
+                uint8_t* st = stage_ptr(s);
+                mbar_expect_tx(&full_raw[s], kTileABytes + T::kTileBBytes);
+                const int k0 = (kb_begin + i) * BK;
+                tma_load_2d(st, &map_a, k0, m0, &full_raw[s]);
+                tma_load_2d(st + 2 * kTileABytes, &map_b, k0, n0, &full_raw[s]);
+                issued = i + 1;
+            }
+            if (*abort_flag) {
+                // let the copies that were issued land before the CTA goes away
+                for (int i = max(0, issued - kStages); i < issued; ++i)
+                    gemm_wait(&full_raw[i % kStages], static_cast<uint32_t>(i / kStages) & 1u);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue ----------------
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc<BN>();
+            bool ok = true;
+            for (int i = 0; i < num_kb && ok; ++i) {
+                const int s = i % kStages;
+                const uint32_t round = static_cast<uint32_t>(i / kStages);
+                if (*abort_flag || !gemm_wait(&full_split[s], round & 1u)) {
+                    atomicOr(p.status, kStatusGemmTimeout);
+                    *abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_hi = smem_u32(stage_ptr(s));
+                const uint32_t a_lo = a_hi + kTileABytes;
+                const uint32_t b_hi = a_hi + 2 * kTileABytes;
+                const uint32_t b_lo = b_hi + T::kTileBBytes;
+#pragma unroll
+                for (int kk = 0; kk < BK / 8; ++kk) {
+                    const uint32_t off = kk * 32;   // 8 TF32 values along k
+                    const uint64_t dah = operand_desc(a_hi + off), dal = operand_desc(a_lo + off);
+                    const uint64_t dbh = operand_desc(b_hi + off), dbl = operand_desc(b_lo + off);
+                    mma_tf32(tmem_base, dal, dbh, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+                    mma_tf32(tmem_base, dah, dbl, idesc, 1u);
+                    mma_tf32(tmem_base, dah, dbh, idesc, 1u);
+                }
+                mma_commit(&empty[s]);   // arrives when these MMAs no longer read the stage
+            }
+            if (ok) mma_commit(accum_full);
+        }
+    } else {
+        // ---------------- splitters, then epilogue ----------------
+        const int t = threadIdx.x - 64;          // 0..127
+        bool ok = true;
+        for (int i = 0; i < num_kb && ok; ++i) {
+            const int s = i % kStages;
+            const uint32_t round = static_cast<uint32_t>(i / kStages);
+            if (*abort_flag || !gemm_wait(&full_raw[s], round & 1u)) {
+                if (lane == 0) atomicOr(p.status, kStatusGemmTimeout);
+                *abort_flag = 1;
+                ok = false;
+                break;
+            }
+            uint8_t* st = stage_ptr(s);
+            // A: raw at st, lo at st + 16 KiB; B: raw at st + 32 KiB, lo right after it
+            auto split = [&](uint8_t* raw, uint8_t* lo_buf, int vecs) {
+#pragma unroll 4
+                for (int v = t; v < vecs; v += 128) {
+                    uint4 x = *reinterpret_cast<uint4*>(raw + v * 16);
+                    uint4 hi, lo;
+                    hi.x = x.x & 0xffffe000u;
+                    hi.y = x.y & 0xffffe000u;
+                    hi.z = x.z & 0xffffe000u;
+                    hi.w = x.w & 0xffffe000u;
+                    lo.x = __float_as_uint(__uint_as_float(x.x) - __uint_as_float(hi.x));
+                    lo.y = __float_as_uint(__uint_as_float(x.y) - __uint_as_float(hi.y));
+                    lo.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(hi.z));
+                    lo.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(hi.w));
+                    *reinterpret_cast<uint4*>(raw + v * 16) = hi;
+                    *reinterpret_cast<uint4*>(lo_buf + v * 16) = lo;
+                }
+            };
+            split(st, st + kTileABytes, kTileABytes / 16);
+            split(st + 2 * kTileABytes, st + 2 * kTileABytes + T::kTileBBytes, T::kTileBBytes / 16);
+            // make the generic-proxy writes visible to the tensor core's reads
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_split[s]);
+        }
+        if (ok && !gemm_wait(accum_full, 0)) {
+            if (lane == 0) atomicOr(p.status, kStatusGemmTimeout);
+            *abort_flag = 1;
+            ok = false;
+        }
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int q = warp & 3;                       // tensor-memory lane quarter of this warp
+            const int m = m0 + 32 * q + lane;
+            const bool vec_ok = (p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_load_32(tmem_base + (static_cast<uint32_t>(32 * q) << 16) + c * 32, r);
+                if (m >= p.M) continue;
+                const int n_first = n0 + c * 32;
+                float* row = p.C + static_cast<long long>(m) * p.ldc;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    const int n = n_first + j;
+                    if (n >= p.N) break;
+                    float v[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        v[e] = __uint_as_float(r[j + e]);
+                        if (p.bias != nullptr && n + e < p.N) v[e] += p.bias[n + e];
+                    }
+                    if (vec_ok && n + 3 < p.N) {
+                        if (p.reduce) red_add_f32x4(row + n, v[0], v[1], v[2], v[3]);
+                        else *reinterpret_cast<float4*>(row + n) = make_float4(v[0], v[1], v[2], v[3]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            if (n + e < p.N) {
+                                if (p.reduce) atomicAdd(row + n + e, v[e]);
+                                else row[n + e] = v[e];
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(static_cast<uint32_t>(BN))
+                     : "memory");
+    }
+}
+
+// ------------------------------- host side -------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+std::atomic<EncodeTiledFn> g_encode{nullptr};
+
+cudaError_t encode_fn(EncodeTiledFn* out) {
+    EncodeTiledFn fn = g_encode.load(std::memory_order_acquire);
+    if (fn == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q);
+        if (e != cudaSuccess) return e;
+        if (q != cudaDriverEntryPointSuccess || sym == nullptr) return cudaErrorNotSupported;
+        fn = reinterpret_cast<EncodeTiledFn>(sym);
+        g_encode.store(fn, std::memory_order_release);
+    }
+    *out = fn;
+    return cudaSuccess;
+}
+
+// [rows, K] fp32 matrix with k contiguous -> map with boxes of (BK k) x (box_rows rows)
+cudaError_t make_map(CUtensorMap* map, const float* base, long long row_stride, int rows, int K,
+                     int box_rows) {
+    EncodeTiledFn fn = nullptr;
+    cudaError_t e = encode_fn(&fn);
+    if (e != cudaSuccess) return e;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_stride) * 4};
+    const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims,
+                          strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+template <int BN>
+cudaError_t launch(const GemmArgs& g, int splits, int* status, cudaStream_t stream) {
+    static std::atomic<int> configured{0};
+    if (!configured.load(std::memory_order_acquire)) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             Tile<BN>::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured.store(1, std::memory_order_release);
+    }
+    CUtensorMap map_a, map_b;
+    cudaError_t e = make_map(&map_a, g.A, g.a_row, g.M, g.K, BM);
+    if (e != cudaSuccess) return e;
+    e = make_map(&map_b, g.B, g.b_row, g.N, g.K, BN);
+    if (e != cudaSuccess) return e;
+    const int kb_total = (g.K + BK - 1) / BK;
+    if (splits < 1) splits = 1;
+    if (splits > kb_total) splits = kb_total;
+    TcParams p;
+    p.C = g.C;
+    p.ldc = g.ldc;
+    p.bias = g.bias;
+    p.M = g.M;
+    p.N = g.N;
+    p.K = g.K;
+    p.kb_per_split = (kb_total + splits - 1) / splits;
+    p.reduce = splits > 1 ? 1 : 0;
+    p.status = status;
+    const dim3 grid((g.M + BM - 1) / BM, (g.N + BN - 1) / BN,
+                    (kb_total + p.kb_per_split - 1) / p.kb_per_split);
+    gemm_tc_kernel<BN><<<grid, kGemmThreads, Tile<BN>::kSmemBytes, stream>>>(map_a, map_b, p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool gemm_tc_supported(const GemmArgs& g) {
+    if (g.M <= 0 || g.N <= 0 || g.K <= 0) return false;
+    if (g.a_k != 1 || g.b_k != 1) return false;
+    if (g.a_row % 4 != 0 || g.b_row % 4 != 0) return false;
+    if ((reinterpret_cast<uintptr_t>(g.A) | reinterpret_cast<uintptr_t>(g.B)) % 16 != 0) return false;
+    if (g.a_row * 4 >= (1ll << 40) || g.b_row * 4 >= (1ll << 40)) return false;
+    return true;
+}
+
+cudaError_t gemm_tc(const GemmArgs& g, int splits, int* status_word, cudaStream_t stream) {
+    if (!gemm_tc_supported(g) || status_word == nullptr) return cudaErrorInvalidValue;
+    if (splits > 1 && g.bias != nullptr) return cudaErrorInvalidValue;
+    if (g.N > 128 + 64) return launch<256>(g, splits, status_word, stream);
+    if (g.N > 64 + 32) return launch<128>(g, splits, status_word, stream);
+    return launch<64>(g, splits, status_word, stream);
+}
+
+}  // namespace msda

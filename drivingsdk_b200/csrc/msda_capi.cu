@@ -287,6 +287,14 @@ int forward_impl(const void* value, const int32_t* spatial_shapes,
 namespace msda {
 void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 int note_cuda_error(cudaError_t e) { return fail_cuda(e); }
+int device_facts(int* sm_count, int** status_word) {
+    const DeviceInfo* d = nullptr;
+    const int rc = device_info(&d);
+    if (rc != MSDA_OK) return rc;
+    if (sm_count != nullptr) *sm_count = d->sm_count;
+    if (status_word != nullptr) *status_word = d->status_ptr;
+    return MSDA_OK;
+}
 }  // namespace msda
 
 extern "C" {

@@ -70,6 +70,11 @@ void count_launches(int n);
 // returns MSDA_ERR_CUDA.
 int note_cuda_error(cudaError_t e);
 
+// SM count of the current device and the device address of the library's sticky status word
+// (msda_sm100_device_status reads and clears it); either pointer may be null. Returns an
+// msda_status value.
+int device_facts(int* sm_count, int** status_word);
+
 // out[i] = (T)acc[i] for n elements; dtype 1 = fp16, 2 = bf16.
 cudaError_t launch_downcast(const float* acc, void* out, long long n, int dtype,
                             cudaStream_t stream);

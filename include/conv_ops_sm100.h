@@ -47,6 +47,80 @@ int addrelu_sm100_backward(const void* out, const void* grad_out, void* grad_in,
 int maxpool_sm100_forward(const void* x, void* y, int N, int C, int H, int W, int dtype,
                           void* stream);
 
+/*
+ * Deformable and modulated deformable 2-D convolution (DCNv1 / DCNv2), fp32, channels-last
+ * tensors as the reference's extension takes them (mx_driving/ops/deform_conv2d.py:42-44):
+ *   x       [N, H, W, C]
+ *   offset  [N, Ho, Wo, deform_groups * 2 * kh * kw]   per tap (dy, dx)
+ *   mask    [N, Ho, Wo, deform_groups * kh * kw]       or NULL (plain deformable convolution)
+ *   weight  [Co, kh, kw, C / groups]
+ *   bias    [Co] or NULL
+ *   out     [N, Ho, Wo, Co]
+ *   columns [N * Ho * Wo, groups, kh * kw, C / groups]  the sampled (and modulated) input,
+ *           the reference's `offset_output`; written by the forward, read by the backward.
+ * Ho, Wo follow from the offset tensor; they must equal the convolution's output size for the
+ * given stride, padding and dilation. Rows move as 16-byte pieces when C / deform_groups and
+ * C / groups are multiples of 4 (x and columns then have to be 16-byte aligned), else float
+ * by float.
+ */
+typedef struct dcn_shape {
+    int N, H, W, C;
+    int Ho, Wo, Co;
+    int kh, kw;
+    int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+    int groups, deform_groups;
+} dcn_shape;
+
+/* Bytes of the `columns` tensor for this shape (0 when the shape is invalid). */
+size_t dcn_sm100_columns_bytes(const dcn_shape* s);
+
+/*
+ * Bytes of scratch memory dcn_sm100_backward needs (the gradient of `columns`, plus
+ * transposed operands for the tensor-core products).
+ */
+size_t dcn_sm100_backward_workspace_bytes(const dcn_shape* s);
+
+/*
+ * Forward. Replaces aclnnDeformableConv2d with modulated = false / true
+ * (mx_driving/csrc/DeformableConv2d.cpp:59-60, ModulatedDeformableConv2d.cpp:70-71), i.e. the
+ * gather of kernels/deformable_conv2d/op_kernel/deformable_conv2d.cpp:223-420 followed by the
+ * per-group matrix product (:206-221). `columns` must hold dcn_sm100_columns_bytes().
+ */
+int dcn_sm100_forward(const float* x, const float* offset, const float* mask, const float* weight,
+                      const float* bias, float* out, float* columns, const dcn_shape* s,
+                      void* stream);
+
+/*
+ * Backward. Replaces aclnnDeformableConv2dGrad (mx_driving/csrc/DeformableConv2d.cpp:92-94,
+ * ModulatedDeformableConv2d.cpp:127-130). `columns` is what the forward wrote. Gradients
+ * have the layouts of their tensors; grad_mask is required iff mask is given; grad_bias may
+ * be NULL. grad_x, grad_weight and grad_bias are overwritten (zero-filled here first).
+ */
+int dcn_sm100_backward(const float* x, const float* offset, const float* mask,
+                       const float* weight, const float* columns, const float* grad_out,
+                       float* grad_x, float* grad_offset, float* grad_mask, float* grad_weight,
+                       float* grad_bias, void* workspace, size_t workspace_bytes,
+                       const dcn_shape* s, void* stream);
+
+/*
+ * Which matrix-product kernels the two calls above use: 1 (default) = the tcgen05 kernel
+ * (fp32 operands split into two TF32 parts, three tensor-core products per tile, fp32
+ * accumulation in tensor memory) where the shape allows it; 0 = the plain fp32 FMA kernel
+ * everywhere. Returns the previous setting; any other value only queries.
+ */
+int dcn_sm100_use_tensor_cores(int on);
+
+/*
+ * The matrix product underneath, exposed for tests and benchmarks:
+ *   C[m, n] = sum_k A[m * lda + k] * B[n * ldb + k] (+ bias[n]),  C row stride ldc.
+ * Uses the tcgen05 kernel when dcn_sm100_use_tensor_cores is on and A, B are 16-byte aligned
+ * with lda, ldb multiples of 4, else the fp32 FMA kernel. splits > 1 cuts K across CTAs
+ * (tcgen05 kernel only; C is zero-filled first, bias must be NULL). No reference counterpart.
+ */
+int gemm_nt_sm100_f32(const float* A, long long lda, const float* B, long long ldb, float* C,
+                      long long ldc, const float* bias, int M, int N, int K, int splits,
+                      void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,65 @@
+"""The matrix product under the deformable convolution: tcgen05 kernel (3 x TF32) and fp32 FMA
+kernel against a float64 product of the same fp32 inputs. The bar is fp32-class accuracy: max
+error <= 2e-5 of the largest |C| for the FMA kernel and <= 5e-5 for the tensor-core kernel
+(its fp32 accumulator in tensor memory does not round to nearest; measured 2.1e-5 at K = 2304).
+A single-pass TF32 product would miss either bar by more than 10x."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [
+    # M, N, K, lda_extra, ldb_extra
+    (128, 64, 32, 0, 0),
+    (128, 256, 256, 0, 0),
+    (1, 8, 8, 0, 0),
+    (130, 72, 40, 0, 4),
+    (300, 200, 100, 8, 0),
+    (1000, 512, 1152, 0, 0),
+    (517, 96, 2304, 4, 4),
+    (64, 4608, 520, 0, 0),
+]
+
+
+def run(M, N, K, ea, eb, tensor_cores, splits=1, bias=False):
+    from drivingsdk_b200 import capi
+    lib = capi.load()
+    g = torch.Generator().manual_seed(M * 7 + N * 3 + K)
+    A = torch.randn(M, K + ea, generator=g).cuda()
+    B = torch.randn(N, K + eb, generator=g).cuda()
+    b = torch.randn(N, generator=g).cuda() if bias else None
+    C = torch.full((M, N), float("nan"), device="cuda")
+    old = lib.dcn_sm100_use_tensor_cores(tensor_cores)
+    try:
+        capi.check(lib.gemm_nt_sm100_f32(A.data_ptr(), K + ea, B.data_ptr(), K + eb, C.data_ptr(), N,
+                                         b.data_ptr() if bias else None, M, N, K, splits,
+                                         torch.cuda.current_stream().cuda_stream), "gemm")
+    finally:
+        lib.dcn_sm100_use_tensor_cores(old)
+    torch.cuda.synchronize()
+    assert lib.msda_sm100_device_status(1) == 0
+    want = A[:, :K].double() @ B[:, :K].double().t()
+    if bias:
+        want = want + b.double()
+    err = (C.double() - want).abs().max().item()
+    return err, want.abs().max().item()
+
+
+@pytest.mark.parametrize("tensor_cores", [0, 1])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_product_has_fp32_accuracy(shape, tensor_cores):
+    err, scale = run(*shape, tensor_cores)
+    assert err <= (5e-5 if tensor_cores else 2e-5) * scale, (err, scale)
+
+
+@pytest.mark.parametrize("splits", [2, 5])
+def test_k_split_across_ctas(splits):
+    err, scale = run(256, 384, 4096, 0, 0, 1, splits=splits)
+    assert err <= 5e-5 * scale, (err, scale)
+
+
+@pytest.mark.parametrize("tensor_cores", [0, 1])
+def test_bias_is_added_per_column(tensor_cores):
+    err, scale = run(200, 136, 64, 0, 0, tensor_cores, bias=True)
+    assert err <= 5e-5 * scale, (err, scale)
