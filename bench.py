@@ -46,10 +46,15 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--op", default="msda", choices=["msda", "fused", "gka", "da"],
+    ap.add_argument("--op", default="msda", choices=["msda", "fused", "gka", "da", "dcn", "addrelu", "maxpool"],
                     help="msda (the headline path, default); fused: MSDA with its callers' softmax and "
                          "location arithmetic inside; gka / da: the sibling operators geometric "
-                         "kernel attention / deformable aggregation; these three on one GPU")
+                         "kernel attention / deformable aggregation; dcn / addrelu / maxpool: modulated "
+                         "deformable convolution, add+ReLU, stem max pooling (the operators "
+                         "behind the other default patches); all of these on one GPU")
+    ap.add_argument("--tensor-cores", type=int, default=1, choices=[0, 1, 2],
+                    help="--op dcn: 1 = tcgen05 3xTF32 products (default), 2 = tcgen05 single "
+                         "TF32 product, 0 = fp32 FMA kernel")
     ap.add_argument("--workload", default="bevformer_sca")
     ap.add_argument("--dtype", default="float32", choices=["float32", "float16", "bfloat16"])
     ap.add_argument("--shard", default="batch", choices=["batch", "query"])
@@ -654,9 +659,185 @@ def run_sibling(args):
     print(json.dumps(line))
 
 
+def load_tensor_peak():
+    """Dense TF32 TFLOP/s for the roofline of the tensor-core products: half the measured
+    bf16 burst figure (TF32 issues at half the bf16 rate), else half the fallback."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]) / 2, "measured bf16 / 2"
+    except Exception:
+        return 1590.0 / 2, "fallback bf16 / 2"
+
+
+def run_conv_side(args):
+    """One-GPU timing, through the C ABI with operands in HBM, of the operators behind the
+    other default patches: modulated deformable convolution (--op dcn, forward + backward at
+    the shape of the reference's unit test, tests/torch/test_deformable_conv2d.py:59), add+ReLU
+    with its gradient (--op addrelu, tests/torch/test_add_relu.py:42) and the ResNet stem's
+    max pooling (--op maxpool, tests/torch/test_npu_max_pool2d.py:33)."""
+    import ctypes
+    import numpy as np
+    import torch
+    from drivingsdk_b200 import capi
+
+    lib = capi.load()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(2468)
+    stream = torch.cuda.current_stream()
+    st = stream.cuda_stream
+    u = lambda lo, hi, *shape: (torch.rand(*shape, generator=g) * (hi - lo) + lo).to(dev)
+    hbm_peak, hbm_kind = load_peaks()
+    bwd = None
+    if args.op == "dcn":
+        from oracle import dcn_oracle
+        N, C, Co, H, W, k = 18, 512, 512, 29, 50, 3
+        shape = capi.DcnShape(N, H, W, C, H, W, Co, k, k, 1, 1, 1, 1, 1, 1, 1, 1)
+        M, Kd = N * H * W, k * k * C
+        x, off = u(-5, 5, N, H, W, C), u(-2, 2, N, H, W, 2 * k * k)
+        mask, w = u(-5, 5, N, H, W, k * k), u(-0.05, 0.05, Co, k, k, C)
+        go = u(-5, 5, N, H, W, Co)
+        out = torch.empty(N, H, W, Co, device=dev)
+        cols = torch.empty(lib.dcn_sm100_columns_bytes(ctypes.byref(shape)) // 4, device=dev)
+        ws_bytes = lib.dcn_sm100_backward_workspace_bytes(ctypes.byref(shape))
+        ws = torch.empty(ws_bytes // 4 + 4, device=dev)
+        gx, goff, gmask, gw = (torch.empty_like(t) for t in (x, off, mask, w))
+        old_tc = lib.dcn_sm100_use_tensor_cores(args.tensor_cores)
+
+        def fwd():
+            capi.check(lib.dcn_sm100_forward(x.data_ptr(), off.data_ptr(), mask.data_ptr(),
+                                             w.data_ptr(), None, out.data_ptr(), cols.data_ptr(),
+                                             ctypes.byref(shape), st), "dcn fwd")
+
+        def bwd():
+            capi.check(lib.dcn_sm100_backward(
+                x.data_ptr(), off.data_ptr(), mask.data_ptr(), w.data_ptr(), cols.data_ptr(),
+                go.data_ptr(), gx.data_ptr(), goff.data_ptr(), gmask.data_ptr(), gw.data_ptr(), None,
+                ws.data_ptr(), ws_bytes, ctypes.byref(shape), st), "dcn bwd")
+
+        def cpu_once():
+            nchw = lambda t, n=1: t[:n].permute(0, 3, 1, 2).cpu().numpy()
+            wn = w.permute(0, 3, 1, 2).cpu().numpy()
+            dcn_oracle.forward(nchw(x), nchw(off), nchw(mask), wn, None, 1, 1, 1)
+            dcn_oracle.backward(nchw(x), nchw(off), nchw(mask), wn, nchw(go), 1, 1, 1)
+        samples, cpu_samples = N, 1
+        gemm_flops = 2.0 * M * Co * Kd
+        peak, peak_kind = load_tensor_peak()
+        bound, roof_unit, scale = "tensor", "TFLOP/s", 1e12
+        work_fwd, work_bwd = gemm_flops, 2 * gemm_flops
+        # operands and results once; the columns tensor once out (forward), once in (backward)
+        nx, no, nw, nc, ns = x.numel(), out.numel(), w.numel(), cols.numel(), off.numel() + mask.numel()
+        hbm_bytes = {"forward": 4 * (nx + ns + nw + no + nc),
+                     "backward": 4 * (2 * nx + 2 * ns + 2 * nw + no + nc)}
+        config = {"workload": "modulated_dcn_test_shape", "N": N, "C": C, "Co": Co, "H": H, "W": W,
+                  "kernel": k, "groups": 1, "deform_groups": 1,
+                  "products": ["fp32 FMA", "tcgen05 3xTF32", "tcgen05 1xTF32"][args.tensor_cores]}
+        kernel_name = "three matrix products (forward, grad_columns, grad_weight)"
+    elif args.op == "addrelu":
+        shape_t = (18, 256, 232, 100)
+        x, y = u(-1, 1, *shape_t), u(-1, 1, *shape_t)
+        go, gi = u(-1, 1, *shape_t), torch.empty(shape_t, device=dev)
+        n = x.numel()
+
+        def fwd():
+            capi.check(lib.addrelu_sm100_forward(x.data_ptr(), y.data_ptr(), n, capi.F32, st), "addrelu")
+
+        def bwd():
+            capi.check(lib.addrelu_sm100_backward(x.data_ptr(), go.data_ptr(), gi.data_ptr(), n,
+                                                  capi.F32, st), "addrelu grad")
+
+        def cpu_once():
+            a, b = x[:1].cpu().numpy(), y[:1].cpu().numpy()
+            r = np.maximum(a + b, 0)
+            np.where(r > 0, go[:1].cpu().numpy(), 0)
+        samples, cpu_samples = shape_t[0], 1
+        peak, peak_kind = hbm_peak, hbm_kind
+        bound, roof_unit, scale = "hbm", "GB/s", 1e9
+        work_fwd, work_bwd = 12.0 * n, 12.0 * n
+        hbm_bytes = {"forward": 12 * n, "backward": 12 * n}
+        config = {"workload": "add_relu_test_shape", "shape": list(shape_t)}
+        kernel_name = "add+relu gradient kernel"
+    else:
+        shape_t = (18, 64, 464, 800)
+        x = u(0, 1, *shape_t)
+        y = torch.empty(shape_t[0], shape_t[1], (shape_t[2] + 1) // 2, (shape_t[3] + 1) // 2, device=dev)
+
+        def fwd():
+            capi.check(lib.maxpool_sm100_forward(x.data_ptr(), y.data_ptr(), *shape_t, capi.F32, st),
+                       "maxpool")
+
+        def cpu_once():
+            torch.nn.functional.max_pool2d(x[:1].cpu(), 3, 2, 1)
+        samples, cpu_samples = shape_t[0], 1
+        peak, peak_kind = hbm_peak, hbm_kind
+        bound, roof_unit, scale = "hbm", "GB/s", 1e9
+        work_fwd, work_bwd = 4.0 * (x.numel() + y.numel()), 0.0
+        hbm_bytes = {"forward": 4 * (x.numel() + y.numel())}
+        config = {"workload": "resnet_stem_maxpool_test_shape", "shape": list(shape_t),
+                  "note": "inference only, as in the reference"}
+        kernel_name = "maxpool3s2 kernel"
+
+    def step():
+        fwd()
+        if bwd is not None:
+            bwd()
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    K_steps = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K_steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = lib.msda_sm100_launch_count()
+    e0.record(stream)
+    for i in range(K_steps):
+        ev[i][0].record(stream)
+        fwd()
+        ev[i][1].record(stream)
+        if bwd is not None:
+            bwd()
+        ev[i][2].record(stream)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / K_steps
+    fwd_ms = sum(q[0].elapsed_time(q[1]) for q in ev) / K_steps
+    bwd_ms = sum(q[1].elapsed_time(q[2]) for q in ev) / K_steps
+    main_ms, main_work = (bwd_ms, work_bwd) if bwd is not None else (fwd_ms, work_fwd)
+    roof = {"bound": bound, "kernel": kernel_name,
+            "achieved": main_work / (main_ms * 1e-3) / scale, "peak": peak, "unit": roof_unit,
+            "frac": main_work / (main_ms * 1e-3) / scale / peak, "traffic": None,
+            "peak_kind": peak_kind, "kernel_ms": main_ms,
+            "forward": {"achieved": work_fwd / (fwd_ms * 1e-3) / scale,
+                        "frac": work_fwd / (fwd_ms * 1e-3) / scale / peak, "kernel_ms": fwd_ms},
+            "step": {"frac": (work_fwd + work_bwd) / (ms * 1e-3) / scale / peak},
+            "hbm_algorithmic_bytes": hbm_bytes}
+    if args.op == "dcn":
+        roof["note"] = ("achieved counts each fp32 product once (2*M*N*K); with --tensor-cores 1 "
+                        "the tensor cores execute three TF32 products for it")
+        lib.dcn_sm100_use_tensor_cores(old_tc)
+    line = {
+        "metric": f"{args.op}_samples_per_s", "value": samples / (ms * 1e-3), "unit": UNIT,
+        "n_gpus": 1, "steps": K_steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": config, "roofline": roof,
+        "gpu_launches": int(lib.msda_sm100_launch_count() - launches0),
+        "device_status": int(lib.msda_sm100_device_status(1)),
+    }
+    if not args.no_cpu_baseline:
+        t0 = time.perf_counter()
+        cpu_once()
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": cpu_samples / dt, "unit": UNIT, "cores": os.cpu_count() or 1,
+                                "kind": "port",
+                                "sample": "1 batch entry through the numpy/torch CPU restatement"}
+    print(json.dumps(line))
+
+
 def main():
     args = parse_args()
-    if args.op != "msda":
+    if args.op in ("dcn", "addrelu", "maxpool"):
+        run_conv_side(args)
+    elif args.op != "msda":
         run_sibling(args)
     elif args.impl == "reference":
         run_reference_arm(args)

@@ -347,8 +347,9 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) % 16) == 
 // One product, on the tensor cores when allowed and possible.
 int product(const msda::GemmArgs& g, int splits, int* status_word, cudaStream_t stream) {
     cudaError_t e;
-    if (g_use_tc.load(std::memory_order_relaxed) != 0 && msda::gemm_tc_supported(g)) {
-        e = msda::gemm_tc(g, splits, status_word, stream);
+    const int mode = g_use_tc.load(std::memory_order_relaxed);
+    if (mode != 0 && msda::gemm_tc_supported(g)) {
+        e = msda::gemm_tc(g, splits, mode == 2 ? 1 : 3, status_word, stream);
     } else {
         e = msda::gemm_simt(g, stream);
     }
@@ -385,7 +386,7 @@ Workspace plan_workspace(const dcn_shape* s, const Derived& d) {
 extern "C" {
 
 int dcn_sm100_use_tensor_cores(int on) {
-    if (on == 0 || on == 1) return g_use_tc.exchange(on, std::memory_order_relaxed);
+    if (on >= 0 && on <= 2) return g_use_tc.exchange(on, std::memory_order_relaxed);
     return g_use_tc.load(std::memory_order_relaxed);
 }
 

@@ -24,11 +24,13 @@ cudaError_t gemm_simt(const GemmArgs& g, cudaStream_t stream);
 
 // tcgen05 kernel: operands with k contiguous (a_k == b_k == 1), 16-byte aligned bases, row
 // strides that are multiples of 4 elements. fp32 accuracy through a two-term TF32 split of
-// both operands (three tensor-core products per tile). `splits` > 1 cuts K into that many
+// both operands (passes == 3: three tensor-core products per tile), or one TF32 product per
+// tile (passes == 1, about 1e-3 relative accuracy). `splits` > 1 cuts K into that many
 // parts whose partial results are added into C with reductions; C must be zero before, and
 // bias must be null. Overwrites C when splits == 1.
 bool gemm_tc_supported(const GemmArgs& g);
-cudaError_t gemm_tc(const GemmArgs& g, int splits, int* status_word, cudaStream_t stream);
+cudaError_t gemm_tc(const GemmArgs& g, int splits, int passes, int* status_word,
+                    cudaStream_t stream);
 
 // out[c, r] = in[r, c] for an R x Cc matrix (row strides ld_in, ld_out, in elements).
 cudaError_t transpose_f32(const float* in, long long ld_in, float* out, long long ld_out, int R,

@@ -10,15 +10,17 @@
 // One CTA computes one 128 x BN tile of C (BN = 64, 128 or 256) over its share of K, in steps
 // of 32 k (one 128-byte swizzled row per operand row):
 //   warp 0        producer: one lane issues the two TMA tile loads of a stage
-//   warps 2..5    splitters: turn the raw tile in shared memory into its hi part (in place)
-//                 and its lo part (second buffer at the same offsets, so the swizzle pattern
-//                 does not matter), then hand the stage to the MMA warp; afterwards they are
+//   warps 2..5    splitters: write the lo part of the raw tile into a second buffer at the same
+//                 offsets (so the swizzle pattern does not matter; the raw tile itself serves
+//                 as the hi part because the tensor core ignores the low 13 mantissa bits),
+//                 then hand the stage to the MMA warp; afterwards they are
 //                 the epilogue: tcgen05.ld of the accumulator (warp q reads lanes 32q..32q+31),
 //                 bias, stores (or reductions when K is cut across CTAs)
 //   warp 1        MMA: one lane issues 4 k-slices x 3 products of tcgen05.mma per stage and
 //                 commits the stage's "empty" barrier; owns the tensor-memory allocation
 // Out-of-range parts of a tile (M, N or K tails) are zero-filled by TMA and masked in the
-// epilogue. Every barrier wait is bounded: on a timeout the CTA raises the library's sticky
+// epilogue. A single-product mode (PASSES == 1) skips the split and uses the freed shared
+// memory for twice as many stages. Every barrier wait is bounded: on a timeout the CTA raises the library's sticky
 // status word, stops issuing work, waits (bounded) for its own copies, frees its tensor memory
 // and returns.
 #include <cuda.h>
@@ -40,11 +42,13 @@ constexpr int kTileABytes = BM * BK * 4;    // 16 KiB
 constexpr int kStatusGemmTimeout = 2;       // bit in the sticky status word
 constexpr int kWaitLimit = 1 << 22;
 
-template <int BN>
+// A stage holds the raw A and B tiles and, for the three-product mode, their lo parts.
+template <int BN, int PASSES>
 struct Tile {
     static constexpr int kTileBBytes = BN * BK * 4;
-    static constexpr int kStageBytes = 2 * kTileABytes + 2 * kTileBBytes;
-    static constexpr int kStages = (BN == 256) ? 2 : (BN == 128 ? 3 : 4);
+    static constexpr int kStageBytes = (PASSES == 3 ? 2 : 1) * (kTileABytes + kTileBBytes);
+    static constexpr int kFit = (192 * 1024) / kStageBytes;
+    static constexpr int kStages = kFit > 8 ? 8 : kFit;
     // + barriers and the tensor-memory address, + slack to align the tiles to 1 KiB
     static constexpr int kSmemBytes = kStages * kStageBytes + 256 + 1024;
 };
@@ -138,11 +142,12 @@ struct TcParams {
     int* status;
 };
 
-template <int BN>
+// PASSES == 3: hi/lo split, fp32-class accuracy; PASSES == 1: one TF32 product per tile.
+template <int BN, int PASSES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const TcParams p) {
-    using T = Tile<BN>;
+    using T = Tile<BN, PASSES>;
     constexpr int kStages = T::kStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base_u32 = smem_u32(smem_raw);
@@ -202,7 +207,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 mbar_expect_tx(&full_raw[s], kTileABytes + T::kTileBBytes);
                 const int k0 = (kb_begin + i) * BK;
                 tma_load_2d(st, &map_a, k0, m0, &full_raw[s]);
-                tma_load_2d(st + 2 * kTileABytes, &map_b, k0, n0, &full_raw[s]);
+                tma_load_2d(st + kTileABytes, &map_b, k0, n0, &full_raw[s]);
                 issued = i + 1;
             }
             if (*abort_flag) {
@@ -227,17 +232,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a_hi = smem_u32(stage_ptr(s));
-                const uint32_t a_lo = a_hi + kTileABytes;
-                const uint32_t b_hi = a_hi + 2 * kTileABytes;
-                const uint32_t b_lo = b_hi + T::kTileBBytes;
+                const uint32_t b_hi = a_hi + kTileABytes;
+                const uint32_t a_lo = b_hi + T::kTileBBytes;   // only present when PASSES == 3
+                const uint32_t b_lo = a_lo + kTileABytes;
 #pragma unroll
                 for (int kk = 0; kk < BK / 8; ++kk) {
                     const uint32_t off = kk * 32;   // 8 TF32 values along k
                     const uint64_t dah = operand_desc(a_hi + off), dal = operand_desc(a_lo + off);
                     const uint64_t dbh = operand_desc(b_hi + off), dbl = operand_desc(b_lo + off);
-                    mma_tf32(tmem_base, dal, dbh, idesc, (i > 0 || kk > 0) ? 1u : 0u);
-                    mma_tf32(tmem_base, dah, dbl, idesc, 1u);
-                    mma_tf32(tmem_base, dah, dbh, idesc, 1u);
+                    const uint32_t fresh = (i > 0 || kk > 0) ? 1u : 0u;
+                    if (PASSES == 3) {
+                        mma_tf32(tmem_base, dal, dbh, idesc, fresh);
+                        mma_tf32(tmem_base, dah, dbl, idesc, 1u);
+                        mma_tf32(tmem_base, dah, dbh, idesc, 1u);
+                    } else {
+                        // the tensor core reads the upper 19 bits of each fp32 operand
+                        mma_tf32(tmem_base, dah, dbh, idesc, fresh);
+                    }
                 }
                 mma_commit(&empty[s]);   // arrives when these MMAs no longer read the stage
             }
@@ -257,28 +268,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 break;
             }
             uint8_t* st = stage_ptr(s);
-            // A: raw at st, lo at st + 16 KiB; B: raw at st + 32 KiB, lo right after it
-            auto split = [&](uint8_t* raw, uint8_t* lo_buf, int vecs) {
+            // The tensor core uses the upper 19 bits of an fp32 operand (sign, exponent, 10
+            // mantissa bits) and ignores the rest, so the raw tile already acts as the hi part;
+            // only lo = v - hi has to be produced.
+            auto split = [&](const uint8_t* raw, uint8_t* lo_buf, int vecs) {
 #pragma unroll 4
                 for (int v = t; v < vecs; v += 128) {
-                    uint4 x = *reinterpret_cast<uint4*>(raw + v * 16);
-                    uint4 hi, lo;
-                    hi.x = x.x & 0xffffe000u;
-                    hi.y = x.y & 0xffffe000u;
-                    hi.z = x.z & 0xffffe000u;
-                    hi.w = x.w & 0xffffe000u;
-                    lo.x = __float_as_uint(__uint_as_float(x.x) - __uint_as_float(hi.x));
-                    lo.y = __float_as_uint(__uint_as_float(x.y) - __uint_as_float(hi.y));
-                    lo.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(hi.z));
-                    lo.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(hi.w));
-                    *reinterpret_cast<uint4*>(raw + v * 16) = hi;
+                    const uint4 x = *reinterpret_cast<const uint4*>(raw + v * 16);
+                    uint4 lo;
+                    lo.x = __float_as_uint(__uint_as_float(x.x) - __uint_as_float(x.x & 0xffffe000u));
+                    lo.y = __float_as_uint(__uint_as_float(x.y) - __uint_as_float(x.y & 0xffffe000u));
+                    lo.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(x.z & 0xffffe000u));
+                    lo.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(x.w & 0xffffe000u));
                     *reinterpret_cast<uint4*>(lo_buf + v * 16) = lo;
                 }
             };
-            split(st, st + kTileABytes, kTileABytes / 16);
-            split(st + 2 * kTileABytes, st + 2 * kTileABytes + T::kTileBBytes, T::kTileBBytes / 16);
-            // make the generic-proxy writes visible to the tensor core's reads
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            if (PASSES == 3) {
+                // raw A and B are contiguous, and so are their lo parts behind them
+                split(st, st + kTileABytes + T::kTileBBytes, (kTileABytes + T::kTileBBytes) / 16);
+                // make the generic-proxy writes visible to the tensor core's reads
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(&full_split[s]);
         }
@@ -375,13 +385,13 @@ cudaError_t make_map(CUtensorMap* map, const float* base, long long row_stride, 
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <int BN>
+template <int BN, int PASSES>
 cudaError_t launch(const GemmArgs& g, int splits, int* status, cudaStream_t stream) {
     static std::atomic<int> configured{0};
     if (!configured.load(std::memory_order_acquire)) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, PASSES>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             Tile<BN>::kSmemBytes);
+                                             Tile<BN, PASSES>::kSmemBytes);
         if (e != cudaSuccess) return e;
         configured.store(1, std::memory_order_release);
     }
@@ -405,7 +415,7 @@ cudaError_t launch(const GemmArgs& g, int splits, int* status, cudaStream_t stre
     p.status = status;
     const dim3 grid((g.M + BM - 1) / BM, (g.N + BN - 1) / BN,
                     (kb_total + p.kb_per_split - 1) / p.kb_per_split);
-    gemm_tc_kernel<BN><<<grid, kGemmThreads, Tile<BN>::kSmemBytes, stream>>>(map_a, map_b, p);
+    gemm_tc_kernel<BN, PASSES><<<grid, kGemmThreads, Tile<BN, PASSES>::kSmemBytes, stream>>>(map_a, map_b, p);
     return cudaGetLastError();
 }
 
@@ -420,12 +430,22 @@ bool gemm_tc_supported(const GemmArgs& g) {
     return true;
 }
 
-cudaError_t gemm_tc(const GemmArgs& g, int splits, int* status_word, cudaStream_t stream) {
+cudaError_t gemm_tc(const GemmArgs& g, int splits, int passes, int* status_word,
+                    cudaStream_t stream) {
     if (!gemm_tc_supported(g) || status_word == nullptr) return cudaErrorInvalidValue;
     if (splits > 1 && g.bias != nullptr) return cudaErrorInvalidValue;
-    if (g.N > 128 + 64) return launch<256>(g, splits, status_word, stream);
-    if (g.N > 64 + 32) return launch<128>(g, splits, status_word, stream);
-    return launch<64>(g, splits, status_word, stream);
+    if (passes != 1 && passes != 3) return cudaErrorInvalidValue;
+    // widest tile that N fills to at least three quarters; measured on B200 at N = 512 and
+    // N = 4608: 256-wide tiles are 10-40 % faster than 128-wide ones in both modes
+    const int bn = g.N > 128 + 64 ? 256 : (g.N > 64 + 32 ? 128 : 64);
+    if (passes == 3) {
+        if (bn == 256) return launch<256, 3>(g, splits, status_word, stream);
+        if (bn == 128) return launch<128, 3>(g, splits, status_word, stream);
+        return launch<64, 3>(g, splits, status_word, stream);
+    }
+    if (bn == 256) return launch<256, 1>(g, splits, status_word, stream);
+    if (bn == 128) return launch<128, 1>(g, splits, status_word, stream);
+    return launch<64, 1>(g, splits, status_word, stream);
 }
 
 }  // namespace msda

@@ -152,38 +152,78 @@ int dispatch_pointwise(const void* a, const void* b, void* dst, size_t n, int dt
 }
 
 // ---------------------------------------------------------------------------------------------
-// 3x3 / stride 2 / pad 1 max pooling, NCHW. One thread per output element; neighbouring threads
-// take neighbouring output columns, so a warp reads one contiguous stretch of 64 input columns
-// per window row and the 2x overlap between windows is served by L1.
+// 3x3 / stride 2 / pad 1 max pooling, NCHW. One thread produces four neighbouring outputs of
+// one output row: they need nine input columns (2*ow0 - 1 .. 2*ow0 + 7) of three input rows,
+// read as eight contiguous elements (16-byte loads where the row allows it) plus the one column
+// to their left. Neighbouring threads take neighbouring groups, so a warp reads contiguous
+// stretches of each input row; the overlap between output rows is served by L1 / L2.
 // ---------------------------------------------------------------------------------------------
+struct NanMax {
+    float best = -INFINITY;
+    bool seen_nan = false;
+    __device__ __forceinline__ void take(float v) {
+        seen_nan |= (v != v);
+        best = fmaxf(best, v);
+    }
+    __device__ __forceinline__ float result() const {
+        return seen_nan ? __int_as_float(0x7fc00000) : best;
+    }
+};
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 maxpool3s2_kernel(const T* __restrict__ x, T* __restrict__ y, int H, int W, int OH, int OW,
-                  size_t total) {
-    for (size_t idx = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; idx < total;
+                  int groups_per_row, size_t total_groups, int vec_in, int vec_out) {
+    constexpr int kPerVec = 16 / sizeof(T);   // elements per 16-byte load
+    for (size_t idx = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; idx < total_groups;
          idx += static_cast<size_t>(gridDim.x) * kThreads) {
-        const int ow = static_cast<int>(idx % OW);
-        const size_t t = idx / OW;
+        const int gq = static_cast<int>(idx % groups_per_row);
+        const size_t t = idx / groups_per_row;
         const int oh = static_cast<int>(t % OH);
         const size_t plane = t / OH;  // n * C + c
         const T* src = x + plane * static_cast<size_t>(H) * W;
-        const int h0 = 2 * oh - 1, w0 = 2 * ow - 1;
-        float best = -INFINITY;
-        bool seen_nan = false;
+        const int ow0 = 4 * gq, c0 = 2 * ow0;
+        NanMax acc[4];
+        const bool whole = vec_in && (c0 + 7 < W);
 #pragma unroll
         for (int i = 0; i < 3; ++i) {
-            const int h = h0 + i;
+            const int h = 2 * oh - 1 + i;
             if (h < 0 || h >= H) continue;
+            const T* row = src + static_cast<size_t>(h) * W;
+            float v[9];   // columns c0 - 1 .. c0 + 7; -inf where outside the image
+            v[0] = (c0 >= 1) ? Cvt<T>::up(row[c0 - 1]) : -INFINITY;
+            if (whole) {
+                alignas(16) T tmp[8];
 #pragma unroll
-            for (int j = 0; j < 3; ++j) {
-                const int w = w0 + j;
-                if (w < 0 || w >= W) continue;
-                const float v = Cvt<T>::up(src[static_cast<size_t>(h) * W + w]);
-                seen_nan |= (v != v);
-                best = fmaxf(best, v);
+                for (int q = 0; q < 8 / kPerVec; ++q)
+                    *reinterpret_cast<uint4*>(&tmp[q * kPerVec]) =
+                        *reinterpret_cast<const uint4*>(row + c0 + q * kPerVec);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[1 + j] = Cvt<T>::up(tmp[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[1 + j] = (c0 + j < W) ? Cvt<T>::up(row[c0 + j]) : -INFINITY;
+            }
+#pragma unroll
+            for (int o = 0; o < 4; ++o) {
+                // a column outside the image was read as -inf, which never wins and is not NaN
+                acc[o].take(v[2 * o]);
+                acc[o].take(v[2 * o + 1]);
+                acc[o].take(v[2 * o + 2]);
             }
         }
-        y[idx] = Cvt<T>::down(seen_nan ? __int_as_float(0x7fc00000) : best);
+        T* dst = y + (plane * OH + oh) * static_cast<size_t>(OW) + ow0;
+        if (vec_out && ow0 + 3 < OW) {
+            alignas(16) T out4[4];
+#pragma unroll
+            for (int o = 0; o < 4; ++o) out4[o] = Cvt<T>::down(acc[o].result());
+            if (sizeof(T) == 4) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(out4);
+            else *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<uint2*>(out4);
+        } else {
+#pragma unroll
+            for (int o = 0; o < 4; ++o)
+                if (ow0 + o < OW) dst[o] = Cvt<T>::down(acc[o].result());
+        }
     }
 }
 
@@ -193,12 +233,18 @@ int launch_maxpool(const void* x, void* y, int N, int C, int H, int W, cudaStrea
     const int rc = sm_count_of_current_device(&sms);
     if (rc != MSDA_OK) return rc;
     const int OH = (H + 1) / 2, OW = (W + 1) / 2;
-    const size_t total = static_cast<size_t>(N) * C * OH * OW;
+    const int groups_per_row = (OW + 3) / 4;
+    const size_t total = static_cast<size_t>(N) * C * OH * groups_per_row;
+    // 16-byte loads need every row to start on a 16-byte boundary; vector stores likewise
+    const int per_vec = 16 / static_cast<int>(sizeof(T));
+    const int vec_in = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (W % per_vec == 0);
+    const int vec_out = (reinterpret_cast<uintptr_t>(y) % 16 == 0) && (OW % 4 == 0);
     const size_t want = (total + kThreads - 1) / kThreads;
     const size_t cap = static_cast<size_t>(sms) * 8 * 4;  // four waves of resident CTAs at most
     const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
-    maxpool3s2_kernel<T><<<grid, kThreads, 0, stream>>>(static_cast<const T*>(x),
-                                                        static_cast<T*>(y), H, W, OH, OW, total);
+    maxpool3s2_kernel<T><<<grid, kThreads, 0, stream>>>(static_cast<const T*>(x), static_cast<T*>(y),
+                                                        H, W, OH, OW, groups_per_row, total, vec_in,
+                                                        vec_out);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return msda::note_cuda_error(e);
     msda::count_launches(1);

@@ -5,9 +5,9 @@
 
 Same surface as the reference's patcher for this path (mx_driving/patcher/__init__.py):
 ``Patcher``, ``Patch``, ``AtomicPatch``, ``BasePatch``, ``PatchStatus``, ``PatchResult``,
-``MultiScaleDeformableAttention`` (alias ``MSDA``), ``ResNetAddRelu``, ``ResNetMaxPool``,
-``default_patcher``, the legacy functions ``msda(module, options)``, ``resnet_add_relu``,
-``resnet_maxpool``, ``configure_patcher_logging`` and ``set_patcher_log_level``. The
+``MultiScaleDeformableAttention`` (alias ``MSDA``), ``DeformConv``, ``ModulatedDeformConv``,
+``ResNetAddRelu``, ``ResNetMaxPool``, ``default_patcher``, the legacy functions
+``msda(module, options)``, ``dc``, ``mdc``, ``resnet_add_relu``, ``resnet_maxpool``, ``configure_patcher_logging`` and ``set_patcher_log_level``. The
 reference's other predefined patches (sparse convolution, dataset and optimizer shims, ...)
 belong to operators that are not part of this package.
 """
@@ -17,7 +17,7 @@ from .patcher_logger import configure_patcher_logging, patcher_logger, set_patch
 from .reporting import PatchResult, PatchStatus
 from .patch import AtomicPatch, BasePatch, Patch
 from .patcher import Patcher, replace_with
-from .mmcv_patch import MultiScaleDeformableAttention
+from .mmcv_patch import DeformConv, ModulatedDeformConv, MultiScaleDeformableAttention
 from .mmdet_patch import ResNetAddRelu, ResNetMaxPool
 
 MSDA = MultiScaleDeformableAttention  # alias
@@ -25,11 +25,11 @@ MSDA = MultiScaleDeformableAttention  # alias
 # same order as the reference's registry (mx_driving/patcher/__init__.py:116-149), restricted
 # to the patches whose operators exist in this package
 _ALL_PATCH_CLASSES: List[Type[Patch]] = [
-    MultiScaleDeformableAttention,
+    MultiScaleDeformableAttention, DeformConv, ModulatedDeformConv,
     ResNetAddRelu, ResNetMaxPool,
 ]
 _DEFAULT_PATCH_CLASSES: List[Type[Patch]] = [
-    MultiScaleDeformableAttention,
+    MultiScaleDeformableAttention, DeformConv, ModulatedDeformConv,
     ResNetAddRelu, ResNetMaxPool,
 ]
 
@@ -57,6 +57,8 @@ def _create_legacy_patch_func(patch_cls: Type[Patch]):
 
 
 msda = _create_legacy_patch_func(MultiScaleDeformableAttention)
+dc = _create_legacy_patch_func(DeformConv)
+mdc = _create_legacy_patch_func(ModulatedDeformConv)
 resnet_add_relu = _create_legacy_patch_func(ResNetAddRelu)
 resnet_maxpool = _create_legacy_patch_func(ResNetMaxPool)
 
@@ -65,6 +67,7 @@ __all__ = [
     "patcher_logger", "configure_patcher_logging", "set_patcher_log_level",
     "PatchStatus", "PatchResult",
     "default_patcher", "MultiScaleDeformableAttention", "MSDA", "msda",
+    "DeformConv", "ModulatedDeformConv", "dc", "mdc",
     "ResNetAddRelu", "ResNetMaxPool", "resnet_add_relu", "resnet_maxpool",
     "_ALL_PATCH_CLASSES", "_DEFAULT_PATCH_CLASSES", "_LEGACY_NAME_TO_CLASS",
 ]

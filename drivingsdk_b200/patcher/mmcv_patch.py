@@ -1,4 +1,5 @@
-"""The mmcv hook of the MSDA path.
+"""The mmcv hooks: multi-scale deformable attention, and (further down) deformable and
+modulated deformable convolution.
 
 mmcv models call ``mmcv.ops.multi_scale_deform_attn.MultiScaleDeformableAttnFunction
 .apply(value, spatial_shapes, level_start_index, sampling_locations, attention_weights,
@@ -42,4 +43,40 @@ class MultiScaleDeformableAttention(Patch):
         return [
             AtomicPatch(f"{theirs}.forward", f"{ours}.forward", replacement_wrapper=adapt_forward),
             AtomicPatch(f"{theirs}.backward", f"{ours}.backward", replacement_wrapper=adapt_backward),
+        ]
+
+
+class DeformConv(Patch):
+    """Deformable Convolution patch for mmcv: the autograd function and the functional form
+    are replaced by this package's (mx_driving/patcher/mmcv_patch.py:74-93); mmcv's
+    ``DeformConv2d`` modules call the functional form, so they follow."""
+
+    name = "deform_conv"
+    legacy_name = "dc"
+    target_module = "mmcv"
+
+    @classmethod
+    def patches(cls, options=None) -> List[BasePatch]:
+        return [
+            AtomicPatch("mmcv.ops.deform_conv.DeformConv2dFunction",
+                        "mx_driving.DeformConv2dFunction"),
+            AtomicPatch("mmcv.ops.deform_conv.deform_conv2d", "mx_driving.deform_conv2d"),
+        ]
+
+
+class ModulatedDeformConv(Patch):
+    """Modulated Deformable Convolution patch for mmcv
+    (mx_driving/patcher/mmcv_patch.py:100-119)."""
+
+    name = "modulated_deform_conv"
+    legacy_name = "mdc"
+    target_module = "mmcv"
+
+    @classmethod
+    def patches(cls, options=None) -> List[BasePatch]:
+        return [
+            AtomicPatch("mmcv.ops.modulated_deform_conv.ModulatedDeformConv2dFunction",
+                        "mx_driving.ModulatedDeformConv2dFunction"),
+            AtomicPatch("mmcv.ops.modulated_deform_conv.modulated_deform_conv2d",
+                        "mx_driving.modulated_deform_conv2d"),
         ]

@@ -105,8 +105,11 @@ int dcn_sm100_backward(const float* x, const float* offset, const float* mask,
 /*
  * Which matrix-product kernels the two calls above use: 1 (default) = the tcgen05 kernel
  * (fp32 operands split into two TF32 parts, three tensor-core products per tile, fp32
- * accumulation in tensor memory) where the shape allows it; 0 = the plain fp32 FMA kernel
- * everywhere. Returns the previous setting; any other value only queries.
+ * accumulation in tensor memory; fp32-class accuracy) where the shape allows it; 2 = the same
+ * kernel with a single TF32 product per tile (three times fewer tensor-core instructions,
+ * about 1e-3 relative accuracy, the trade torch.backends.cuda.matmul.allow_tf32 makes);
+ * 0 = the plain fp32 FMA kernel everywhere. Returns the previous setting; any other value
+ * only queries.
  */
 int dcn_sm100_use_tensor_cores(int on);
 

@@ -17,7 +17,7 @@ def declared_functions():
             continue
         text = open(os.path.join(INCLUDE, header)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-        names.update(re.findall(r"\b([a-z]+_sm100_\w+)\s*\(", text))
+        names.update(re.findall(r"\b([a-z][a-z0-9_]*_sm100_\w+)\s*\(", text))
     return sorted(names)
 
 

@@ -256,3 +256,43 @@ def test_alias_modules_expose_the_reference_paths():
     from mx_driving.patcher.mmcv_patch import MultiScaleDeformableAttention as M2
     assert A2 is AtomicPatch and S2 is PatchStatus and M2 is MultiScaleDeformableAttention
     assert alias.default_patcher is default_patcher and alias.MSDA is MSDA
+
+
+def test_deform_conv_patches_replace_function_class_and_functional_form():
+    """DeformConv / ModulatedDeformConv: same targets and replacements as the reference
+    (mx_driving/patcher/mmcv_patch.py:74-119), applied to a module tree shaped like mmcv's."""
+    from drivingsdk_b200.patcher import DeformConv, ModulatedDeformConv, dc, mdc
+    assert (DeformConv.name, DeformConv.legacy_name) == ("deform_conv", "dc")
+    assert (ModulatedDeformConv.name, ModulatedDeformConv.legacy_name) == ("modulated_deform_conv", "mdc")
+    names = ["mmcv", "mmcv.ops", "mmcv.ops.deform_conv", "mmcv.ops.modulated_deform_conv"]
+    mods = {n: types.ModuleType(n) for n in names}
+    mods["mmcv"].ops = mods["mmcv.ops"]
+    mods["mmcv.ops"].deform_conv = mods["mmcv.ops.deform_conv"]
+    mods["mmcv.ops"].modulated_deform_conv = mods["mmcv.ops.modulated_deform_conv"]
+    mods["mmcv.ops.deform_conv"].DeformConv2dFunction = "theirs"
+    mods["mmcv.ops.deform_conv"].deform_conv2d = "theirs"
+    mods["mmcv.ops.modulated_deform_conv"].ModulatedDeformConv2dFunction = "theirs"
+    mods["mmcv.ops.modulated_deform_conv"].modulated_deform_conv2d = "theirs"
+    saved = {n: sys.modules.get(n) for n in names}
+    sys.modules.update(mods)
+    try:
+        import mx_driving
+        p = Patcher().add(DeformConv, ModulatedDeformConv)
+        p.apply()
+        assert [r.status for r in p.results] == [PatchStatus.APPLIED] * 4
+        assert mods["mmcv.ops.deform_conv"].DeformConv2dFunction is mx_driving.DeformConv2dFunction
+        assert mods["mmcv.ops.deform_conv"].deform_conv2d is mx_driving.deform_conv2d
+        assert (mods["mmcv.ops.modulated_deform_conv"].ModulatedDeformConv2dFunction
+                is mx_driving.ModulatedDeformConv2dFunction)
+        assert (mods["mmcv.ops.modulated_deform_conv"].modulated_deform_conv2d
+                is mx_driving.modulated_deform_conv2d)
+        assert callable(dc) and callable(mdc)
+        targets = [patch.name for patch, _ in default_patcher.collect()]
+        assert "mmcv.ops.deform_conv.deform_conv2d" in targets
+        assert "mmcv.ops.modulated_deform_conv.modulated_deform_conv2d" in targets
+    finally:
+        for n, v in saved.items():
+            if v is None:
+                sys.modules.pop(n, None)
+            else:
+                sys.modules[n] = v
