@@ -36,16 +36,22 @@ namespace msda {
 namespace {
 
 constexpr int BM = 128;
-constexpr int BK = 32;                      // fp32 elements = one 128-byte swizzle row
+// k extent of a stage in fp32 elements: one swizzled shared-memory row per operand row.
+// The three-product mode doubles a stage's footprint (lo parts), so it uses 64-byte rows to
+// keep four stages in flight; two were not enough to cover the TMA latency.
+constexpr int kBkSplit = 16;                // 64-byte rows, 64-byte swizzle
+constexpr int kBkPlain = 32;                // 128-byte rows, 128-byte swizzle
 constexpr int kGemmThreads = 192;
-constexpr int kTileABytes = BM * BK * 4;    // 16 KiB
 constexpr int kStatusGemmTimeout = 2;       // bit in the sticky status word
 constexpr int kWaitLimit = 1 << 22;
 
 // A stage holds the raw A and B tiles and, for the three-product mode, their lo parts.
 template <int BN, int PASSES>
 struct Tile {
-    static constexpr int kTileBBytes = BN * BK * 4;
+    static constexpr int BK = (PASSES == 3) ? kBkSplit : kBkPlain;
+    static constexpr int kRowBytes = BK * 4;
+    static constexpr int kTileABytes = BM * kRowBytes;
+    static constexpr int kTileBBytes = BN * kRowBytes;
     static constexpr int kStageBytes = (PASSES == 3 ? 2 : 1) * (kTileABytes + kTileBBytes);
     static constexpr int kFit = (192 * 1024) / kStageBytes;
     static constexpr int kStages = kFit > 8 ? 8 : kFit;
@@ -84,13 +90,16 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         : "memory");
 }
 
-// Shared-memory operand descriptor: k-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+// Shared-memory operand descriptor: k-major rows of ROW_BYTES (128 or 64) swizzled at that
+// width, 8-row groups 8 * ROW_BYTES apart.
+template <int ROW_BYTES>
 __device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr) {
+    static_assert(ROW_BYTES == 128 || ROW_BYTES == 64, "row width");
     uint64_t d = 0;
-    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);   // start address
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;                // stride between 8-row groups
-    d |= 1ull << 46;                                            // descriptor version (sm_100)
-    d |= 2ull << 61;                                            // 128-byte swizzle
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);            // start address
+    d |= static_cast<uint64_t>((8 * ROW_BYTES) >> 4) << 32;              // stride between 8-row groups
+    d |= 1ull << 46;                                                     // descriptor version (sm_100)
+    d |= static_cast<uint64_t>(ROW_BYTES == 128 ? 2 : 4) << 61;          // 128- / 64-byte swizzle
     return d;
 }
 
@@ -138,6 +147,7 @@ struct TcParams {
     const float* bias;
     int M, N, K;
     int kb_per_split;   // k-blocks (of BK) per CTA along gridDim.z
+    int n_tiles;        // tiles along N; blockIdx.x = m_tile * n_tiles + n_tile
     int reduce;         // add into C with reductions (K is cut across CTAs)
     int* status;
 };
@@ -149,6 +159,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                const TcParams p) {
     using T = Tile<BN, PASSES>;
     constexpr int kStages = T::kStages;
+    constexpr int BK = T::BK;
+    constexpr int kTileABytes = T::kTileABytes;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base_u32 = smem_u32(smem_raw);
     uint8_t* tiles = smem_raw + ((1024u - (base_u32 & 1023u)) & 1023u);
@@ -161,7 +173,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    // tiles that share a row block of A are neighbours in launch order, so A comes from HBM once
+    const int m0 = (blockIdx.x / p.n_tiles) * BM, n0 = (blockIdx.x % p.n_tiles) * BN;
     const int kb_total = (p.K + BK - 1) / BK;
     const int kb_begin = blockIdx.z * p.kb_per_split;
     const int kb_end = min(kb_total, kb_begin + p.kb_per_split);
@@ -238,8 +251,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                 for (int kk = 0; kk < BK / 8; ++kk) {
                     const uint32_t off = kk * 32;   // 8 TF32 values along k
-                    const uint64_t dah = operand_desc(a_hi + off), dal = operand_desc(a_lo + off);
-                    const uint64_t dbh = operand_desc(b_hi + off), dbl = operand_desc(b_lo + off);
+                    const uint64_t dah = operand_desc<T::kRowBytes>(a_hi + off);
+                    const uint64_t dal = operand_desc<T::kRowBytes>(a_lo + off);
+                    const uint64_t dbh = operand_desc<T::kRowBytes>(b_hi + off);
+                    const uint64_t dbl = operand_desc<T::kRowBytes>(b_lo + off);
                     const uint32_t fresh = (i > 0 || kk > 0) ? 1u : 0u;
                     if (PASSES == 3) {
                         mma_tf32(tmem_base, dal, dbh, idesc, fresh);
@@ -368,19 +383,21 @@ cudaError_t encode_fn(EncodeTiledFn* out) {
     return cudaSuccess;
 }
 
-// [rows, K] fp32 matrix with k contiguous -> map with boxes of (BK k) x (box_rows rows)
+// [rows, K] fp32 matrix with k contiguous -> map with boxes of (bk k) x (box_rows rows),
+// swizzled at the width of a box row
 cudaError_t make_map(CUtensorMap* map, const float* base, long long row_stride, int rows, int K,
-                     int box_rows) {
+                     int box_rows, int bk) {
     EncodeTiledFn fn = nullptr;
     cudaError_t e = encode_fn(&fn);
     if (e != cudaSuccess) return e;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_stride) * 4};
-    const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(bk), static_cast<cuuint32_t>(box_rows)};
     const cuuint32_t elem_strides[2] = {1, 1};
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims,
                           strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          bk * 4 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
@@ -396,9 +413,10 @@ cudaError_t launch(const GemmArgs& g, int splits, int* status, cudaStream_t stre
         configured.store(1, std::memory_order_release);
     }
     CUtensorMap map_a, map_b;
-    cudaError_t e = make_map(&map_a, g.A, g.a_row, g.M, g.K, BM);
+    constexpr int BK = Tile<BN, PASSES>::BK;
+    cudaError_t e = make_map(&map_a, g.A, g.a_row, g.M, g.K, BM, BK);
     if (e != cudaSuccess) return e;
-    e = make_map(&map_b, g.B, g.b_row, g.N, g.K, BN);
+    e = make_map(&map_b, g.B, g.b_row, g.N, g.K, BN, BK);
     if (e != cudaSuccess) return e;
     const int kb_total = (g.K + BK - 1) / BK;
     if (splits < 1) splits = 1;
@@ -413,8 +431,10 @@ cudaError_t launch(const GemmArgs& g, int splits, int* status, cudaStream_t stre
     p.kb_per_split = (kb_total + splits - 1) / splits;
     p.reduce = splits > 1 ? 1 : 0;
     p.status = status;
-    const dim3 grid((g.M + BM - 1) / BM, (g.N + BN - 1) / BN,
-                    (kb_total + p.kb_per_split - 1) / p.kb_per_split);
+    p.n_tiles = (g.N + BN - 1) / BN;
+    const long long tiles = static_cast<long long>((g.M + BM - 1) / BM) * p.n_tiles;
+    if (tiles >= (1ll << 31)) return cudaErrorInvalidValue;
+    const dim3 grid(static_cast<unsigned>(tiles), 1, (kb_total + p.kb_per_split - 1) / p.kb_per_split);
     gemm_tc_kernel<BN, PASSES><<<grid, kGemmThreads, Tile<BN, PASSES>::kSmemBytes, stream>>>(map_a, map_b, p);
     return cudaGetLastError();
 }
