@@ -44,6 +44,8 @@ SIGNATURES = {
     "dcn_sm100_forward": (_i, [_vp] * 7 + [_vp, _vp]),
     "dcn_sm100_backward": (_i, [_vp] * 11 + [_vp, _sz, _vp, _vp]),
     "dcn_sm100_use_tensor_cores": (_i, [_i]),
+    "gemm_tn_sm100_f32": (_i, [_vp, ctypes.c_longlong, _vp, ctypes.c_longlong, _vp,
+                               ctypes.c_longlong, _i, _i, _i, _i, _vp]),
     "gemm_nt_sm100_f32": (_i, [_vp, ctypes.c_longlong, _vp, ctypes.c_longlong, _vp,
                                ctypes.c_longlong, _vp, _i, _i, _i, _i, _vp]),
     "msda_sm100_forward_bytes": (_sz, _DIMS7 + [_i]),

@@ -362,39 +362,25 @@ size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Layout of the backward's scratch memory.
 struct Workspace {
-    size_t grad_columns, weight_t, grad_out_t, columns_t, total;
-    long long m_pad;  // row stride of the transposed operands (elements)
+    size_t grad_columns, weight_t, total;
 };
 Workspace plan_workspace(const dcn_shape* s, const Derived& d) {
     Workspace w;
-    w.m_pad = static_cast<long long>(round_up(static_cast<size_t>(d.M), 4));
     size_t at = 0;
     w.grad_columns = at;
     at += round_up(static_cast<size_t>(d.M) * s->groups * d.Kd * 4, 256);
     w.weight_t = at;       // per group [Kd, Cog]
     at += round_up(static_cast<size_t>(s->Co) * d.Kd * 4, 256);
-    w.grad_out_t = at;     // [Co, m_pad]
-    at += round_up(static_cast<size_t>(s->Co) * w.m_pad * 4, 256);
-    w.columns_t = at;      // [G * Kd, m_pad]
-    at += round_up(static_cast<size_t>(s->groups) * d.Kd * w.m_pad * 4, 256);
     w.total = at;
     return w;
 }
 
-}  // namespace
-
-extern "C" {
-
-int dcn_sm100_use_tensor_cores(int on) {
-    if (on >= 0 && on <= 2) return g_use_tc.exchange(on, std::memory_order_relaxed);
-    return g_use_tc.load(std::memory_order_relaxed);
-}
-
-int gemm_nt_sm100_f32(const float* A, long long lda, const float* B, long long ldb, float* C,
-                      long long ldc, const float* bias, int M, int N, int K, int splits,
-                      void* stream_v) {
+// The exported products: argument checks, optional K split with its zero-fill.
+int public_product(const float* A, long long a_row, long long a_k, const float* B, long long b_row,
+                   long long b_k, float* C, long long ldc, const float* bias, int M, int N, int K,
+                   int splits, void* stream_v) {
     if (A == nullptr || B == nullptr || C == nullptr) return MSDA_ERR_NULL;
-    if (M <= 0 || N <= 0 || K <= 0 || lda < K || ldb < K || ldc < N) return MSDA_ERR_DIMS;
+    if (M <= 0 || N <= 0 || K <= 0 || ldc < N) return MSDA_ERR_DIMS;
     if (splits > 1 && bias != nullptr) return MSDA_ERR_DIMS;
     int* status_word = nullptr;
     int rc = msda::device_facts(nullptr, &status_word);
@@ -402,11 +388,11 @@ int gemm_nt_sm100_f32(const float* A, long long lda, const float* B, long long l
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     msda::GemmArgs g{};
     g.A = A;
-    g.a_row = lda;
-    g.a_k = 1;
+    g.a_row = a_row;
+    g.a_k = a_k;
     g.B = B;
-    g.b_row = ldb;
-    g.b_k = 1;
+    g.b_row = b_row;
+    g.b_k = b_k;
     g.C = C;
     g.ldc = ldc;
     g.bias = bias;
@@ -421,6 +407,28 @@ int gemm_nt_sm100_f32(const float* A, long long lda, const float* B, long long l
         if (e != cudaSuccess) return msda::note_cuda_error(e);
     }
     return product(g, splits, status_word, stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+int dcn_sm100_use_tensor_cores(int on) {
+    if (on >= 0 && on <= 2) return g_use_tc.exchange(on, std::memory_order_relaxed);
+    return g_use_tc.load(std::memory_order_relaxed);
+}
+
+int gemm_nt_sm100_f32(const float* A, long long lda, const float* B, long long ldb, float* C,
+                      long long ldc, const float* bias, int M, int N, int K, int splits,
+                      void* stream_v) {
+    if (M > 0 && N > 0 && K > 0 && (lda < K || ldb < K)) return MSDA_ERR_DIMS;
+    return public_product(A, lda, 1, B, ldb, 1, C, ldc, bias, M, N, K, splits, stream_v);
+}
+
+int gemm_tn_sm100_f32(const float* A, long long lda, const float* B, long long ldb, float* C,
+                      long long ldc, int M, int N, int K, int splits, void* stream_v) {
+    if (M > 0 && N > 0 && K > 0 && (lda < M || ldb < N)) return MSDA_ERR_DIMS;
+    return public_product(A, 1, lda, B, 1, ldb, C, ldc, nullptr, M, N, K, splits, stream_v);
 }
 
 size_t dcn_sm100_columns_bytes(const dcn_shape* s) {
@@ -509,8 +517,6 @@ int dcn_sm100_backward(const float* x, const float* offset, const float* mask,
     char* wsp = static_cast<char*>(workspace);
     float* grad_columns = reinterpret_cast<float*>(wsp + ws.grad_columns);
     float* weight_t = reinterpret_cast<float*>(wsp + ws.weight_t);
-    float* grad_out_t = reinterpret_cast<float*>(wsp + ws.grad_out_t);
-    float* columns_t = reinterpret_cast<float*>(wsp + ws.columns_t);
     const long long ld_cols = static_cast<long long>(s->groups) * d.Kd;
     const int M = static_cast<int>(d.M);
     const bool tc = g_use_tc.load(std::memory_order_relaxed) != 0;
@@ -563,51 +569,37 @@ int dcn_sm100_backward(const float* x, const float* offset, const float* mask,
     rc = launch_sample<true>(p, piece_width(s, d), sms, stream);
     if (rc != MSDA_OK) return rc;
 
-    // 3. grad_weight[co, kd] = sum over m of grad_out[m, co] * columns[m, g, kd]
+    // 3. grad_weight[co, kd] = sum over m of grad_out[m, co] * columns[m, g, kd]: both operands
+    //    are stored pixel row by pixel row, i.e. with the row index (co, kd) contiguous and
+    //    k = m strided. The tensor-core kernel takes that form directly (K cut over CTAs so
+    //    that every SM has work); operands that miss its alignment rules go to the FMA kernel.
     {
-        msda::GemmArgs probe{};
-        probe.A = grad_out_t;
-        probe.a_row = ws.m_pad;
-        probe.a_k = 1;
-        probe.B = columns_t;
-        probe.b_row = ws.m_pad;
-        probe.b_k = 1;
-        probe.C = grad_weight;
-        probe.ldc = d.Kd;
-        probe.M = d.Cog;
-        probe.N = d.Kd;
-        probe.K = M;
-        const bool use_t = tc && msda::gemm_tc_supported(probe);
-        if (use_t) {
-            e = msda::transpose_f32(grad_out, s->Co, grad_out_t, ws.m_pad, M, s->Co, stream);
-            if (e != cudaSuccess) return msda::note_cuda_error(e);
-            e = msda::transpose_f32(columns, ld_cols, columns_t, ws.m_pad, M,
-                                    static_cast<int>(ld_cols), stream);
-            if (e != cudaSuccess) return msda::note_cuda_error(e);
-            e = cudaMemsetAsync(grad_weight, 0, static_cast<size_t>(s->Co) * d.Kd * 4, stream);
-            if (e != cudaSuccess) return msda::note_cuda_error(e);
-            msda::count_launches(2);
-        }
+        bool zeroed = false;
         for (int g = 0; g < s->groups; ++g) {
-            msda::GemmArgs a = probe;
+            msda::GemmArgs a{};
+            a.A = grad_out + static_cast<size_t>(g) * d.Cog;
+            a.a_row = 1;
+            a.a_k = s->Co;
+            a.B = columns + static_cast<size_t>(g) * d.Kd;
+            a.b_row = 1;
+            a.b_k = ld_cols;
             a.C = grad_weight + static_cast<size_t>(g) * d.Cog * d.Kd;
+            a.ldc = d.Kd;
+            a.M = d.Cog;
+            a.N = d.Kd;
+            a.K = M;
             int splits = 1;
-            if (use_t) {
-                a.A = grad_out_t + static_cast<size_t>(g) * d.Cog * ws.m_pad;
-                a.B = columns_t + static_cast<size_t>(g) * d.Kd * ws.m_pad;
-                // few output tiles, long K: cut K so that every SM has work
-                const long long tiles = ((d.Cog + 127) / 128) * static_cast<long long>((d.Kd + 127) / 128);
+            if (tc && msda::gemm_tc_supported(a)) {
+                const long long tiles = ((d.Cog + 127) / 128) * static_cast<long long>((d.Kd + 255) / 256);
                 splits = static_cast<int>((2ll * sms + tiles - 1) / tiles);
                 const int max_splits = (M + 1023) / 1024;
                 if (splits > max_splits) splits = max_splits;
                 if (splits < 1) splits = 1;
-            } else {
-                a.A = grad_out + static_cast<size_t>(g) * d.Cog;
-                a.a_row = 1;
-                a.a_k = s->Co;
-                a.B = columns + static_cast<size_t>(g) * d.Kd;
-                a.b_row = 1;
-                a.b_k = ld_cols;
+                if (splits > 1 && !zeroed) {
+                    e = cudaMemsetAsync(grad_weight, 0, static_cast<size_t>(s->Co) * d.Kd * 4, stream);
+                    if (e != cudaSuccess) return msda::note_cuda_error(e);
+                    zeroed = true;
+                }
             }
             rc = product(a, splits, status_word, stream);
             if (rc != MSDA_OK) return rc;

@@ -22,8 +22,10 @@ struct GemmArgs {
 // Plain fp32 FMA kernel: any strides, any sizes. Overwrites C.
 cudaError_t gemm_simt(const GemmArgs& g, cudaStream_t stream);
 
-// tcgen05 kernel: operands with k contiguous (a_k == b_k == 1), 16-byte aligned bases, row
-// strides that are multiples of 4 elements. fp32 accuracy through a two-term TF32 split of
+// tcgen05 kernel: 16-byte aligned bases and either both operands with k contiguous (a_k ==
+// b_k == 1, row strides multiples of 4 elements) or both with the row index contiguous
+// (a_row == b_row == 1, k strides multiples of 4 elements, M and N multiples of 32; this is
+// the grad_weight product, whose k is the pixel index). fp32 accuracy through a two-term TF32 split of
 // both operands (passes == 3: three tensor-core products per tile), or one TF32 product per
 // tile (passes == 1, about 1e-3 relative accuracy). `splits` > 1 cuts K into that many
 // parts whose partial results are added into C with reductions; C must be zero before, and

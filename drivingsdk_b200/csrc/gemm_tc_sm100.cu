@@ -90,6 +90,17 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         : "memory");
 }
 
+// The same for a 3-D map; used for operands whose contiguous index is the row (m or n):
+// coordinates are (0, k, row / 32).
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1,
+                                            int c2, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+        : "memory");
+}
+
 // Shared-memory operand descriptor: k-major rows of ROW_BYTES (128 or 64) swizzled at that
 // width, 8-row groups 8 * ROW_BYTES apart.
 template <int ROW_BYTES>
@@ -103,11 +114,27 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr) {
     return d;
 }
 
-// Instruction descriptor: TF32 x TF32 -> fp32, both operands k-major, M = 128, N = BN.
+// Descriptor of a row-contiguous ("MN-major") operand tile: 128-byte lines of 32 consecutive
+// m (or n) for one k. For 32-bit operands the tensor core takes this form only with the
+// "128-byte swizzle on 32-byte chunks" pattern, whose groups are four lines (four k) of
+// 512 bytes; groups follow each other along k, the next 32 m (or n) start `block_bytes`
+// further on.
+__device__ __forceinline__ uint64_t operand_desc_mn(uint32_t smem_addr, uint32_t block_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(block_bytes >> 4) << 16;      // leading offset: next 32 rows
+    d |= static_cast<uint64_t>(512 >> 4) << 32;               // stride offset: next 4 k
+    d |= 1ull << 46;
+    d |= 1ull << 61;                                          // 128-byte swizzle, 32-byte chunks
+    return d;
+}
+
+// Instruction descriptor: TF32 x TF32 -> fp32, M = 128, N = BN; both operands k-major, or
+// both row-contiguous (bits 15 and 16).
 template <int BN>
-__device__ __forceinline__ uint32_t instr_desc() {
-    return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
-           (static_cast<uint32_t>(BM >> 4) << 24);
+__device__ __forceinline__ uint32_t instr_desc(bool mn_major) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | (mn_major ? (3u << 15) : 0u) |
+           (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
 }
 
 __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc,
@@ -148,6 +175,7 @@ struct TcParams {
     int M, N, K;
     int kb_per_split;   // k-blocks (of BK) per CTA along gridDim.z
     int n_tiles;        // tiles along N; blockIdx.x = m_tile * n_tiles + n_tile
+    int mn_major;       // operands are row-contiguous (A[k][m], B[k][n]) instead of k-contiguous
     int reduce;         // add into C with reductions (K is cut across CTAs)
     int* status;
 };
@@ -219,8 +247,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint8_t* st = stage_ptr(s);
                 mbar_expect_tx(&full_raw[s], kTileABytes + T::kTileBBytes);
                 const int k0 = (kb_begin + i) * BK;
-                tma_load_2d(st, &map_a, k0, m0, &full_raw[s]);
-                tma_load_2d(st + kTileABytes, &map_b, k0, n0, &full_raw[s]);
+                if (p.mn_major) {
+                    tma_load_3d(st, &map_a, 0, k0, m0 / 32, &full_raw[s]);
+                    tma_load_3d(st + kTileABytes, &map_b, 0, k0, n0 / 32, &full_raw[s]);
+                } else {
+                    tma_load_2d(st, &map_a, k0, m0, &full_raw[s]);
+                    tma_load_2d(st + kTileABytes, &map_b, k0, n0, &full_raw[s]);
+                }
                 issued = i + 1;
             }
             if (*abort_flag) {
@@ -232,7 +265,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         // ---------------- MMA issue ----------------
         if (lane == 0) {
-            const uint32_t idesc = instr_desc<BN>();
+            const uint32_t idesc = instr_desc<BN>(p.mn_major != 0);
             bool ok = true;
             for (int i = 0; i < num_kb && ok; ++i) {
                 const int s = i % kStages;
@@ -250,11 +283,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint32_t b_lo = a_lo + kTileABytes;
 #pragma unroll
                 for (int kk = 0; kk < BK / 8; ++kk) {
-                    const uint32_t off = kk * 32;   // 8 TF32 values along k
-                    const uint64_t dah = operand_desc<T::kRowBytes>(a_hi + off);
-                    const uint64_t dal = operand_desc<T::kRowBytes>(a_lo + off);
-                    const uint64_t dbh = operand_desc<T::kRowBytes>(b_hi + off);
-                    const uint64_t dbl = operand_desc<T::kRowBytes>(b_lo + off);
+                    uint64_t dah, dal, dbh, dbl;
+                    if (p.mn_major) {
+                        const uint32_t off = kk * 1024;       // next group of 8 k
+                        constexpr uint32_t kBlock = BK * 128;  // 32 rows x BK k
+                        dah = operand_desc_mn(a_hi + off, kBlock);
+                        dal = operand_desc_mn(a_lo + off, kBlock);
+                        dbh = operand_desc_mn(b_hi + off, kBlock);
+                        dbl = operand_desc_mn(b_lo + off, kBlock);
+                    } else {
+                        const uint32_t off = kk * 32;         // 8 TF32 values along k
+                        dah = operand_desc<T::kRowBytes>(a_hi + off);
+                        dal = operand_desc<T::kRowBytes>(a_lo + off);
+                        dbh = operand_desc<T::kRowBytes>(b_hi + off);
+                        dbl = operand_desc<T::kRowBytes>(b_lo + off);
+                    }
                     const uint32_t fresh = (i > 0 || kk > 0) ? 1u : 0u;
                     if (PASSES == 3) {
                         mma_tf32(tmem_base, dal, dbh, idesc, fresh);
@@ -402,6 +445,34 @@ cudaError_t make_map(CUtensorMap* map, const float* base, long long row_stride, 
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// [K, rows] fp32 matrix with the row index contiguous (element (row, k) at base[k * k_stride +
+// row]) seen as [rows / 32][K][32]: one box brings (box_rows / 32) blocks of bk k x 32 rows, each
+// k a 128-byte line swizzled in 32-byte chunks. rows must be a multiple of 32.
+cudaError_t make_map_mn(CUtensorMap* map, const float* base, long long k_stride, int rows, int K,
+                        int box_rows, int bk) {
+    EncodeTiledFn fn = nullptr;
+    cudaError_t e = encode_fn(&fn);
+    if (e != cudaSuccess) return e;
+    const cuuint64_t dims[3] = {32, static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows / 32)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(k_stride) * 4, 128};
+    const cuuint32_t box[3] = {32, static_cast<cuuint32_t>(bk), static_cast<cuuint32_t>(box_rows / 32)};
+    const cuuint32_t elem_strides[3] = {1, 1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims,
+                          strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+bool k_major_ok(const GemmArgs& g) {
+    return g.a_k == 1 && g.b_k == 1 && g.a_row % 4 == 0 && g.b_row % 4 == 0 &&
+           g.a_row * 4 < (1ll << 40) && g.b_row * 4 < (1ll << 40);
+}
+bool mn_major_ok(const GemmArgs& g) {
+    return g.a_row == 1 && g.b_row == 1 && g.a_k % 4 == 0 && g.b_k % 4 == 0 && g.M % 32 == 0 &&
+           g.N % 32 == 0 && g.a_k * 4 < (1ll << 40) && g.b_k * 4 < (1ll << 40);
+}
+
 template <int BN, int PASSES>
 cudaError_t launch(const GemmArgs& g, int splits, int* status, cudaStream_t stream) {
     static std::atomic<int> configured{0};
@@ -414,9 +485,12 @@ cudaError_t launch(const GemmArgs& g, int splits, int* status, cudaStream_t stre
     }
     CUtensorMap map_a, map_b;
     constexpr int BK = Tile<BN, PASSES>::BK;
-    cudaError_t e = make_map(&map_a, g.A, g.a_row, g.M, g.K, BM, BK);
+    const bool mn_major = !k_major_ok(g);
+    cudaError_t e = mn_major ? make_map_mn(&map_a, g.A, g.a_k, g.M, g.K, BM, BK)
+                             : make_map(&map_a, g.A, g.a_row, g.M, g.K, BM, BK);
     if (e != cudaSuccess) return e;
-    e = make_map(&map_b, g.B, g.b_row, g.N, g.K, BN, BK);
+    e = mn_major ? make_map_mn(&map_b, g.B, g.b_k, g.N, g.K, BN, BK)
+                 : make_map(&map_b, g.B, g.b_row, g.N, g.K, BN, BK);
     if (e != cudaSuccess) return e;
     const int kb_total = (g.K + BK - 1) / BK;
     if (splits < 1) splits = 1;
@@ -432,6 +506,7 @@ cudaError_t launch(const GemmArgs& g, int splits, int* status, cudaStream_t stre
     p.reduce = splits > 1 ? 1 : 0;
     p.status = status;
     p.n_tiles = (g.N + BN - 1) / BN;
+    p.mn_major = mn_major ? 1 : 0;
     const long long tiles = static_cast<long long>((g.M + BM - 1) / BM) * p.n_tiles;
     if (tiles >= (1ll << 31)) return cudaErrorInvalidValue;
     const dim3 grid(static_cast<unsigned>(tiles), 1, (kb_total + p.kb_per_split - 1) / p.kb_per_split);
@@ -443,11 +518,8 @@ cudaError_t launch(const GemmArgs& g, int splits, int* status, cudaStream_t stre
 
 bool gemm_tc_supported(const GemmArgs& g) {
     if (g.M <= 0 || g.N <= 0 || g.K <= 0) return false;
-    if (g.a_k != 1 || g.b_k != 1) return false;
-    if (g.a_row % 4 != 0 || g.b_row % 4 != 0) return false;
     if ((reinterpret_cast<uintptr_t>(g.A) | reinterpret_cast<uintptr_t>(g.B)) % 16 != 0) return false;
-    if (g.a_row * 4 >= (1ll << 40) || g.b_row * 4 >= (1ll << 40)) return false;
-    return true;
+    return k_major_ok(g) || mn_major_ok(g);
 }
 
 cudaError_t gemm_tc(const GemmArgs& g, int splits, int passes, int* status_word,

@@ -75,8 +75,8 @@ typedef struct dcn_shape {
 size_t dcn_sm100_columns_bytes(const dcn_shape* s);
 
 /*
- * Bytes of scratch memory dcn_sm100_backward needs (the gradient of `columns`, plus
- * transposed operands for the tensor-core products).
+ * Bytes of scratch memory dcn_sm100_backward needs (the gradient of `columns`, plus a
+ * transposed copy of the weights for the tensor-core product that forms it).
  */
 size_t dcn_sm100_backward_workspace_bytes(const dcn_shape* s);
 
@@ -123,6 +123,14 @@ int dcn_sm100_use_tensor_cores(int on);
 int gemm_nt_sm100_f32(const float* A, long long lda, const float* B, long long ldb, float* C,
                       long long ldc, const float* bias, int M, int N, int K, int splits,
                       void* stream);
+
+/*
+ * Same with both operands stored k-row by k-row (the grad_weight product of the convolution,
+ * whose k is the pixel index):  C[m, n] = sum_k A[k * lda + m] * B[k * ldb + n].
+ * tcgen05 kernel when lda, ldb are multiples of 4 and M, N multiples of 32.
+ */
+int gemm_tn_sm100_f32(const float* A, long long lda, const float* B, long long ldb, float* C,
+                      long long ldc, int M, int N, int K, int splits, void* stream);
 
 #ifdef __cplusplus
 }

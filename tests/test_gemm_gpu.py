@@ -69,3 +69,42 @@ def test_single_pass_mode_trades_accuracy_for_speed():
     """Mode 2: one TF32 product per tile; accuracy of a 10-bit mantissa, not fp32."""
     err, scale = run(1000, 512, 1152, 0, 0, 2)
     assert 2e-5 * scale < err <= 4e-3 * scale, (err, scale)
+
+
+TN_SHAPES = [
+    # M, N, K, lda_extra, ldb_extra (operands stored [K, M] and [K, N])
+    (128, 256, 64, 0, 0),
+    (32, 32, 8, 0, 0),
+    (512, 4608, 1000, 0, 0),
+    (64, 96, 333, 4, 8),
+    (96, 64, 50, 0, 0),       # tensor-core path (multiples of 32)
+    (100, 72, 40, 0, 0),      # not multiples of 32: FMA kernel
+]
+
+
+@pytest.mark.parametrize("tensor_cores", [0, 1, 2])
+@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("shape", TN_SHAPES)
+def test_row_contiguous_operands(shape, splits, tensor_cores):
+    """C = A^T B with A stored [K, M], B stored [K, N] (the grad_weight product)."""
+    from drivingsdk_b200 import capi
+    lib = capi.load()
+    M, N, K, ea, eb = shape
+    g = torch.Generator().manual_seed(M + 3 * N + 7 * K)
+    A = torch.randn(K, M + ea, generator=g).cuda()
+    B = torch.randn(K, N + eb, generator=g).cuda()
+    C = torch.full((M, N), float("nan"), device="cuda")
+    old = lib.dcn_sm100_use_tensor_cores(tensor_cores)
+    try:
+        capi.check(lib.gemm_tn_sm100_f32(A.data_ptr(), M + ea, B.data_ptr(), N + eb, C.data_ptr(), N,
+                                         M, N, K, splits, torch.cuda.current_stream().cuda_stream),
+                   "gemm tn")
+    finally:
+        lib.dcn_sm100_use_tensor_cores(old)
+    torch.cuda.synchronize()
+    assert lib.msda_sm100_device_status(1) == 0
+    want = A[:, :M].double().t() @ B[:, :N].double()
+    err = (C.double() - want).abs().max().item()
+    scale = want.abs().max().item()
+    tol = {0: 2e-5, 1: 5e-5, 2: 4e-3}[tensor_cores]
+    assert err <= tol * scale, (err, scale)
