@@ -7,22 +7,27 @@
 // and three products are accumulated per tile: lo*hi + hi*lo + hi*hi (lo*lo is below fp32
 // resolution). Accumulation is fp32, in tensor memory.
 //
-// One CTA computes one 128 x BN tile of C (BN = 64, 128 or 256) over its share of K, in steps
-// of 32 k (one 128-byte swizzled row per operand row):
+// A work item is one 128 x BN tile of C (BN = 64, 128 or 256) over one part of K; the kernel is
+// persistent (one CTA per SM, items dealt round-robin) and walks K in stages of 16 or 32 k (one
+// swizzled shared-memory row per operand row):
 //   warp 0        producer: one lane issues the two TMA tile loads of a stage
+//   warp 1        MMA: one lane issues the k-slices x 3 products of tcgen05.mma per stage and
+//                 commits the stage's "empty" barrier; owns the tensor-memory allocation, which
+//                 holds two accumulators used alternately
 //   warps 2..5    splitters: write the lo part of the raw tile into a second buffer at the same
 //                 offsets (so the swizzle pattern does not matter; the raw tile itself serves
 //                 as the hi part because the tensor core ignores the low 13 mantissa bits),
-//                 then hand the stage to the MMA warp; afterwards they are
-//                 the epilogue: tcgen05.ld of the accumulator (warp q reads lanes 32q..32q+31),
-//                 bias, stores (or reductions when K is cut across CTAs)
-//   warp 1        MMA: one lane issues 4 k-slices x 3 products of tcgen05.mma per stage and
-//                 commits the stage's "empty" barrier; owns the tensor-memory allocation
+//                 then hand the stage to the MMA warp
+//   warps 6..9    epilogue: tcgen05.ld of a finished accumulator (warp q reads lanes
+//                 32q..32q+31), bias, stores (or reductions when K is cut across items), then
+//                 hand the accumulator back; this overlaps the products of the next item
+// Operands may also be stored with the row index contiguous (the grad_weight product): 3-D TMA
+// maps and the 32-byte-chunk swizzle, same pipeline.
 // Out-of-range parts of a tile (M, N or K tails) are zero-filled by TMA and masked in the
 // epilogue. A single-product mode (PASSES == 1) skips the split and uses the freed shared
-// memory for twice as many stages. Every barrier wait is bounded: on a timeout the CTA raises the library's sticky
-// status word, stops issuing work, waits (bounded) for its own copies, frees its tensor memory
-// and returns.
+// memory for twice as many stages. Every barrier wait is bounded: on a timeout the CTA raises
+// the library's sticky status word, stops issuing work, waits (bounded) for its own copies,
+// frees its tensor memory and returns.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -41,7 +46,7 @@ constexpr int BM = 128;
 // keep four stages in flight; two were not enough to cover the TMA latency.
 constexpr int kBkSplit = 16;                // 64-byte rows, 64-byte swizzle
 constexpr int kBkPlain = 32;                // 128-byte rows, 128-byte swizzle
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;           // producer, MMA, 4 splitter and 4 epilogue warps
 constexpr int kStatusGemmTimeout = 2;       // bit in the sticky status word
 constexpr int kWaitLimit = 1 << 22;
 
@@ -173,14 +178,36 @@ struct TcParams {
     long long ldc;
     const float* bias;
     int M, N, K;
-    int kb_per_split;   // k-blocks (of BK) per CTA along gridDim.z
-    int n_tiles;        // tiles along N; blockIdx.x = m_tile * n_tiles + n_tile
+    int kb_per_split;   // k-blocks (of BK) per work item
+    int n_splits;       // parts K is cut into
+    int n_tiles;        // tiles along N
+    int total_tiles;    // tiles of C; work item w = split * total_tiles + tile, tile = m_tile * n_tiles + n_tile
     int mn_major;       // operands are row-contiguous (A[k][m], B[k][n]) instead of k-contiguous
-    int reduce;         // add into C with reductions (K is cut across CTAs)
+    int reduce;         // add into C with reductions (K is cut across work items)
     int* status;
 };
 
+// One work item: a 128 x BN tile of C over one part of K.
+struct WorkItem {
+    int m0, n0, kb_begin, num_kb;
+};
+template <int BN, int BK>
+__device__ __forceinline__ WorkItem work_item(const TcParams& p, int w) {
+    const int split = w / p.total_tiles;
+    const int tile = w - split * p.total_tiles;
+    WorkItem it;
+    // tiles that share a row block of A are neighbours in the order, so A comes from HBM once
+    it.m0 = (tile / p.n_tiles) * BM;
+    it.n0 = (tile % p.n_tiles) * BN;
+    const int kb_total = (p.K + BK - 1) / BK;
+    it.kb_begin = split * p.kb_per_split;
+    it.num_kb = min(kb_total, it.kb_begin + p.kb_per_split) - it.kb_begin;
+    return it;
+}
+
 // PASSES == 3: hi/lo split, fp32-class accuracy; PASSES == 1: one TF32 product per tile.
+// Persistent: CTA c takes work items c, c + gridDim.x, ...; the accumulator alternates between
+// two tensor-memory buffers so that the epilogue of one item overlaps the products of the next.
 template <int BN, int PASSES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -193,21 +220,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t base_u32 = smem_u32(smem_raw);
     uint8_t* tiles = smem_raw + ((1024u - (base_u32 & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + kStages * T::kStageBytes);
-    uint64_t* full_raw = bars;                  // TMA landed
-    uint64_t* full_split = bars + kStages;      // hi/lo parts written
-    uint64_t* empty = bars + 2 * kStages;       // the MMAs that read the stage have finished
-    uint64_t* accum_full = bars + 3 * kStages;  // every MMA of the tile has finished
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 1);
+    uint64_t* full_raw = bars;                      // TMA landed
+    uint64_t* full_split = bars + kStages;          // lo parts written
+    uint64_t* empty = bars + 2 * kStages;           // the MMAs that read the stage have finished
+    uint64_t* accum_full = bars + 3 * kStages;      // [2] every MMA of the item has finished
+    uint64_t* accum_empty = bars + 3 * kStages + 2; // [2] the epilogue has read the accumulator
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 4);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // tiles that share a row block of A are neighbours in launch order, so A comes from HBM once
-    const int m0 = (blockIdx.x / p.n_tiles) * BM, n0 = (blockIdx.x % p.n_tiles) * BN;
-    const int kb_total = (p.K + BK - 1) / BK;
-    const int kb_begin = blockIdx.z * p.kb_per_split;
-    const int kb_end = min(kb_total, kb_begin + p.kb_per_split);
-    const int num_kb = kb_end - kb_begin;
-    if (num_kb <= 0) return;   // uniform over the CTA
+    const int total_items = p.total_tiles * p.n_splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -215,13 +237,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(&full_split[s], 4);
             mbar_init(&empty[s], 1);
         }
-        mbar_init(accum_full, 1);
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&accum_full[a], 1);
+            mbar_init(&accum_empty[a], 4);
+        }
         *abort_flag = 0;
         mbar_fence_init();
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::
-                         "r"(smem_u32(tmem_slot)), "r"(static_cast<uint32_t>(BN))
+                         "r"(smem_u32(tmem_slot)), "r"(static_cast<uint32_t>(2 * BN))
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -231,141 +256,164 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
 
     auto stage_ptr = [&](int s) { return tiles + s * T::kStageBytes; };
+    auto give_up = [&]() {
+        atomicOr(p.status, kStatusGemmTimeout);
+        *abort_flag = 1;
+    };
 
     if (warp == 0) {
         // ---------------- producer ----------------
         if (lane == 0) {
-            int issued = 0;
-            for (int i = 0; i < num_kb && !*abort_flag; ++i) {
-                const int s = i % kStages;
-                const uint32_t round = static_cast<uint32_t>(i / kStages);
-                if (!gemm_wait(&empty[s], (round & 1u) ^ 1u)) {
-                    atomicOr(p.status, kStatusGemmTimeout);
-                    *abort_flag = 1;
-                    break;
+            uint32_t it = 0;   // k-blocks issued so far, over all items
+            for (int w = blockIdx.x; w < total_items && !*abort_flag; w += gridDim.x) {
+                const WorkItem wi = work_item<BN, BK>(p, w);
+                for (int i = 0; i < wi.num_kb && !*abort_flag; ++i, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t round = it / kStages;
+                    if (!gemm_wait(&empty[s], (round & 1u) ^ 1u)) {
+                        give_up();
+                        break;
+                    }
+                    uint8_t* st = stage_ptr(s);
+                    mbar_expect_tx(&full_raw[s], kTileABytes + T::kTileBBytes);
+                    const int k0 = (wi.kb_begin + i) * BK;
+                    if (p.mn_major) {
+                        tma_load_3d(st, &map_a, 0, k0, wi.m0 / 32, &full_raw[s]);
+                        tma_load_3d(st + kTileABytes, &map_b, 0, k0, wi.n0 / 32, &full_raw[s]);
+                    } else {
+                        tma_load_2d(st, &map_a, k0, wi.m0, &full_raw[s]);
+                        tma_load_2d(st + kTileABytes, &map_b, k0, wi.n0, &full_raw[s]);
+                    }
                 }
-                uint8_t* st = stage_ptr(s);
-                mbar_expect_tx(&full_raw[s], kTileABytes + T::kTileBBytes);
-                const int k0 = (kb_begin + i) * BK;
-                if (p.mn_major) {
-                    tma_load_3d(st, &map_a, 0, k0, m0 / 32, &full_raw[s]);
-                    tma_load_3d(st + kTileABytes, &map_b, 0, k0, n0 / 32, &full_raw[s]);
-                } else {
-                    tma_load_2d(st, &map_a, k0, m0, &full_raw[s]);
-                    tma_load_2d(st + kTileABytes, &map_b, k0, n0, &full_raw[s]);
-                }
-                issued = i + 1;
             }
             if (*abort_flag) {
                 // let the copies that were issued land before the CTA goes away
-                for (int i = max(0, issued - kStages); i < issued; ++i)
-                    gemm_wait(&full_raw[i % kStages], static_cast<uint32_t>(i / kStages) & 1u);
+                const uint32_t first = it > static_cast<uint32_t>(kStages) ? it - kStages : 0u;
+                for (uint32_t j = first; j < it; ++j)
+                    gemm_wait(&full_raw[j % kStages], (j / kStages) & 1u);
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issue ----------------
         if (lane == 0) {
             const uint32_t idesc = instr_desc<BN>(p.mn_major != 0);
+            uint32_t it = 0, item = 0;
             bool ok = true;
-            for (int i = 0; i < num_kb && ok; ++i) {
-                const int s = i % kStages;
-                const uint32_t round = static_cast<uint32_t>(i / kStages);
-                if (*abort_flag || !gemm_wait(&full_split[s], round & 1u)) {
-                    atomicOr(p.status, kStatusGemmTimeout);
-                    *abort_flag = 1;
+            for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x, ++item) {
+                const WorkItem wi = work_item<BN, BK>(p, w);
+                const uint32_t acc = item & 1u, use = item >> 1;
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                // the epilogue must have drained this accumulator's previous item
+                if (*abort_flag || !gemm_wait(&accum_empty[acc], (use & 1u) ^ 1u)) {
+                    give_up();
                     ok = false;
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_hi = smem_u32(stage_ptr(s));
-                const uint32_t b_hi = a_hi + kTileABytes;
-                const uint32_t a_lo = b_hi + T::kTileBBytes;   // only present when PASSES == 3
-                const uint32_t b_lo = a_lo + kTileABytes;
+                for (int i = 0; i < wi.num_kb; ++i, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t round = it / kStages;
+                    if (*abort_flag || !gemm_wait(&full_split[s], round & 1u)) {
+                        give_up();
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_hi = smem_u32(stage_ptr(s));
+                    const uint32_t b_hi = a_hi + kTileABytes;
+                    const uint32_t a_lo = b_hi + T::kTileBBytes;   // only present when PASSES == 3
+                    const uint32_t b_lo = a_lo + kTileABytes;
 #pragma unroll
-                for (int kk = 0; kk < BK / 8; ++kk) {
-                    uint64_t dah, dal, dbh, dbl;
-                    if (p.mn_major) {
-                        const uint32_t off = kk * 1024;       // next group of 8 k
-                        constexpr uint32_t kBlock = BK * 128;  // 32 rows x BK k
-                        dah = operand_desc_mn(a_hi + off, kBlock);
-                        dal = operand_desc_mn(a_lo + off, kBlock);
-                        dbh = operand_desc_mn(b_hi + off, kBlock);
-                        dbl = operand_desc_mn(b_lo + off, kBlock);
-                    } else {
-                        const uint32_t off = kk * 32;         // 8 TF32 values along k
-                        dah = operand_desc<T::kRowBytes>(a_hi + off);
-                        dal = operand_desc<T::kRowBytes>(a_lo + off);
-                        dbh = operand_desc<T::kRowBytes>(b_hi + off);
-                        dbl = operand_desc<T::kRowBytes>(b_lo + off);
+                    for (int kk = 0; kk < BK / 8; ++kk) {
+                        uint64_t dah, dal, dbh, dbl;
+                        if (p.mn_major) {
+                            const uint32_t off = kk * 1024;       // next group of 8 k
+                            constexpr uint32_t kBlock = BK * 128;  // 32 rows x BK k
+                            dah = operand_desc_mn(a_hi + off, kBlock);
+                            dal = operand_desc_mn(a_lo + off, kBlock);
+                            dbh = operand_desc_mn(b_hi + off, kBlock);
+                            dbl = operand_desc_mn(b_lo + off, kBlock);
+                        } else {
+                            const uint32_t off = kk * 32;         // 8 TF32 values along k
+                            dah = operand_desc<T::kRowBytes>(a_hi + off);
+                            dal = operand_desc<T::kRowBytes>(a_lo + off);
+                            dbh = operand_desc<T::kRowBytes>(b_hi + off);
+                            dbl = operand_desc<T::kRowBytes>(b_lo + off);
+                        }
+                        const uint32_t fresh = (i > 0 || kk > 0) ? 1u : 0u;
+                        if (PASSES == 3) {
+                            mma_tf32(tmem_d, dal, dbh, idesc, fresh);
+                            mma_tf32(tmem_d, dah, dbl, idesc, 1u);
+                            mma_tf32(tmem_d, dah, dbh, idesc, 1u);
+                        } else {
+                            // the tensor core reads the upper 19 bits of each fp32 operand
+                            mma_tf32(tmem_d, dah, dbh, idesc, fresh);
+                        }
                     }
-                    const uint32_t fresh = (i > 0 || kk > 0) ? 1u : 0u;
-                    if (PASSES == 3) {
-                        mma_tf32(tmem_base, dal, dbh, idesc, fresh);
-                        mma_tf32(tmem_base, dah, dbl, idesc, 1u);
-                        mma_tf32(tmem_base, dah, dbh, idesc, 1u);
-                    } else {
-                        // the tensor core reads the upper 19 bits of each fp32 operand
-                        mma_tf32(tmem_base, dah, dbh, idesc, fresh);
-                    }
+                    mma_commit(&empty[s]);   // arrives when these MMAs no longer read the stage
                 }
-                mma_commit(&empty[s]);   // arrives when these MMAs no longer read the stage
+                if (ok) mma_commit(&accum_full[acc]);
             }
-            if (ok) mma_commit(accum_full);
+        }
+    } else if (warp < 6) {
+        // ---------------- splitters ----------------
+        const int t = threadIdx.x - 64;          // 0..127
+        uint32_t it = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
+            const WorkItem wi = work_item<BN, BK>(p, w);
+            for (int i = 0; i < wi.num_kb; ++i, ++it) {
+                const int s = it % kStages;
+                const uint32_t round = it / kStages;
+                if (*abort_flag || !gemm_wait(&full_raw[s], round & 1u)) {
+                    if (lane == 0) give_up();
+                    ok = false;
+                    break;
+                }
+                if (PASSES == 3) {
+                    // The tensor core uses the upper 19 bits of an fp32 operand (sign, exponent,
+                    // 10 mantissa bits) and ignores the rest, so the raw tile already acts as the
+                    // hi part; only lo = v - hi has to be produced. Raw A and B are contiguous,
+                    // and so are their lo parts behind them.
+                    const uint8_t* raw = stage_ptr(s);
+                    uint8_t* lo_buf = stage_ptr(s) + kTileABytes + T::kTileBBytes;
+#pragma unroll 4
+                    for (int v = t; v < (kTileABytes + T::kTileBBytes) / 16; v += 128) {
+                        const uint4 x = *reinterpret_cast<const uint4*>(raw + v * 16);
+                        uint4 lo;
+                        lo.x = __float_as_uint(__uint_as_float(x.x) - __uint_as_float(x.x & 0xffffe000u));
+                        lo.y = __float_as_uint(__uint_as_float(x.y) - __uint_as_float(x.y & 0xffffe000u));
+                        lo.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(x.z & 0xffffe000u));
+                        lo.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(x.w & 0xffffe000u));
+                        *reinterpret_cast<uint4*>(lo_buf + v * 16) = lo;
+                    }
+                    // make the generic-proxy writes visible to the tensor core's reads
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full_split[s]);
+            }
         }
     } else {
-        // ---------------- splitters, then epilogue ----------------
-        const int t = threadIdx.x - 64;          // 0..127
-        bool ok = true;
-        for (int i = 0; i < num_kb && ok; ++i) {
-            const int s = i % kStages;
-            const uint32_t round = static_cast<uint32_t>(i / kStages);
-            if (*abort_flag || !gemm_wait(&full_raw[s], round & 1u)) {
-                if (lane == 0) atomicOr(p.status, kStatusGemmTimeout);
-                *abort_flag = 1;
-                ok = false;
+        // ---------------- epilogue ----------------
+        const int q = warp & 3;                       // tensor-memory lane quarter of this warp
+        const bool vec_ok = (p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+        uint32_t item = 0;
+        for (int w = blockIdx.x; w < total_items; w += gridDim.x, ++item) {
+            const WorkItem wi = work_item<BN, BK>(p, w);
+            const uint32_t acc = item & 1u, use = item >> 1;
+            if (*abort_flag || !gemm_wait(&accum_full[acc], use & 1u)) {
+                if (lane == 0) give_up();
                 break;
             }
-            uint8_t* st = stage_ptr(s);
-            // The tensor core uses the upper 19 bits of an fp32 operand (sign, exponent, 10
-            // mantissa bits) and ignores the rest, so the raw tile already acts as the hi part;
-            // only lo = v - hi has to be produced.
-            auto split = [&](const uint8_t* raw, uint8_t* lo_buf, int vecs) {
-#pragma unroll 4
-                for (int v = t; v < vecs; v += 128) {
-                    const uint4 x = *reinterpret_cast<const uint4*>(raw + v * 16);
-                    uint4 lo;
-                    lo.x = __float_as_uint(__uint_as_float(x.x) - __uint_as_float(x.x & 0xffffe000u));
-                    lo.y = __float_as_uint(__uint_as_float(x.y) - __uint_as_float(x.y & 0xffffe000u));
-                    lo.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(x.z & 0xffffe000u));
-                    lo.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(x.w & 0xffffe000u));
-                    *reinterpret_cast<uint4*>(lo_buf + v * 16) = lo;
-                }
-            };
-            if (PASSES == 3) {
-                // raw A and B are contiguous, and so are their lo parts behind them
-                split(st, st + kTileABytes + T::kTileBBytes, (kTileABytes + T::kTileBBytes) / 16);
-                // make the generic-proxy writes visible to the tensor core's reads
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&full_split[s]);
-        }
-        if (ok && !gemm_wait(accum_full, 0)) {
-            if (lane == 0) atomicOr(p.status, kStatusGemmTimeout);
-            *abort_flag = 1;
-            ok = false;
-        }
-        if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int q = warp & 3;                       // tensor-memory lane quarter of this warp
-            const int m = m0 + 32 * q + lane;
-            const bool vec_ok = (p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+            const int m = wi.m0 + 32 * q + lane;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t r[32];
-                tmem_load_32(tmem_base + (static_cast<uint32_t>(32 * q) << 16) + c * 32, r);
+                tmem_load_32(tmem_base + (static_cast<uint32_t>(32 * q) << 16) + acc * BN + c * 32, r);
                 if (m >= p.M) continue;
-                const int n_first = n0 + c * 32;
+                const int n_first = wi.n0 + c * 32;
                 float* row = p.C + static_cast<long long>(m) * p.ldc;
 #pragma unroll
                 for (int j = 0; j < 32; j += 4) {
@@ -391,13 +439,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                 }
             }
+            // hand the accumulator back to the MMA warp
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&accum_empty[acc]);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                     "r"(static_cast<uint32_t>(BN))
+                     "r"(static_cast<uint32_t>(2 * BN))
                      : "memory");
     }
 }
@@ -503,13 +555,21 @@ cudaError_t launch(const GemmArgs& g, int splits, int* status, cudaStream_t stre
     p.N = g.N;
     p.K = g.K;
     p.kb_per_split = (kb_total + splits - 1) / splits;
-    p.reduce = splits > 1 ? 1 : 0;
+    p.n_splits = (kb_total + p.kb_per_split - 1) / p.kb_per_split;   // no part is empty
+    p.reduce = p.n_splits > 1 ? 1 : 0;
     p.status = status;
     p.n_tiles = (g.N + BN - 1) / BN;
     p.mn_major = mn_major ? 1 : 0;
     const long long tiles = static_cast<long long>((g.M + BM - 1) / BM) * p.n_tiles;
-    if (tiles >= (1ll << 31)) return cudaErrorInvalidValue;
-    const dim3 grid(static_cast<unsigned>(tiles), 1, (kb_total + p.kb_per_split - 1) / p.kb_per_split);
+    if (tiles * p.n_splits >= (1ll << 31)) return cudaErrorInvalidValue;
+    p.total_tiles = static_cast<int>(tiles);
+    int dev = 0, sms = 0;
+    e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    const long long items = tiles * p.n_splits;
+    const dim3 grid(static_cast<unsigned>(items < sms ? items : sms));   // one CTA per SM
     gemm_tc_kernel<BN, PASSES><<<grid, kGemmThreads, Tile<BN, PASSES>::kSmemBytes, stream>>>(map_a, map_b, p);
     return cudaGetLastError();
 }
