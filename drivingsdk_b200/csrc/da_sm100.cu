@@ -63,7 +63,7 @@ __host__ __device__ inline uint32_t da_warp_smem(int G, bool backward) {
 }
 
 template <int LPR, int NV, bool SCALAR, bool BACKWARD>
-__global__ void __launch_bounds__(kThreadsPerCta, 2) da_kernel(const __grid_constant__ DaParams p) {
+__global__ void __launch_bounds__(kThreadsPerCta, BACKWARD ? 3 : 2) da_kernel(const __grid_constant__ DaParams p) {
     constexpr int VEC = SCALAR ? 1 : 4;
     constexpr int RPI = 32 / LPR;
     constexpr int UNROLL = (RPI >= 16) ? 2 : 4;
@@ -100,7 +100,8 @@ __global__ void __launch_bounds__(kThreadsPerCta, 2) da_kernel(const __grid_cons
         const int ch = SCALAR ? (j + 32 * k) : (j + k * LPR) * 4;
         grp[k] = min(ch / p.cpg, G - 1);
     }
-    const int lpg = SCALAR ? 1 : max(1, p.cpg / 4);   // lanes that share one group of a row
+    const int lpg = SCALAR ? 1 : max(1, p.cpg / 4);   // lanes that share one group of a row (2^k)
+    const bool group_writer = (j & (lpg - 1)) == 0;   // the lane that stores a group's dot product
 
     const long long stride = static_cast<long long>(gridDim.x) * kWarpsPerCta;
     for (long long task = static_cast<long long>(blockIdx.x) * kWarpsPerCta + warp;
@@ -211,9 +212,10 @@ __global__ void __launch_bounds__(kThreadsPerCta, 2) da_kernel(const __grid_cons
                                                   w * go[k][3]);
                                 }
                                 // sum over the lanes that hold this group's pieces of the row
-                                for (int off = lpg >> 1; off >= 1; off >>= 1)
-                                    part += __shfl_xor_sync(0xffffffffu, part, off);
-                                if (slot < slot_end && (j % lpg) == 0)
+#pragma unroll
+                                for (int off = 16; off >= 1; off >>= 1)
+                                    if (off < lpg) part += __shfl_xor_sync(0xffffffffu, part, off);
+                                if (slot < slot_end && group_writer)
                                     s_A[sl * astride + (slot & 3) * G + grp[k]] = part;
                             }
                         }
