@@ -80,3 +80,27 @@ def test_tuning_knobs_round_trip():
     lib.msda_sm100_tune(capi.TUNE_STAGE, old)
     assert lib.msda_sm100_tune(capi.TUNE_STAGE, -1) == old
     assert lib.msda_sm100_tune(99, 1) == -2
+
+
+def test_deformable_convolution_shape_validation_needs_no_device():
+    """dcn_sm100_*: sizes are derived and checked on the host before anything is launched."""
+    lib = capi.load()
+    ok = capi.DcnShape(2, 7, 9, 8, 7, 9, 16, 3, 3, 1, 1, 1, 1, 1, 1, 1, 1)
+    assert lib.dcn_sm100_columns_bytes(ctypes.byref(ok)) == 4 * 2 * 7 * 9 * 9 * 8
+    assert lib.dcn_sm100_backward_workspace_bytes(ctypes.byref(ok)) >= 4 * 2 * 7 * 9 * 9 * 8
+    wrong_out = capi.DcnShape(2, 7, 9, 8, 6, 9, 16, 3, 3, 1, 1, 1, 1, 1, 1, 1, 1)   # Ho != conv size
+    assert lib.dcn_sm100_columns_bytes(ctypes.byref(wrong_out)) == 0
+    bad_groups = capi.DcnShape(2, 7, 9, 8, 7, 9, 16, 3, 3, 1, 1, 1, 1, 1, 1, 3, 1)  # 8 % 3 != 0
+    assert lib.dcn_sm100_columns_bytes(ctypes.byref(bad_groups)) == 0
+    one = ctypes.c_void_p(16)
+    assert lib.dcn_sm100_forward(None, one, None, one, None, one, one, ctypes.byref(ok), None) == -1
+    assert lib.dcn_sm100_forward(one, one, None, one, None, one, one, ctypes.byref(wrong_out), None) == -2
+    # mask without grad_mask (or the reverse) is refused
+    assert lib.dcn_sm100_backward(one, one, one, one, one, one, one, one, None, one, None, one, 1 << 30,
+                                  ctypes.byref(ok), None) == -1
+    assert lib.dcn_sm100_use_tensor_cores(-1) in (0, 1, 2)
+    assert lib.gemm_nt_sm100_f32(one, 8, one, 8, one, 4, None, 4, 4, 16, 1, None) == -2   # lda < K
+    assert lib.addrelu_sm100_forward(None, one, 4, capi.F32, None) == -1
+    assert lib.addrelu_sm100_forward(one, one, 0, capi.F32, None) == 0
+    assert lib.addrelu_sm100_forward(one, one, 4, 9, None) == -5
+    assert lib.maxpool_sm100_forward(one, one, 1, 1, -1, 4, capi.F32, None) == -2

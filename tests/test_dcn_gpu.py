@@ -204,3 +204,44 @@ def test_argument_checks():
         mx_driving.deform_conv2d(x, torch.zeros(1, 18, 4, 5, device="cuda"), w, 1, 1)
     with pytest.raises(RuntimeError):                 # CPU tensors
         mx_driving.deform_conv2d(x.cpu(), off.cpu(), w.cpu(), 1, 1)
+
+
+def test_full_size_identities_and_agreement_of_the_product_kernels():
+    """The reference's unit-test shape (N=18, C=Co=512, 29x50; tests/torch/test_deformable_conv2d.py:59)
+    is too large for the CPU oracle, so it is checked through properties that hold at any size:
+    the operator is linear in x and in the weights for fixed offsets and masks, hence
+    <grad_out, out> = <grad_x, x> = <grad_weight, weight> = <grad_mask, mask>; and the tensor-core
+    products must agree with the fp32 FMA products."""
+    import mx_driving
+    from drivingsdk_b200 import _C
+    N, C, Co, H, W = 18, 512, 512, 29, 50
+    g = torch.Generator().manual_seed(11)
+    u = lambda lo, hi, *shape: (torch.rand(*shape, generator=g) * (hi - lo) + lo).cuda()
+    x, off, mask = u(-5, 5, N, C, H, W), u(-5, 5, N, 18, H, W), u(-5, 5, N, 9, H, W)
+    w, go = u(-0.05, 0.05, Co, C, 3, 3), u(-1, 1, N, Co, H, W)
+    results = {}
+    for mode in (1, 0):
+        old = _C.dcn_use_tensor_cores(mode)
+        try:
+            xt, ot, mt, wt = (t.clone().requires_grad_() for t in (x, off, mask, w))
+            out = mx_driving.modulated_deform_conv2d(xt, ot, mt, wt, None, 1, 1, 1)
+            out.backward(go)
+            results[mode] = (out.detach(), xt.grad, ot.grad, mt.grad, wt.grad)
+        finally:
+            _C.dcn_use_tensor_cores(old)
+    out, gx, goff, gmask, gw = results[1]
+    dot = lambda a, b: (a.double() * b.double()).sum().item()
+    ref = dot(go, out)
+    # the inner products cancel heavily (13 M terms of either sign), so the bar is relative to
+    # the norms of the factors, not to the result
+    bar = 1e-5 * go.double().norm().item() * out.double().norm().item()
+    for name, val in (("x", dot(gx, x)), ("weight", dot(gw, w)), ("mask", dot(gmask, mask))):
+        assert abs(val - ref) <= bar, (name, val, ref, bar)
+    for name, a, b in zip(("out", "grad_x", "grad_offset", "grad_mask", "grad_weight"), results[1], results[0]):
+        scale = b.abs().max().item()
+        err = (a - b).abs().max().item()
+        assert err <= 1e-4 * scale, (name, err, scale)
+    # linearity in x for fixed offsets and masks
+    with torch.no_grad():
+        o2 = mx_driving.modulated_deform_conv2d(2.5 * x, off, mask, w, None, 1, 1, 1)
+    assert (o2 - 2.5 * out).abs().max().item() <= 1e-4 * out.abs().max().item()
