@@ -527,18 +527,15 @@ bool mn_major_ok(const GemmArgs& g) {
 
 template <int BN, int PASSES>
 cudaError_t launch(const GemmArgs& g, int splits, int* status, cudaStream_t stream) {
-    static std::atomic<int> configured{0};
-    if (!configured.load(std::memory_order_acquire)) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, PASSES>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             Tile<BN, PASSES>::kSmemBytes);
-        if (e != cudaSuccess) return e;
-        configured.store(1, std::memory_order_release);
-    }
+    // per device and cheap, so set on every launch (a process may drive several devices)
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, PASSES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Tile<BN, PASSES>::kSmemBytes);
+    if (e != cudaSuccess) return e;
     CUtensorMap map_a, map_b;
     constexpr int BK = Tile<BN, PASSES>::BK;
     const bool mn_major = !k_major_ok(g);
-    cudaError_t e = mn_major ? make_map_mn(&map_a, g.A, g.a_k, g.M, g.K, BM, BK)
+    e = mn_major ? make_map_mn(&map_a, g.A, g.a_k, g.M, g.K, BM, BK)
                              : make_map(&map_a, g.A, g.a_row, g.M, g.K, BM, BK);
     if (e != cudaSuccess) return e;
     e = mn_major ? make_map_mn(&map_b, g.B, g.b_k, g.N, g.K, BN, BK)
