@@ -245,3 +245,26 @@ def test_full_size_identities_and_agreement_of_the_product_kernels():
     with torch.no_grad():
         o2 = mx_driving.modulated_deform_conv2d(2.5 * x, off, mask, w, None, 1, 1, 1)
     assert (o2 - 2.5 * out).abs().max().item() <= 1e-4 * out.abs().max().item()
+
+
+def test_sixteen_bit_inputs_are_computed_in_fp32():
+    """fp16 / bf16 tensors are converted, computed in fp32 and returned in their own dtype
+    (the reference wraps the modulated operator in custom_fwd(cast_inputs=float32),
+    mx_driving/ops/modulated_deform_conv2d.py:21-26)."""
+    import mx_driving
+    g = torch.Generator().manual_seed(5)
+    u = lambda lo, hi, *shape: (torch.rand(*shape, generator=g) * (hi - lo) + lo).cuda()
+    x, off, mask, w = u(-2, 2, 2, 16, 8, 9), u(-2, 2, 2, 18, 8, 9), u(0, 1, 2, 9, 8, 9), u(-0.2, 0.2, 8, 16, 3, 3)
+    want = mx_driving.modulated_deform_conv2d(x, off, mask, w, None, 1, 1, 1)
+    for dtype in (torch.float16, torch.bfloat16):
+        xh, oh, mh, wh = (t.to(dtype).requires_grad_() for t in (x, off, mask, w))
+        ref = mx_driving.modulated_deform_conv2d(xh.float(), oh.float(), mh.float(), wh.float(), None, 1, 1, 1)
+        out = mx_driving.deform_conv2d(xh, oh, wh, 1, 1, 1)
+        assert out.dtype == dtype
+        with torch.autocast("cuda", dtype=dtype):
+            outm = mx_driving.modulated_deform_conv2d(xh, oh, mh, wh, None, 1, 1, 1)
+        assert outm.dtype == torch.float32          # cast_inputs=float32, as in the reference
+        torch.testing.assert_close(outm, ref.detach(), rtol=1e-4, atol=1e-4)
+        outm.sum().backward()
+        assert xh.grad.dtype == dtype and wh.grad.dtype == dtype and mh.grad is not None
+    assert torch.isfinite(want).all()
