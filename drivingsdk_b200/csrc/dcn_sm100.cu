@@ -360,6 +360,27 @@ int product(const msda::GemmArgs& g, int splits, int* status_word, cudaStream_t 
 
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Into how many parts to cut K for a product with few output tiles, so that the persistent
+// kernel's CTAs (one per SM) all finish together: the smallest count whose work items fill
+// their last round of `sms` to at least 90 %, else the count that fills it best.
+int balanced_splits(long long tiles, int sms, int max_splits) {
+    if (max_splits < 1) max_splits = 1;
+    if (max_splits > 64) max_splits = 64;
+    int best = 1;
+    double best_fill = 0.0;
+    for (int s = 1; s <= max_splits; ++s) {
+        const long long items = tiles * s;
+        const long long rounds = (items + sms - 1) / sms;
+        const double fill = static_cast<double>(items) / static_cast<double>(rounds * sms);
+        if (fill >= 0.9) return s;
+        if (fill > best_fill) {
+            best_fill = fill;
+            best = s;
+        }
+    }
+    return best;
+}
+
 // Layout of the backward's scratch memory.
 struct Workspace {
     size_t grad_columns, weight_t, total;
@@ -591,10 +612,7 @@ int dcn_sm100_backward(const float* x, const float* offset, const float* mask,
             int splits = 1;
             if (tc && msda::gemm_tc_supported(a)) {
                 const long long tiles = ((d.Cog + 127) / 128) * static_cast<long long>((d.Kd + 255) / 256);
-                splits = static_cast<int>((2ll * sms + tiles - 1) / tiles);
-                const int max_splits = (M + 1023) / 1024;
-                if (splits > max_splits) splits = max_splits;
-                if (splits < 1) splits = 1;
+                splits = balanced_splits(tiles, sms, (M + 1023) / 1024);
                 if (splits > 1 && !zeroed) {
                     e = cudaMemsetAsync(grad_weight, 0, static_cast<size_t>(s->Co) * d.Kd * 4, stream);
                     if (e != cudaSuccess) return msda::note_cuda_error(e);
