@@ -7,7 +7,9 @@ Same surface as the reference's patcher for this path (mx_driving/patcher/__init
 ``Patcher``, ``Patch``, ``AtomicPatch``, ``BasePatch``, ``PatchStatus``, ``PatchResult``,
 ``MultiScaleDeformableAttention`` (alias ``MSDA``), ``DeformConv``, ``ModulatedDeformConv``,
 ``ResNetAddRelu``, ``ResNetMaxPool``, ``default_patcher``, the legacy functions
-``msda(module, options)``, ``dc``, ``mdc``, ``resnet_add_relu``, ``resnet_maxpool``, ``configure_patcher_logging`` and ``set_patcher_log_level``. The
+``msda(module, options)``, ``dc``, ``mdc``, ``resnet_add_relu``, ``resnet_maxpool``, ``configure_patcher_logging`` and ``set_patcher_log_level``; and the older builder-style
+API (``PatcherBuilder().add_module_patch("mmcv", Patch(msda)).build()``, ``legacy.py``) that
+the reference's model examples still use. The
 reference's other predefined patches (sparse convolution, dataset and optimizer shims, ...)
 belong to operators that are not part of this package.
 """
@@ -15,7 +17,7 @@ from typing import Dict, List, Type
 
 from .patcher_logger import configure_patcher_logging, patcher_logger, set_patcher_log_level
 from .reporting import PatchResult, PatchStatus
-from .patch import AtomicPatch, BasePatch, Patch
+from .patch import AtomicPatch, BasePatch, LegacyPatch, Patch
 from .patcher import Patcher, replace_with
 from .mmcv_patch import DeformConv, ModulatedDeformConv, MultiScaleDeformableAttention
 from .mmdet_patch import ResNetAddRelu, ResNetMaxPool
@@ -62,8 +64,16 @@ mdc = _create_legacy_patch_func(ModulatedDeformConv)
 resnet_add_relu = _create_legacy_patch_func(ResNetAddRelu)
 resnet_maxpool = _create_legacy_patch_func(ResNetMaxPool)
 
+from .legacy import (  # noqa: E402  (needs the registry above)
+    LegacyPatcherBuilder,
+    LegacyPatcherBuilder as PatcherBuilder,
+    LegacyPatchWrapper,
+    default_patcher_builder,
+)
+
 __all__ = [
-    "Patcher", "BasePatch", "Patch", "AtomicPatch", "replace_with",
+    "Patcher", "BasePatch", "Patch", "AtomicPatch", "LegacyPatch", "replace_with",
+    "PatcherBuilder", "LegacyPatcherBuilder", "LegacyPatchWrapper", "default_patcher_builder",
     "patcher_logger", "configure_patcher_logging", "set_patcher_log_level",
     "PatchStatus", "PatchResult",
     "default_patcher", "MultiScaleDeformableAttention", "MSDA", "msda",

@@ -216,13 +216,69 @@ class AtomicPatch(BasePatch):
         return f"AtomicPatch({self.target})"
 
 
+class LegacyPatch(BasePatch):
+    """Function-style patch of the old API: ``func(module, options)`` edits the imported
+    ``target_module`` in place (mx_driving/patcher/patch.py:562-700). A module that cannot be
+    imported, or a function that raises AttributeError / ImportError (its way of saying "not
+    needed here"), gives SKIPPED; any other exception gives FAILED."""
+
+    def __init__(self, func: Callable[..., Any], options: Optional[dict] = None,
+                 target_module: Optional[str] = None):
+        if target_module is None:
+            raise ValueError(
+                "LegacyPatch requires target_module parameter. "
+                f"Usage: LegacyPatch({getattr(func, '__name__', 'func')}, target_module='module_name')")
+        self.func = func
+        self.options = options or {}
+        self.target_module = target_module
+        self.is_applied = False
+        self._order = 0
+
+    @property
+    def name(self) -> str:
+        return getattr(self.func, "__patch_name__", None) or getattr(self.func, "__name__", "legacy_patch")
+
+    @property
+    def module(self) -> str:
+        return self.target_module
+
+    def apply(self) -> PatchResult:
+        if self.is_applied:
+            return PatchResult(PatchStatus.SKIPPED, self.name, self.module, "already applied")
+        mod = _import_module(self.target_module)
+        if mod is None:
+            return PatchResult(PatchStatus.SKIPPED, self.name, self.module,
+                               f"module not found: {self.target_module}")
+        try:
+            self.func(mod, self.options)
+        except (AttributeError, ImportError) as exc:
+            return PatchResult(PatchStatus.SKIPPED, self.name, self.module, str(exc))
+        except Exception as exc:  # a patch must never take the program down
+            return PatchResult(PatchStatus.FAILED, self.name, self.module, str(exc))
+        self.is_applied = True
+        return PatchResult(PatchStatus.APPLIED, self.name, self.module)
+
+    def __repr__(self) -> str:
+        return f"LegacyPatch({self.name})"
+
+
 class _PatchType(type(ABC)):
-    """Gives Patch subclasses a class-level ``name`` that defaults to the class name."""
+    """Gives Patch subclasses a class-level ``name`` that defaults to the class name, and keeps
+    the old call style alive: ``Patch(func)`` — the base class called with a patch function —
+    returns a ``LegacyPatchWrapper`` for the old ``PatcherBuilder`` API
+    (mx_driving/patcher/legacy.py:26-27)."""
 
     def __new__(mcls, clsname, bases, ns):
         if "name" not in ns and any(isinstance(b, _PatchType) for b in bases):
             ns["name"] = clsname
         return super().__new__(mcls, clsname, bases, ns)
+
+    def __call__(cls, *args, **kwargs):
+        if cls.__name__ == "Patch" and not any(isinstance(b, _PatchType) for b in cls.__bases__) \
+                and args and callable(args[0]) and not isinstance(args[0], type):
+            from .legacy import LegacyPatchWrapper
+            return LegacyPatchWrapper(*args, **kwargs)
+        return super().__call__(*args, **kwargs)
 
 
 class Patch(BasePatch, metaclass=_PatchType):

@@ -22,6 +22,7 @@ class Patcher:
         self._applied = False
         self._resolved: Dict[int, List[BasePatch]] = {}
         self.results: List[PatchResult] = []
+        self._inert_requests: List[str] = []
 
     # ------------------------------------------------------------------ building
     @staticmethod
@@ -64,6 +65,19 @@ class Patcher:
                 patcher_logger.warning(
                     f"Patch '{new_cls.name}' conflicts with already-enabled patch '{cls.name}'; "
                     f"disable one of them, e.g. patcher.disable('{cls.name}')")
+
+    # Training-loop shims of the reference (mx_driving/patcher/patcher.py:672-707): they patch
+    # the mmcv / mmengine runners to drive the NPU profiler or to stop a run after N steps.
+    # The calls are accepted so that existing launch scripts keep working; they change nothing
+    # here, and apply() says so once.
+    def with_profiling(self, path: str, level: int = 0, skip_first: int = 20, wait: int = 1,
+                       warmup: int = 1, active: int = 1, repeat: int = 1) -> "Patcher":
+        self._inert_requests.append(f"with_profiling(path={path!r})")
+        return self
+
+    def brake_at(self, step: int) -> "Patcher":
+        self._inert_requests.append(f"brake_at({step})")
+        return self
 
     # ------------------------------------------------------------------ inspection
     def collect(self) -> List[Tuple[BasePatch, str]]:
@@ -131,6 +145,9 @@ class Patcher:
             return self
         for patch, group in self.collect():
             self._apply_one(patch, group)
+        for request in self._inert_requests:
+            patcher_logger.warning(
+                f"{request}: training-loop shims are not part of this package; ignored")
         self._applied = True
         patcher_logger.flush_summary()
         return self

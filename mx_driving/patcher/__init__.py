@@ -6,12 +6,12 @@ from drivingsdk_b200 import patcher as _impl
 from drivingsdk_b200.patcher import *  # noqa: F401,F403
 from drivingsdk_b200.patcher import (  # noqa: F401
     _ALL_PATCH_CLASSES, _DEFAULT_PATCH_CLASSES, _LEGACY_NAME_TO_CLASS,
-    mmcv_patch, mmdet_patch, patch, patcher, patcher_logger as _logger_obj, reporting,
+    legacy, mmcv_patch, mmdet_patch, patch, patcher, patcher_logger as _logger_obj, reporting,
 )
 import drivingsdk_b200.patcher.patcher_logger as _logger_mod
 
 __all__ = list(_impl.__all__)
 
 for _name, _mod in (("patch", patch), ("patcher", patcher), ("reporting", reporting),
-                    ("mmcv_patch", mmcv_patch), ("mmdet_patch", mmdet_patch), ("patcher_logger", _logger_mod)):
+                    ("legacy", legacy), ("mmcv_patch", mmcv_patch), ("mmdet_patch", mmdet_patch), ("patcher_logger", _logger_mod)):
     sys.modules[f"{__name__}.{_name}"] = _mod

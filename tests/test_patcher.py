@@ -296,3 +296,53 @@ def test_deform_conv_patches_replace_function_class_and_functional_form():
                 sys.modules.pop(n, None)
             else:
                 sys.modules[n] = v
+
+
+def test_builder_style_api_of_the_model_examples(fake_mmcv, fake_operator):
+    """PatcherBuilder().add_module_patch("mmcv", Patch(msda)).build() as the reference's
+    model examples call it (mx_driving/patcher/legacy.py:8-18; e.g.
+    model_examples/Sparse4D/patch.py:1101-1115)."""
+    from mx_driving.patcher import LegacyPatchWrapper, Patch as P, PatcherBuilder, msda as msda_fn
+    calls = []
+
+    def custom(module, options):          # an example's own function-style patch
+        calls.append((module.__name__, options))
+        module.patched_by_custom = True
+
+    def not_needed(module, options):
+        raise AttributeError("already fine")
+
+    wrapped = P(msda_fn)
+    assert isinstance(wrapped, LegacyPatchWrapper) and wrapped.name == "msda"
+    builder = (PatcherBuilder()
+               .add_module_patch("mmcv", wrapped, P(custom, {"k": 1}), P(not_needed))
+               .add_module_patch("no_such_module_anywhere", P(custom))
+               .brake_at(500).with_profiling("/tmp/prof"))
+    with builder.build() as applied:
+        assert applied.is_applied
+        fn = fake_mmcv.MultiScaleDeformableAttnFunction
+        assert fn.forward("ctx", "v", "s", "l", "loc", "aw", 64) == "ours forward"
+    statuses = [(r.name, r.status) for r in applied.results]
+    assert (("custom", PatchStatus.APPLIED) in statuses and ("not_needed", PatchStatus.SKIPPED) in statuses)
+    assert sum(1 for _, st in statuses if st is PatchStatus.APPLIED) == 3      # 2 of msda + custom
+    assert [st for n, st in statuses if n == "custom"].count(PatchStatus.SKIPPED) == 1  # missing module
+    assert calls == [("mmcv", {"k": 1})] and sys.modules["mmcv"].patched_by_custom
+
+
+def test_builder_blacklist_priority_and_default_builder(fake_mmcv, fake_operator):
+    from mx_driving.patcher import Patch as P, PatcherBuilder, default_patcher_builder, msda as msda_fn
+    order = []
+    first = lambda m, o: order.append("first")
+    second = lambda m, o: order.append("second")
+    first.__name__, second.__name__ = "first", "second"
+    built = (PatcherBuilder()
+             .add_module_patch("mmcv", P(second, priority=5), P(first, priority=1), P(msda_fn))
+             .disable_patches("msda").build())
+    built.apply()
+    assert order == ["first", "second"]
+    assert fake_mmcv.MultiScaleDeformableAttnFunction.forward(0, 1, 2, 3, 4, 5, 6) == "mmcv forward"
+    default_patcher_builder.build().apply()
+    assert fake_mmcv.MultiScaleDeformableAttnFunction.forward(0, 1, 2, 3, 4, 5, 6) == "ours forward"
+    with pytest.raises(ValueError):
+        from mx_driving.patcher import LegacyPatch
+        LegacyPatch(first)
