@@ -12,8 +12,14 @@
 // loc * size - 0.5, corners outside the map read as zero (same rules as the bilinear MSDA
 // kernels, whose per-sample set-up and slot records are reused here).
 //
-// One warp per (batch, anchor). Samples (pts, cam, scale) are walked in passes of at most 32
-// (a multiple of `scales`, so the scales of one (pts, cam) never straddle passes):
+// One warp per task = (batch, camera, block of points, anchor): the points are cut into blocks
+// of floor(32 / scales), so a task's samples (point, scale) fill one warp pass and the scales
+// of one point never straddle tasks. Tasks are ordered batch-major, then camera: the warps in
+// flight at any time sample the maps of one or two cameras of one batch entry (15 MB each at
+// the Sparse4D shape), which stay in L2; walking all cameras of an anchor in one task instead
+// spread the working set over the whole batch entry (92 MB) and 4x the compulsory bytes came
+// from DRAM. The price: a task's output row is a partial sum, added into `out` with vector
+// reductions (out is zero-filled first; the order of those additions is not fixed).
 //   phase 1  lane = sample: slot records {row offset | no row, bilinear weight}; the pass's
 //            group weights are copied to shared memory.
 //   phase 2  lane = (row slot, 16-byte piece of the C-channel row): gather, multiply by
@@ -46,12 +52,13 @@ struct DaParams {
     const int* starts_dev;   // [cams*scales]
     int use_table;
     int B, F, C, A, Pts, cams, scales, G;
-    int S;         // samples per task: Pts * cams * scales
-    int pass;      // samples per warp pass: floor(32 / scales) * scales
+    int S;         // samples per (batch, anchor): Pts * cams * scales
+    int ppt;       // points per task: floor(32 / scales)
+    int nparts;    // blocks of points: ceil(Pts / ppt)
     int cpg;       // channels per group
     uint32_t row_units;
     uint32_t warp_smem;
-    long long ntasks;   // B * A
+    long long ntasks;   // B * cams * nparts * A
     int lv_h[kDaMaxMaps], lv_w[kDaMaxMaps], lv_start[kDaMaxMaps];
 };
 
@@ -106,7 +113,16 @@ __global__ void __launch_bounds__(kThreadsPerCta, BACKWARD ? 3 : 2) da_kernel(co
     const long long stride = static_cast<long long>(gridDim.x) * kWarpsPerCta;
     for (long long task = static_cast<long long>(blockIdx.x) * kWarpsPerCta + warp;
          task < p.ntasks; task += stride) {
-        const uint32_t b = static_cast<uint32_t>(task / p.A);
+        // task -> (b, cam, part, anchor); `row` = b * A + anchor indexes out / grad_out / loc / wts
+        const long long per_b = static_cast<long long>(p.cams) * p.nparts * p.A;
+        const uint32_t b = static_cast<uint32_t>(task / per_b);
+        const int rem = static_cast<int>(task - static_cast<long long>(b) * per_b);
+        const int anchor = rem % p.A;
+        const int part = (rem / p.A) % p.nparts;
+        const int cam = rem / (p.A * p.nparts);
+        const long long row = static_cast<long long>(b) * p.A + anchor;
+        const int pt0 = part * p.ppt;
+        const int ns = min(p.ppt, p.Pts - pt0) * p.scales;   // samples of this task
         float acc[NV][VEC];
         float go[NV][VEC];
 #pragma unroll
@@ -118,19 +134,17 @@ __global__ void __launch_bounds__(kThreadsPerCta, BACKWARD ? 3 : 2) da_kernel(co
             for (int k = 0; k < NV; ++k) {
                 if constexpr (!SCALAR) {
                     const float4 t = *reinterpret_cast<const float4*>(
-                        p.grad_out + task * p.C + (j + k * LPR) * 4);
+                        p.grad_out + row * p.C + (j + k * LPR) * 4);
                     go[k][0] = t.x; go[k][1] = t.y; go[k][2] = t.z; go[k][3] = t.w;
                 } else {
                     const int c = j + 32 * k;
-                    go[k][0] = (c < p.C) ? p.grad_out[task * p.C + c] : 0.f;
+                    go[k][0] = (c < p.C) ? p.grad_out[row * p.C + c] : 0.f;
                 }
             }
         }
 
-        for (int c0 = 0; c0 < p.S; c0 += p.pass) {
-            const int ns = min(p.pass, p.S - c0);
+        {
             // ---- phase 1: lane = sample ---------------------------------------------
-            const int s = c0 + lane;
             const bool active = lane < ns;
             uint4 rec01 = make_uint4(kNoRow, 0u, kNoRow, 0u);
             uint4 rec23 = rec01;
@@ -139,11 +153,10 @@ __global__ void __launch_bounds__(kThreadsPerCta, BACKWARD ? 3 : 2) da_kernel(co
             geom.valid = false;
             int pc = 0, scale = 0;
             if (active) {
-                scale = s % p.scales;
-                pc = s / p.scales;                 // pts * cams + cam
-                const int cam = pc % p.cams;
+                scale = lane % p.scales;
+                pc = (pt0 + lane / p.scales) * p.cams + cam;   // pts * cams + cam
                 const int map = cam * p.scales + scale;
-                const long long li = (task * p.Pts * p.cams + pc) * 2;
+                const long long li = (row * p.Pts * p.cams + pc) * 2;
                 const float lw_n = p.loc[li];
                 const float lh_n = p.loc[li + 1];
                 const bool inside = (lw_n > 0.f) && (lw_n < 1.f) && (lh_n > 0.f) && (lh_n < 1.f);
@@ -157,8 +170,12 @@ __global__ void __launch_bounds__(kThreadsPerCta, BACKWARD ? 3 : 2) da_kernel(co
             uint4* dst = reinterpret_cast<uint4*>(s_slot) + 2 * lane;
             dst[0] = rec01;
             dst[1] = rec23;
-            for (int i = lane; i < ns * G; i += 32)
-                s_wt[i] = p.wts[(task * p.S + c0) * G + i];
+            // the weights of one (point, camera) are scales * G contiguous floats
+            const int per_pt = p.scales * G;
+            for (int i = lane; i < ns * G; i += 32) {
+                const int ptl = i / per_pt;
+                s_wt[i] = p.wts[((row * p.Pts + pt0 + ptl) * p.cams + cam) * per_pt + (i - ptl * per_pt)];
+            }
             if constexpr (BACKWARD && SCALAR) {
                 for (int i = lane; i < kChunk * astride; i += 32) s_A[i] = 0.f;
             }
@@ -255,7 +272,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, BACKWARD ? 3 : 2) da_kernel(co
                     const float hw = 1.f - lw, hh = 1.f - lh;
                     const float b1 = hh * hw, b2 = hh * lw, b3 = lh * hw, b4 = lh * lw;
                     float T1 = 0.f, T2 = 0.f, T3 = 0.f, T4 = 0.f;
-                    float* gw = p.grad_wts + (task * p.S + s) * G;
+                    float* gw = p.grad_wts + ((row * p.Pts * p.cams + pc) * p.scales + scale) * G;
                     const float* A = s_A + lane * astride;
                     for (int q = 0; q < G; ++q) {
                         float a1 = 0.f, a2 = 0.f, a3 = 0.f, a4 = 0.f;
@@ -290,7 +307,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, BACKWARD ? 3 : 2) da_kernel(co
                     }
                 }
                 if (active && scale == 0) {
-                    const long long li = (task * p.Pts * p.cams + pc) * 2;
+                    const long long li = (row * p.Pts * p.cams + pc) * 2;
                     p.grad_loc[li] = sum_w;
                     p.grad_loc[li + 1] = sum_h;
                 }
@@ -309,11 +326,11 @@ __global__ void __launch_bounds__(kThreadsPerCta, BACKWARD ? 3 : 2) da_kernel(co
                 }
                 if (g == 0) {
                     if constexpr (!SCALAR) {
-                        *reinterpret_cast<float4*>(p.out + task * p.C + (j + k * LPR) * 4) =
-                            make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
+                        red_add_f32x4(p.out + row * p.C + (j + k * LPR) * 4, acc[k][0], acc[k][1],
+                                      acc[k][2], acc[k][3]);
                     } else {
                         const int c = j + 32 * k;
-                        if (c < p.C) p.out[task * p.C + c] = acc[k][0];
+                        if (c < p.C) atomicAdd(p.out + row * p.C + c, acc[k][0]);
                     }
                 }
             }
@@ -382,9 +399,10 @@ int da_common(DaParams& p, const void* feat, const int32_t* shapes, const int32_
     p.wts = static_cast<const float*>(wts);
     p.B = B; p.F = F; p.C = C; p.A = A; p.Pts = Pts; p.cams = cams; p.scales = scales; p.G = G;
     p.S = Pts * cams * scales;
-    p.pass = (msda::kChunk / scales) * scales;
+    p.ppt = msda::kChunk / scales;
+    p.nparts = (Pts + p.ppt - 1) / p.ppt;
     p.cpg = C / G;
-    p.ntasks = static_cast<long long>(B) * A;
+    p.ntasks = static_cast<long long>(B) * cams * p.nparts * A;
 
     cudaPointerAttributes attr;
     bool on_dev = false;
@@ -450,8 +468,10 @@ int da_sm100_forward(const void* feat, const int32_t* spatial_shape, const int32
     if (rc != MSDA_OK) return rc;
     p.out = static_cast<float*>(out);
     p.warp_smem = msda::da_warp_smem(G, false);
-    const cudaError_t e =
-        msda::da_launch<false>(p, scalar, lpr, nv, sms, static_cast<cudaStream_t>(stream));
+    cudaError_t e = cudaMemsetAsync(out, 0, static_cast<size_t>(B) * A * C * sizeof(float),
+                                    static_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess)
+        e = msda::da_launch<false>(p, scalar, lpr, nv, sms, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) {
         t_da_cuda_error = static_cast<int>(e);
         return MSDA_ERR_CUDA;
