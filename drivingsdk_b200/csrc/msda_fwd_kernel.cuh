@@ -174,20 +174,27 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
                     }
                 };
 
-                // full trips, then shorter ones, then single guarded instructions: a task with
-                // few slots (small L*P) does not pay for instructions that carry no row
+                // full trips, then the rest: a task with few slots left (small L*P) does not
+                // pay for instructions that carry no row
                 int base = slot_begin;
 #pragma unroll 1
                 for (; base < unguarded_end; base += STEP)
                     gather(base, std::integral_constant<int, UNROLL>{}, std::false_type{});
-                if constexpr (UNROLL > 2) {
+                if (slot_end - base > 2 * RPI) {
+                    // more than two instructions' worth left: one guarded trip at full width
+                    // keeps them all in flight (a chain of short trips is latency-bound)
+                    gather(base, std::integral_constant<int, UNROLL>{}, std::true_type{});
+                } else {
+                    if constexpr (UNROLL > 2) {
+                        if (base + 2 * RPI <= slot_end) {
+                            gather(base, std::integral_constant<int, 2>{}, std::false_type{});
+                            base += 2 * RPI;
+                        }
+                    }
 #pragma unroll 1
-                    for (; base + 2 * RPI <= slot_end; base += 2 * RPI)
-                        gather(base, std::integral_constant<int, 2>{}, std::false_type{});
+                    for (; base < slot_end; base += RPI)
+                        gather(base, std::integral_constant<int, 1>{}, std::true_type{});
                 }
-#pragma unroll 1
-                for (; base < slot_end; base += RPI)
-                    gather(base, std::integral_constant<int, 1>{}, std::true_type{});
 
                 // ---- epilogue ---------------------------------------------------
                 if (chunk == nchunks - 1) {

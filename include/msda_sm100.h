@@ -184,8 +184,9 @@ int gka_sm100_backward_ws(const void* value, const int32_t* spatial_shapes,
  *   (int32, host or device); sampling_location [B, A, Pts, cams, 2] (w, h) in (0, 1);
  *   weights [B, A, Pts, cams, scales, G]; out / grad_out [B, A, C].
  * A sample counts only if 0 < w < 1 and 0 < h < 1. Limits: C <= 256, C % G == 0, G <= 32,
- * scales <= 32, cams * scales <= 64. Backward zero-fills grad_feat on `stream` and fully
- * writes grad_sampling_location and grad_weights. */
+ * scales <= 32, cams * scales <= 64. Forward zero-fills `out` on `stream` and adds partial sums
+ * into it (the order of the fp32 additions is not fixed); backward zero-fills grad_feat on
+ * `stream` and fully writes grad_sampling_location and grad_weights. */
 int da_sm100_forward(const void* feat, const int32_t* spatial_shape, const int32_t* scale_start,
                      const void* sampling_location, const void* weights, void* out, int B, int F,
                      int C, int A, int Pts, int cams, int scales, int G, void* stream);
@@ -200,10 +201,13 @@ int da_sm100_last_cuda_error(void);
 size_t msda_sm100_forward_bytes(int B, int K, int H, int D, int L, int Q, int P, int dtype);
 size_t msda_sm100_backward_bytes(int B, int K, int H, int D, int L, int Q, int P, int dtype);
 
-/* Sticky device-side status of the current device (bit 0: a staged
+/* Sticky device-side status of the current device. Bit 0 (value 1): a staged
  * location/weight tile did not arrive within the polling limit and the kernel
- * fell back to direct loads). Synchronises the device. clear != 0 resets it.
- * Returns the status word (>= 0) or a negative msda_status. */
+ * fell back to direct loads (results are still correct). Bit 1 (value 2): a
+ * pipeline barrier of the tensor-core matrix product (conv_ops_sm100.h) timed
+ * out and the CTA stopped early (that call's results are undefined).
+ * Synchronises the device. clear != 0 resets it. Returns the status word
+ * (>= 0) or a negative msda_status. */
 int msda_sm100_device_status(int clear);
 
 /* Tuning knobs, process-wide. Returns the previous value, or MSDA_ERR_DIMS for
