@@ -21,6 +21,7 @@ constexpr int kMaxDevices = 64;
 __device__ int g_status_word;
 
 std::atomic<int> g_tune_stage{1};
+std::atomic<int> g_tune_interleave{1};
 std::atomic<int> g_tune_cps_fwd{0};
 std::atomic<int> g_tune_cps_bwd{0};
 std::atomic<long long> g_launches{0};
@@ -153,6 +154,22 @@ int fill_common(Params& p, const DeviceInfo* dev, const void* value, const int32
         }
     }
     const size_t e = elem_size(dtype);
+    // Interleave the batch entries in the walk when all of value stays in L2 whatever the
+    // order (a quarter of the 126 MB), every entry holds a whole number of items, and the
+    // counters fit the 32-bit fast division.
+    p.walk_b = 0;
+    p.walk_items_per_b = 0;
+    p.fd_walk_b = msda::make_fastdiv(1);
+    {
+        const long long tasks_per_b = static_cast<long long>(Q) * H;
+        const size_t value_bytes = static_cast<size_t>(B) * K * H * D * e;
+        if (g_tune_interleave.load() != 0 && B > 1 && value_bytes <= (32u << 20) &&
+            tasks_per_b % p.tasks_per_item == 0 && p.nitems < (1ll << 31)) {
+            p.walk_b = static_cast<uint32_t>(B);
+            p.walk_items_per_b = static_cast<uint32_t>(tasks_per_b / p.tasks_per_item);
+            p.fd_walk_b = msda::make_fastdiv(static_cast<uint32_t>(B));
+        }
+    }
     p.fd_qh = msda::make_fastdiv(static_cast<uint32_t>(Q) * static_cast<uint32_t>(H));
     p.fd_h = msda::make_fastdiv(static_cast<uint32_t>(H));
     p.fd_lp = msda::make_fastdiv(static_cast<uint32_t>(p.LP));
@@ -420,6 +437,7 @@ int msda_sm100_tune(int knob, int value) {
         case MSDA_TUNE_STAGE: target = &g_tune_stage; break;
         case MSDA_TUNE_CTAS_PER_SM: target = &g_tune_cps_fwd; break;
         case MSDA_TUNE_CTAS_PER_SM_BWD: target = &g_tune_cps_bwd; break;
+        case MSDA_TUNE_INTERLEAVE: target = &g_tune_interleave; break;
         default: return MSDA_ERR_DIMS;
     }
     if (value < 0) return target->load();

@@ -100,6 +100,10 @@ struct Params {
     uint32_t row_units;      // offset units per value row: 16-byte pieces, or elements (scalar path)
     uint32_t warp_smem;      // bytes of dynamic shared memory per warp
     FastDiv fd_qh, fd_h, fd_lp;  // division by Q*H, H, L*P
+    // walk order of the items: 0 = memory order; B > 0 = batch entries interleaved (walk
+    // position i -> item (i % B) * walk_items_per_b + i / B)
+    uint32_t walk_b, walk_items_per_b;
+    FastDiv fd_walk_b;
     LevelTable lv;
 };
 

@@ -56,17 +56,17 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
     ItemWalk walk = make_walk(p, warp);
     auto full = [&](long long it) { return (it + 1) * TPC <= p.ntasks; };
 
-    if (st.ok && lane == 0 && walk.idx < walk.end && full(walk.item())) {
-        st.issue(p, walk.item(), 0);
+    if (st.ok && lane == 0 && walk.idx < walk.end && full(walk.item(p))) {
+        st.issue(p, walk.item(p), 0);
     }
 
     for (int n = 0; walk.idx < walk.end; walk.idx += walk.stride, ++n) {
         const int buf = n & 1;
-        const long long item = walk.item();
+        const long long item = walk.item(p);
         const T* sloc = nullptr;
         const T* sattn = nullptr;
         if (st.ok) {
-            const long long next = walk.item_at(walk.idx + walk.stride);
+            const long long next = walk.item_at(p, walk.idx + walk.stride);
             if (lane == 0 && walk.idx + walk.stride < walk.end && full(next)) {
                 st.issue(p, next, buf ^ 1);
             }

@@ -80,8 +80,17 @@ __device__ __forceinline__ LaneLevels load_lane_levels(const Params& p, int lane
 // heads of one query).
 struct ItemWalk {
     long long idx, stride, end;
-    __device__ __forceinline__ long long item() const { return idx; }
-    __device__ __forceinline__ long long item_at(long long i) const { return i; }
+    __device__ __forceinline__ long long item(const Params& p) const { return item_at(p, idx); }
+    // Items are walked in memory order, which keeps the batch entry in flight L2-resident, or
+    // - when the host found the whole value tensor small enough to stay in L2 anyway - with
+    // the batch entries interleaved, so that the reductions of the warps in flight spread
+    // over all entries' gradient maps instead of piling onto one entry's few rows.
+    __device__ __forceinline__ long long item_at(const Params& p, long long i) const {
+        if (p.walk_b == 0) return i;
+        const uint32_t q = fd_div(static_cast<uint32_t>(i), p.fd_walk_b);
+        const uint32_t r = static_cast<uint32_t>(i) - q * p.walk_b;
+        return static_cast<long long>(r) * p.walk_items_per_b + q;
+    }
 };
 __device__ __forceinline__ ItemWalk make_walk(const Params& p, int warp) {
     ItemWalk w;

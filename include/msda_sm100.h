@@ -218,11 +218,17 @@ int msda_sm100_device_status(int clear);
  *                            0 = direct loads
  *   MSDA_TUNE_CTAS_PER_SM    persistent CTAs per SM for the forward kernel
  *                            (default 0 = as many as are resident at once)
- *   MSDA_TUNE_CTAS_PER_SM_BWD  same for the backward kernel */
+ *   MSDA_TUNE_CTAS_PER_SM_BWD  same for the backward kernel
+ *   MSDA_TUNE_INTERLEAVE     1 = when the whole value tensor is at most 32 MiB (it stays in L2
+ *                            whatever the order), walk the (batch, query, head) tasks with
+ *                            the batch entries interleaved, so that concurrent reductions
+ *                            spread over all entries' gradient maps (default); 0 = always
+ *                            walk in memory order */
 typedef enum msda_tune {
     MSDA_TUNE_STAGE = 0,
     MSDA_TUNE_CTAS_PER_SM = 1,
-    MSDA_TUNE_CTAS_PER_SM_BWD = 2
+    MSDA_TUNE_CTAS_PER_SM_BWD = 2,
+    MSDA_TUNE_INTERLEAVE = 3
 } msda_tune;
 int msda_sm100_tune(int knob, int value);
 
