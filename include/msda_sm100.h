@@ -219,7 +219,7 @@ int msda_sm100_device_status(int clear);
  *   MSDA_TUNE_CTAS_PER_SM    persistent CTAs per SM for the forward kernel
  *                            (default 0 = as many as are resident at once)
  *   MSDA_TUNE_CTAS_PER_SM_BWD  same for the backward kernel
- *   MSDA_TUNE_INTERLEAVE     1 = when the whole value tensor is at most 32 MiB (it stays in L2
+ *   MSDA_TUNE_INTERLEAVE     1 = when the whole value tensor is at most 16 MiB (it stays in L2
  *                            whatever the order), walk the (batch, query, head) tasks with
  *                            the batch entries interleaved, so that concurrent reductions
  *                            spread over all entries' gradient maps (default); 0 = always
