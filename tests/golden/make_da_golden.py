@@ -3,7 +3,7 @@ aggregation (tests/torch/test_deformable_aggregation.py:33-125, a method of its 
 cache decorator is bypassed through ``__wrapped__``). Inputs are seeded draws with several
 cameras and scales (the reference's own generator, :15-24, uses one camera and one 32x88
 map); some locations lie outside (0, 1) to exercise the skip rule. Needs the reference
-checkout (MSDA_REFERENCE_ROOT, default /root/reference).
+checkout: set MSDA_REFERENCE_ROOT to its directory.
 """
 import os
 import sys
@@ -12,7 +12,9 @@ import unittest
 
 import numpy as np
 
-REF = os.environ.get("MSDA_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("MSDA_REFERENCE_ROOT")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set MSDA_REFERENCE_ROOT to the directory of the reference checkout")
 OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "da_golden.npz")
 
 # name: (B, C, anchors, pts, G, maps[cam][scale] = (h, w))

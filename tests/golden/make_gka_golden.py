@@ -3,8 +3,8 @@ kernel attention (tests/torch/test_geometric_kernel_attention.py): its input gen
 `cpu_gen_inputs` (:20-41) and its CPU implementation `cpu_geometric_kernel_attention`
 (:44-92) + autograd (:95-103), run in float64 on seeded draws. `torch_npu` and `mx_driving`
 are stubbed (the module asks torch_npu for a device name at import); the cache decorator is
-bypassed through ``__wrapped__``. Needs the reference checkout (MSDA_REFERENCE_ROOT,
-default /root/reference).
+bypassed through ``__wrapped__``. Needs the reference checkout: set MSDA_REFERENCE_ROOT
+to its directory.
 """
 import os
 import sys
@@ -14,7 +14,9 @@ import unittest
 import numpy as np
 import torch
 
-REF = os.environ.get("MSDA_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("MSDA_REFERENCE_ROOT")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set MSDA_REFERENCE_ROOT to the directory of the reference checkout")
 OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "gka_golden.npz")
 
 # [bs, num_queries, embed_dims, num_heads, num_levels, num_points] as in the reference test

@@ -1,7 +1,7 @@
 """Generates tests/golden/msda_golden.npz from the REFERENCE's own golden functions.
 
-Run in a container that has the reference checkout (default /root/reference;
-override with MSDA_REFERENCE_ROOT). It imports the reference's unit-test module
+Run where the reference checkout is available, with MSDA_REFERENCE_ROOT set to its
+directory. It imports the reference's unit-test module
 tests/torch/test_multi_scale_deformable_attn.py unchanged — with `torch_npu`
 and `mx_driving` stubbed, because only the two pure-PyTorch golden functions
 are used — and records their float64 results on seeded inputs:
@@ -22,7 +22,9 @@ import unittest
 import numpy as np
 import torch
 
-REF = os.environ.get("MSDA_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("MSDA_REFERENCE_ROOT")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set MSDA_REFERENCE_ROOT to the directory of the reference checkout")
 OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "msda_golden.npz")
 
 # name: (B, Q, H, D, levels[(h, w)], P, dtype, loc range, seed)
