@@ -402,7 +402,6 @@ int public_product(const float* A, long long a_row, long long a_k, const float* 
                    int splits, void* stream_v) {
     if (A == nullptr || B == nullptr || C == nullptr) return MSDA_ERR_NULL;
     if (M <= 0 || N <= 0 || K <= 0 || ldc < N) return MSDA_ERR_DIMS;
-    if (splits > 1 && bias != nullptr) return MSDA_ERR_DIMS;
     int* status_word = nullptr;
     int rc = msda::device_facts(nullptr, &status_word);
     if (rc != MSDA_OK) return rc;
@@ -490,6 +489,7 @@ int dcn_sm100_forward(const float* x, const float* offset, const float* mask, co
     if (rc != MSDA_OK) return rc;
 
     const long long ld_cols = static_cast<long long>(s->groups) * d.Kd;
+    bool zeroed = false;
     for (int g = 0; g < s->groups; ++g) {
         msda::GemmArgs a{};
         a.A = columns + static_cast<size_t>(g) * d.Kd;
@@ -504,7 +504,18 @@ int dcn_sm100_forward(const float* x, const float* offset, const float* mask, co
         a.M = static_cast<int>(d.M);
         a.N = d.Cog;
         a.K = d.Kd;
-        rc = product(a, 1, status_word, stream);
+        // few output tiles (small batches): cut K so that every SM has work
+        int splits = 1;
+        if (g_use_tc.load(std::memory_order_relaxed) != 0 && msda::gemm_tc_supported(a)) {
+            const long long tiles = ((d.M + 127) / 128) * static_cast<long long>((d.Cog + 255) / 256);
+            if (2 * tiles <= sms) splits = balanced_splits(tiles, sms, (d.Kd + 255) / 256);
+            if (splits > 1 && !zeroed) {
+                const cudaError_t e = cudaMemsetAsync(out, 0, static_cast<size_t>(d.M) * s->Co * 4, stream);
+                if (e != cudaSuccess) return msda::note_cuda_error(e);
+                zeroed = true;
+            }
+        }
+        rc = product(a, splits, status_word, stream);
         if (rc != MSDA_OK) return rc;
     }
     return MSDA_OK;

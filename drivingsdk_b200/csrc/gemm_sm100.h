@@ -28,8 +28,8 @@ cudaError_t gemm_simt(const GemmArgs& g, cudaStream_t stream);
 // the grad_weight product, whose k is the pixel index). fp32 accuracy through a two-term TF32 split of
 // both operands (passes == 3: three tensor-core products per tile), or one TF32 product per
 // tile (passes == 1, about 1e-3 relative accuracy). `splits` > 1 cuts K into that many
-// parts whose partial results are added into C with reductions; C must be zero before, and
-// bias must be null. Overwrites C when splits == 1.
+// parts whose partial results are added into C with reductions (the first part adds the
+// bias); C must be zero before. Overwrites C when splits == 1.
 bool gemm_tc_supported(const GemmArgs& g);
 cudaError_t gemm_tc(const GemmArgs& g, int splits, int passes, int* status_word,
                     cudaStream_t stream);

@@ -189,13 +189,14 @@ struct TcParams {
 
 // One work item: a 128 x BN tile of C over one part of K.
 struct WorkItem {
-    int m0, n0, kb_begin, num_kb;
+    int m0, n0, kb_begin, num_kb, split;
 };
 template <int BN, int BK>
 __device__ __forceinline__ WorkItem work_item(const TcParams& p, int w) {
     const int split = w / p.total_tiles;
     const int tile = w - split * p.total_tiles;
     WorkItem it;
+    it.split = split;
     // tiles that share a row block of A are neighbours in the order, so A comes from HBM once
     it.m0 = (tile / p.n_tiles) * BM;
     it.n0 = (tile % p.n_tiles) * BN;
@@ -423,7 +424,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         v[e] = __uint_as_float(r[j + e]);
-                        if (p.bias != nullptr && n + e < p.N) v[e] += p.bias[n + e];
+                        // with K cut across work items the first part carries the bias
+                        if (p.bias != nullptr && wi.split == 0 && n + e < p.N) v[e] += p.bias[n + e];
                     }
                     if (vec_ok && n + 3 < p.N) {
                         if (p.reduce) red_add_f32x4(row + n, v[0], v[1], v[2], v[3]);
@@ -582,7 +584,6 @@ bool gemm_tc_supported(const GemmArgs& g) {
 cudaError_t gemm_tc(const GemmArgs& g, int splits, int passes, int* status_word,
                     cudaStream_t stream) {
     if (!gemm_tc_supported(g) || status_word == nullptr) return cudaErrorInvalidValue;
-    if (splits > 1 && g.bias != nullptr) return cudaErrorInvalidValue;
     if (passes != 1 && passes != 3) return cudaErrorInvalidValue;
     // widest tile that N fills to at least three quarters; measured on B200 at N = 512 and
     // N = 4608: 256-wide tiles are 10-40 % faster than 128-wide ones in both modes

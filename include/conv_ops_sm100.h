@@ -118,7 +118,7 @@ int dcn_sm100_use_tensor_cores(int on);
  *   C[m, n] = sum_k A[m * lda + k] * B[n * ldb + k] (+ bias[n]),  C row stride ldc.
  * Uses the tcgen05 kernel when dcn_sm100_use_tensor_cores is on and A, B are 16-byte aligned
  * with lda, ldb multiples of 4, else the fp32 FMA kernel. splits > 1 cuts K across CTAs
- * (tcgen05 kernel only; C is zero-filled first, bias must be NULL). No reference counterpart.
+ * (tcgen05 kernel only; C is zero-filled first). No reference counterpart.
  */
 int gemm_nt_sm100_f32(const float* A, long long lda, const float* B, long long ldb, float* C,
                       long long ldc, const float* bias, int M, int N, int K, int splits,

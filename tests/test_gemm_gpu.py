@@ -59,9 +59,11 @@ def test_k_split_across_ctas(splits):
     assert err <= 5e-5 * scale, (err, scale)
 
 
+@pytest.mark.parametrize("splits", [1, 3])
 @pytest.mark.parametrize("tensor_cores", [0, 1])
-def test_bias_is_added_per_column(tensor_cores):
-    err, scale = run(200, 136, 64, 0, 0, tensor_cores, bias=True)
+def test_bias_is_added_per_column(tensor_cores, splits):
+    """With K cut across work items the bias must be added exactly once."""
+    err, scale = run(200, 136, 640, 0, 0, tensor_cores, splits=splits, bias=True)
     assert err <= 5e-5 * scale, (err, scale)
 
 
