@@ -75,6 +75,8 @@ def test_fused_matches_float64_composition(name, w, dtype):
         # location gradients: skip samples that sit on a pixel boundary (one-sided derivative)
         from oracle import msda_oracle
         smooth = msda_oracle.kink_distance(inp["shapes"].numpy(), want[5].astype(np.float32)) > 1e-3
+        # the mask may only ever hide a small share of the samples
+        assert (~smooth).sum() <= max(4, 1e-2 * smooth.size), ((~smooth).sum(), smooth.size)
         parity.assert_close("grad_offsets", got[3], want[3], tol,
                             mask=np.broadcast_to(smooth[..., None], want[3].shape))
         # a reference point collects all heads and points of its level (a sum of H * P location

@@ -208,64 +208,52 @@ FULL_SIZE = [
     ("bevformer_tsa", torch.bfloat16),
     ("stress_d128", torch.bfloat16),
 ]
+# grad_sampling_loc samples that may be left out of the comparison because they sit on a
+# cell boundary (see parity.KINK_EPS): at most this fraction of all samples.
+MAX_KINK_FRACTION = 1e-3
 
 
 @pytest.mark.parametrize("name,dtype", FULL_SIZE, ids=[f"{n}-{str(d)[6:]}" for n, d in FULL_SIZE])
-def test_full_size_properties(name, dtype):
-    """At the full benchmark sizes the float64 oracle would take minutes, so parity is
-    checked (a) exactly against the oracle on a slice of the queries of every batch entry
-    (output rows and location/weight gradients of a query do not depend on other queries)
-    and (b) through size-independent identities on the whole result:
-      - linearity in value:   out(2 v) == 2 out(v)
-      - adjoint identity:     <grad_out, out(v)> == <grad_value, v>   (forward is linear in v,
-        backward wrt v is its transpose), evaluated in float64 on the device results
-      - sum(grad_attn * attn) == <grad_out, out>   (out is linear in attn as well)
-    """
+def test_full_size_whole_tensor_parity(name, dtype):
+    """Every element of output, grad_value, grad_sampling_loc and grad_attn_weight at the
+    full benchmark sizes (stress at its full batch of 8) against the float64 oracle, as the
+    reference's test compares whole tensors
+    (tests/torch/test_multi_scale_deformable_attn.py:93-101, 256-264). The device runs the
+    whole batch in one call; the oracle is run one batch entry at a time (entries are
+    independent) to bound host memory. Plus two size-independent identities on the full
+    result: linearity in value and <grad_out, out> == <grad_value, value>."""
     import drivingsdk_b200 as sdk
+    from oracle import msda_oracle
     w = workloads.WORKLOADS[name]
-    if name == "stress_d128":
-        w = w.with_batch(2)   # per-batch-entry work is what one GPU sees when sharded 8 ways
     inp = workloads.make_inputs(w, dtype)
     dev = parity.to_device(inp, dtype)
     out, gv, gl, ga = parity.run_python_api(dev)
     tol = parity.TOL[dtype]
+    rounded = (lambda a: a) if dtype == torch.float32 else \
+        (lambda a: torch.from_numpy(a).to(dtype).double().numpy())
+    masked = 0
+    for b in range(w.B):
+        one = {k: (inp[k][b:b + 1] if k not in ("shapes", "starts") else inp[k]) for k in inp}
+        want = [rounded(x) for x in parity.oracle_all(one)]
+        dist = msda_oracle.kink_distance(one["shapes"].numpy(), one["loc"].numpy())
+        smooth = dist > parity.KINK_EPS[dtype]
+        masked += int((~smooth).sum())
+        parity.assert_close(f"output[{b}]", out[b:b + 1], want[0], tol)
+        parity.assert_close(f"grad_value[{b}]", gv[b:b + 1], want[1], tol)
+        parity.assert_close(f"grad_attn_weight[{b}]", ga[b:b + 1], want[3], tol)
+        parity.assert_close(f"grad_sampling_loc[{b}]", gl[b:b + 1], want[2], tol,
+                            mask=np.broadcast_to(smooth[..., None], want[2].shape))
+    nsamples = w.B * w.Q * w.H * w.L * w.P
+    assert masked <= MAX_KINK_FRACTION * nsamples, (masked, nsamples)
 
-    # (a) exact parity on a query slice
-    qs = slice(0, w.Q, max(1, w.Q // 40))
-    sub = {"shapes": inp["shapes"], "starts": inp["starts"], "value": inp["value"],
-           "loc": inp["loc"][:, qs].contiguous(), "attn": inp["attn"][:, qs].contiguous(),
-           "grad_out": inp["grad_out"][:, qs].contiguous()}
-    want_out, _, want_gl, want_ga = parity.oracle_all(sub)
-    if dtype != torch.float32:
-        r = lambda a: torch.from_numpy(a).to(dtype).double().numpy()
-        want_out, want_gl, want_ga = r(want_out), r(want_gl), r(want_ga)
-    from oracle import msda_oracle
-    smooth = msda_oracle.kink_distance(sub["shapes"].numpy(), sub["loc"].numpy()) > parity.KINK_EPS[dtype]
-    parity.assert_close("output[slice]", out[:, qs], want_out, tol)
-    parity.assert_close("grad_attn[slice]", ga[:, qs], want_ga, tol)
-    parity.assert_close("grad_loc[slice]", gl[:, qs], want_gl, tol,
-                        mask=np.broadcast_to(smooth[..., None], want_gl.shape))
-
-    # (b) identities on the full tensors
     out2 = sdk.multi_scale_deformable_attn(dev["value"] * 2, dev["shapes"], dev["starts"],
                                            dev["loc"], dev["attn"])
     torch.testing.assert_close(out2.double(), 2 * out.double(), rtol=tol, atol=tol)
     lhs = (dev["grad_out"].double() * out.double()).sum().item()
     rhs = (gv.double() * dev["value"].double()).sum().item()
-    rhs_attn = (ga.double() * dev["attn"].double()).sum().item()
     scale = (dev["grad_out"].double().abs() * out.double().abs()).sum().item()
     rel = 2e-3 if dtype != torch.float32 else 1e-5
     assert abs(lhs - rhs) <= rel * scale, (lhs, rhs, scale)
-    assert abs(lhs - rhs_attn) <= rel * scale, (lhs, rhs_attn, scale)
-
-
-def test_grad_value_full_parity_on_one_camera():
-    """grad_value depends on every query, so it is checked against the oracle on a whole
-    (single batch entry) BEVFormer-shaped problem."""
-    w = workloads.WORKLOADS["bevformer_sca"].with_batch(1)
-    inp = workloads.make_inputs(w, torch.float32)
-    dev = parity.to_device(inp, torch.float32)
-    parity.compare_all(inp, parity.run_c_abi(dev, torch.float32), torch.float32)
 
 
 def test_repeat_runs_agree():
