@@ -95,6 +95,11 @@ Dims check_inputs(const at::Tensor& value, const at::Tensor& shapes, const at::T
                 "entry per level of attention_weights");
     TORCH_CHECK(shapes.device() == starts.device(),
                 "value_spatial_shapes and value_level_start_index must live on the same device");
+    TORCH_CHECK(!shapes.is_cuda() || shapes.device() == value.device(),
+                "value_spatial_shapes / value_level_start_index must be CPU tensors or live on "
+                "value's device");
+    TORCH_CHECK(loc.device() == value.device() && attn.device() == value.device(),
+                "sampling_locations and attention_weights must live on value's device");
     return d;
 }
 

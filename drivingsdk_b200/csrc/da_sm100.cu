@@ -407,13 +407,17 @@ int da_common(DaParams& p, const void* feat, const int32_t* shapes, const int32_
     p.cpg = C / G;
     p.ntasks = static_cast<long long>(B) * cams * p.nparts * A;
 
-    cudaPointerAttributes attr;
-    bool on_dev = false;
-    if (cudaPointerGetAttributes(&attr, shapes) == cudaSuccess) {
-        on_dev = attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
-    } else {
-        cudaGetLastError();
-    }
+    // both level arrays on the host or both on the device
+    auto on_device = [](const void* ptr) {
+        cudaPointerAttributes attr;
+        if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+    };
+    const bool on_dev = on_device(shapes);
+    if (on_dev != on_device(starts)) return MSDA_ERR_ALIGN;
     if (on_dev) {
         p.use_table = 0;
         p.shapes_dev = shapes;
@@ -430,10 +434,12 @@ int da_common(DaParams& p, const void* feat, const int32_t* shapes, const int32_
                 return MSDA_ERR_DIMS;
         }
     }
-    // vector path: the row is 2^k pieces of 16 bytes and a piece never straddles two groups
+    // vector path: the row is 2^k pieces of 16 bytes, a piece never straddles two groups, and
+    // a group's pieces sit in one pass over the lanes (at most 32 pieces = 128 channels per
+    // group: the backward keeps one dot product per (slot, group) and pass)
     const long long pieces = C / 4;
     *scalar = !(vec_ptrs && C % 4 == 0 && is_pow2(pieces) && pieces <= 64 && p.cpg % 4 == 0 &&
-                is_pow2(p.cpg / 4));
+                is_pow2(p.cpg / 4) && p.cpg <= 128);
     *lpr = 32;
     *nv = 8;
     if (!*scalar) {

@@ -24,6 +24,7 @@ std::atomic<int> g_tune_stage{1};
 std::atomic<int> g_tune_interleave{1};
 std::atomic<int> g_tune_cps_fwd{0};
 std::atomic<int> g_tune_cps_bwd{0};
+std::atomic<int> g_tune_spin{msda::kSpinLimit};
 std::atomic<long long> g_launches{0};
 thread_local int t_last_cuda_error = 0;
 thread_local cudaEvent_t t_prof[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -180,6 +181,7 @@ int fill_common(Params& p, const DeviceInfo* dev, const void* value, const int32
                item_attn_bytes % 16 == 0)
                   ? 1
                   : 0;
+    p.spin_limit = g_tune_spin.load();
     if (!aligned_to(value, e) || !aligned_to(loc, e) || !aligned_to(attn, e)) return MSDA_ERR_ALIGN;
     return MSDA_OK;
 }
@@ -438,6 +440,7 @@ int msda_sm100_tune(int knob, int value) {
         case MSDA_TUNE_CTAS_PER_SM: target = &g_tune_cps_fwd; break;
         case MSDA_TUNE_CTAS_PER_SM_BWD: target = &g_tune_cps_bwd; break;
         case MSDA_TUNE_INTERLEAVE: target = &g_tune_interleave; break;
+        case MSDA_TUNE_SPIN_LIMIT: target = &g_tune_spin; break;
         default: return MSDA_ERR_DIMS;
     }
     if (value < 0) return target->load();

@@ -29,7 +29,8 @@ constexpr int kThreadsPerCta = kWarpsPerCta * 32;
 constexpr int kChunk = 32;          // samples handled by one warp pass
 constexpr int kSlots = 4 * kChunk;  // (sample, corner) pairs per warp pass
 constexpr int kSlotPad = 64;         // readable (never used) records past the last slot
-constexpr int kSpinLimit = 1 << 18; // bound on mbarrier polling
+constexpr int kSpinLimit = 1 << 18; // default bound on mbarrier polling (Params::spin_limit)
+constexpr int kDrainLimit = 1 << 20; // bound on waiting for copies already issued after a time-out
 
 // Device status bits, sticky until read by msda_sm100_device_status().
 constexpr int kStatusStageTimeout = 1;  // a staged tile never arrived
@@ -94,6 +95,8 @@ struct Params {
     int use_table;
     int stage;          // 1: each warp bulk-copies its next item's locations/weights to shared
                         // memory while it works on the current one; 0: direct loads
+    int spin_limit;     // polls of a staging barrier before the warp gives up on it (0: every
+                        // wait times out at once, which is how the fall-back path is tested)
     long long ntasks;   // B * Q * H
     long long nitems;   // ceil(ntasks / tasks_per_item)
     int* status;        // device status word
@@ -284,11 +287,11 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
         "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
         : "memory");
 }
-// Polls until the phase with the given parity completes, or the spin limit is
-// reached. Returns false on timeout; the caller falls back to plain loads.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Polls until the phase with the given parity completes, or `limit` polls have been made.
+// Returns false on timeout; the caller falls back to plain loads.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int limit) {
     const uint32_t addr = smem_u32(bar);
-    for (int spin = 0; spin < kSpinLimit; ++spin) {
+    for (int spin = 0; spin < limit; ++spin) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"

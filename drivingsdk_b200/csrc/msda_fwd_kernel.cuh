@@ -67,18 +67,21 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
         const T* sattn = nullptr;
         if (st.ok) {
             const long long next = walk.item_at(p, walk.idx + walk.stride);
-            if (lane == 0 && walk.idx + walk.stride < walk.end && full(next)) {
-                st.issue(p, next, buf ^ 1);
-            }
+            const bool next_issued = walk.idx + walk.stride < walk.end && full(next);
+            if (lane == 0 && next_issued) st.issue(p, next, buf ^ 1);
             if (full(item)) {
                 const bool arrived =
-                    __all_sync(0xffffffffu, mbar_wait(st.bar + buf, (n >> 1) & 1) ? 1 : 0) != 0;
+                    __all_sync(0xffffffffu,
+                               mbar_wait(st.bar + buf, (n >> 1) & 1, p.spin_limit) ? 1 : 0) != 0;
                 if (arrived) {
                     sloc = st.loc(p, buf);
                     sattn = st.attn(p, buf);
                 } else {
+                    // give up staging for good, report it, let the copies in flight land,
+                    // and carry on with direct loads
                     st.ok = false;
                     if (lane == 0) atomicOr(p.status, kStatusStageTimeout);
+                    st.drain(buf, n, next_issued);
                 }
             }
         }

@@ -18,6 +18,7 @@
 #include <cuda_runtime.h>
 
 #include "../../include/msda_sm100.h"
+#include "msda_launch.h"
 
 namespace {
 
@@ -65,7 +66,10 @@ int msda_sm100_backward_static(const void* value, const int32_t* spatial_shapes,
                                void* grad_value, void* grad_sampling_loc, void* grad_attn_weight,
                                int B, int K, int H, int D, int L, int Q, int P, int dtype,
                                void* stream) {
-    // Size check first, in 64-bit arithmetic and without touching the device: the fp32
+    // An unknown dtype code is refused before anything else, so that it is reported as such
+    // whatever the sizes are.
+    if (dtype != MSDA_F32 && dtype != MSDA_F16 && dtype != MSDA_BF16) return MSDA_ERR_DTYPE;
+    // Size check next, in 64-bit arithmetic and without touching the device: the fp32
     // accumulation buffer of this problem must fit into the static array.
     if (B > 0 && K > 0 && H > 0 && D > 0 && dtype != MSDA_F32) {
         const unsigned long long need = 4ull * static_cast<unsigned long long>(B) *
@@ -77,7 +81,10 @@ int msda_sm100_backward_static(const void* value, const int32_t* spatial_shapes,
     void* scratch = nullptr;
     if (dtype != MSDA_F32) {  // fp32 problems accumulate in grad_value itself: no scratch
         const cudaError_t e = scratch_address(&scratch);
-        if (e != cudaSuccess) return MSDA_ERR_CUDA;
+        if (e != cudaSuccess) {
+            cudaGetLastError();                  // leave no sticky error behind
+            return msda::note_cuda_error(e);     // msda_sm100_last_cuda_error() reports it
+        }
     }
     // Everything else — validation, zero-filling the part of the scratch that is used,
     // the kernel, the conversion into grad_value — is the workspace entry point's job.

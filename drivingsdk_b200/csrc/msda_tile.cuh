@@ -146,6 +146,15 @@ struct WarpStage {
         bulk_g2s(dst, gl, 2 * ab, bar + b);
         bulk_g2s(dst + 2 * ab, ga, ab, bar + b);
     }
+    // After a time-out on buffer `b` (use number n of the barriers): the warp stops staging,
+    // but the copies it has already issued still target its buffers. Wait for them (bounded,
+    // with a far larger limit) so that none is in flight when the CTA exits and its shared
+    // memory is handed to another CTA. All lanes call it.
+    __device__ __forceinline__ void drain(int b, int n, bool next_issued) const {
+        mbar_wait(bar + b, (n >> 1) & 1, kDrainLimit);
+        if (next_issued) mbar_wait(bar + (b ^ 1), ((n + 1) >> 1) & 1, kDrainLimit);
+        __syncwarp();
+    }
 };
 
 template <typename T>

@@ -223,12 +223,17 @@ int msda_sm100_device_status(int clear);
  *                            whatever the order), walk the (batch, query, head) tasks with
  *                            the batch entries interleaved, so that concurrent reductions
  *                            spread over all entries' gradient maps (default); 0 = always
- *                            walk in memory order */
+ *                            walk in memory order
+ *   MSDA_TUNE_SPIN_LIMIT     polls of a staging barrier before a warp gives the staged tile
+ *                            up, sets status bit 0 and carries on with direct loads (default
+ *                            262144). 0 makes every wait run out at once: the way to exercise
+ *                            that path without any fault; results stay correct. */
 typedef enum msda_tune {
     MSDA_TUNE_STAGE = 0,
     MSDA_TUNE_CTAS_PER_SM = 1,
     MSDA_TUNE_CTAS_PER_SM_BWD = 2,
-    MSDA_TUNE_INTERLEAVE = 3
+    MSDA_TUNE_INTERLEAVE = 3,
+    MSDA_TUNE_SPIN_LIMIT = 4
 } msda_tune;
 int msda_sm100_tune(int knob, int value);
 

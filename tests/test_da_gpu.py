@@ -103,6 +103,16 @@ def test_sparse4d_shape():
     _check(c, _run_python_api(c))
 
 
+@pytest.mark.parametrize("C,G", [(256, 1), (256, 2), (128, 1), (64, 1), (40, 2)])
+def test_wide_channel_groups_through_c_abi(C, G):
+    """Few groups over many channels (up to 256 channels in one group), which only the C ABI
+    accepts (the Python wrapper wants a multiple of 8 groups): every group's dot product must
+    cover all of its channels."""
+    c = _random_case(zlib.crc32(str((C, G)).encode()), 2, C, 7, 5, G, [[(9, 14), (5, 7)]] * 2)
+    _check(c, _run_c_abi(c))
+    _check(c, _run_c_abi(c, host_tables=True))
+
+
 def test_half_precision_inputs_round_trip():
     c = _random_case(9, 2, 64, 8, 6, 8, [[(6, 9), (3, 5)]] * 2)
     for k in ("feat", "loc", "wts", "grad_out"):

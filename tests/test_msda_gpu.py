@@ -312,3 +312,28 @@ def test_mmcv_hook_end_to_end():
                 sys.modules.pop(k, None)
             else:
                 sys.modules[k] = v
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_staging_wait_that_runs_out_falls_back_to_direct_loads(dtype):
+    """The only device-side wait of the MSDA kernels is the bounded poll of a staging barrier.
+    With the poll limit set to 0 every wait runs out at once (nothing faults, nothing hangs):
+    the kernels must report it in the status word (bit 0), let the copies already issued land,
+    and still produce results within tolerance through their direct-load path."""
+    from drivingsdk_b200 import capi
+    lib = capi.load()
+    assert lib.msda_sm100_device_status(1) >= 0
+    w = workloads.WORKLOADS["toy"]
+    inp = workloads.make_inputs(w, dtype)
+    dev = parity.to_device(inp, dtype)
+    prev = lib.msda_sm100_tune(capi.TUNE_SPIN_LIMIT, 0)
+    try:
+        results = parity.run_c_abi(dev, dtype)
+        status = lib.msda_sm100_device_status(1)
+    finally:
+        lib.msda_sm100_tune(capi.TUNE_SPIN_LIMIT, prev)
+    assert status >= 0 and (status & 1) == 1, status
+    parity.compare_all(inp, results, dtype)
+    # with the limit restored the same call completes without the bit
+    parity.compare_all(inp, parity.run_c_abi(dev, dtype), dtype)
+    assert lib.msda_sm100_device_status(1) == 0

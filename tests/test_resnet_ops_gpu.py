@@ -32,14 +32,32 @@ def test_add_relu_matches_torch(shape, dtype):
     assert torch.equal(got, want)
 
 
-def test_add_relu_overwrites_x_and_handles_unaligned_views():
+def test_add_relu_overwrites_large_x_and_leaves_small_x_alone():
+    """The reference's observable contract (mx_driving/ops/npu_add_relu.py:22-25): x is
+    overwritten from 2,000,000 elements up, below that the result is a new tensor. Both on
+    views that start 4 bytes past a 16-byte boundary."""
     import mx_driving
-    base_x, base_y = _inputs((4099,), torch.float32, 2)
-    x, y = base_x[1:], base_y[1:]  # 4098 elements each, 4 bytes past a 16-byte boundary
+    base_x, base_y = _inputs((2000001,), torch.float32, 2)
+    x, y = base_x[1:], base_y[1:]
     want = F.relu(x + y)
     got = mx_driving.npu_add_relu(x, y)
     assert got.data_ptr() == x.data_ptr()
     assert torch.equal(x, want)
+
+    base_x, base_y = _inputs((4099,), torch.float32, 2)
+    x, y = base_x[1:], base_y[1:]
+    keep = x.clone()
+    got = mx_driving.npu_add_relu(x, y)
+    assert got.data_ptr() != x.data_ptr()
+    assert torch.equal(x, keep) and torch.equal(got, F.relu(keep + y))
+
+
+def test_add_relu_never_overwrites_non_contiguous_x():
+    import mx_driving
+    x, y = _inputs((1500, 1500), torch.float32, 4)
+    xt, keep = x.t(), x.t().clone()
+    got = mx_driving.npu_add_relu(xt, y)
+    assert torch.equal(xt, keep) and torch.equal(got, F.relu(keep + y))
 
 
 def test_add_relu_propagates_nan_like_torch():

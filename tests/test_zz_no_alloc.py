@@ -66,3 +66,14 @@ def test_static_scratch_refuses_oversized_problems():
                                         B, K, H, D, 4, 10, 8, capi.BF16, None)
     assert rc == -6
     assert b"workspace" in lib.msda_sm100_strerror(rc)
+
+
+def test_static_scratch_refuses_unknown_dtype_before_anything_else():
+    """An unknown dtype code is reported as such for small and for oversized problems alike."""
+    lib = capi.load()
+    one = 256
+    for dims in ((1, 100, 2, 32), (2, 30825, 8, 32)):
+        rc = lib.msda_sm100_backward_static(one, one, one, one, one, one, one, one, one,
+                                            *dims, 4, 10, 8, 7, None)
+        assert rc == -5, rc
+        assert b"dtype" in lib.msda_sm100_strerror(rc)
