@@ -10,8 +10,15 @@
 
 namespace msda {
 
-constexpr int kPartMax = 8;  // partial dot products kept per (sample, corner)
-constexpr int kPartBytes = ((kChunk * (4 * kPartMax + 1) * 4 + 15) / 16) * 16;
+// Partial dot products <value row, grad_out> kept per (sample, corner): 8 floats for 16-bit
+// tensors, 4 doubles for fp32 tensors (see sample_grad for why those are doubles).
+constexpr int kPartMax = 8;
+constexpr int kPartMaxF64 = 4;
+constexpr int kPartBytes = ((kChunk * (4 * kPartMaxF64 + 1) * 8 + 15) / 16) * 16;
+static_assert(kPartBytes >= kChunk * (4 * kPartMax + 1) * 4, "partials of either type must fit");
+// Type of the dot products: double for fp32 tensors, float for 16-bit tensors.
+template <typename T>
+using DotT = typename std::conditional<sizeof(T) == 4, double, float>::type;
 
 // Compile-time tuning, chosen by measurement on B200: three resident CTAs per SM (80
 // registers per thread) and four rows in flight per lane; the kernel is bound by the rate
@@ -23,6 +30,57 @@ constexpr int kPartBytes = ((kChunk * (4 * kPartMax + 1) * 4 + 15) / 16) * 16;
 #define MSDA_BWD_UNROLL 4
 #endif
 
+// Per-sample gradients from the partial dot products S_c = <value row of corner c, grad_out>
+// that phase 2 parked in shared memory (`part`: CPS * PART floats of this sample):
+//   grad_attn  = w1*S1 + w2*S2 + w3*S3 + w4*S4                (bilinear w, no attention)
+//   grad_loc_x = W * attn * (hh*(S2 - S1) + lh*(S4 - S3))
+//   grad_loc_y = H * attn * (hw*(S3 - S1) + lw*(S4 - S2))
+// (op_kernel/multi_scale_deformable_attn_grad.cpp:215-242), all zero for a dropped sample; a
+// corner that does not exist left zero partials behind. For fp32 tensors the sums, the
+// differences and the products run in double precision: the differences of the S_c cancel
+// and are then multiplied by W * attn (up to ~200), which turns the fp32 rounding of the
+// S_c themselves into errors beyond 1e-4 on wide levels (measured on 200-pixel-wide levels
+// with N(0,1) values: fp32 dot products miss rtol = atol = 1e-4 on a few samples per million,
+// fp32 partial sums added in double still on one). So for fp32 tensors the dot products are
+// accumulated in double from the first product on (phase 2) and stay double through here.
+// 16-bit tensors (tolerance 1e-2) keep fp32 arithmetic.
+__device__ __forceinline__ float dot_fma(float v, float g, float acc) { return fmaf(v, g, acc); }
+__device__ __forceinline__ double dot_fma(float v, double g, double acc) {
+    return fma(static_cast<double>(v), g, acc);
+}
+
+struct SampleGrad {
+    float attn, x, y;
+};
+template <typename T, int CPS, int PART>
+__device__ __forceinline__ SampleGrad sample_grad(const DotT<T>* part, const SampleGeom& geom) {
+    using Acc = DotT<T>;
+    Acc S[CPS];
+#pragma unroll
+    for (int c = 0; c < CPS; ++c) {
+        Acc acc = 0;
+#pragma unroll
+        for (int q = 0; q < PART; ++q) acc += part[c * PART + q];
+        S[c] = acc;
+    }
+    SampleGrad r{0.f, 0.f, 0.f};
+    if constexpr (CPS == 4) {
+        if (geom.valid) {
+            const Acc lw = geom.lw, lh = geom.lh;
+            const Acc hw = Acc(1) - lw, hh = Acc(1) - lh;
+            r.attn = static_cast<float>(hh * hw * S[0] + hh * lw * S[1] + lh * hw * S[2] +
+                                        lh * lw * S[3]);
+            r.x = static_cast<float>(static_cast<Acc>(geom.wf) * static_cast<Acc>(geom.a) *
+                                     (hh * (S[1] - S[0]) + lh * (S[3] - S[2])));
+            r.y = static_cast<float>(static_cast<Acc>(geom.hf) * static_cast<Acc>(geom.a) *
+                                     (hw * (S[2] - S[0]) + lw * (S[3] - S[1])));
+        }
+    } else {
+        r.attn = static_cast<float>(S[0]);
+    }
+    return r;
+}
+
 template <typename T, typename TG, int LPR, int NV, bool SCALAR, int MODE>
 __global__ void __launch_bounds__(kThreadsPerCta, (SCALAR || NV > 1) ? 2 : MSDA_BWD_MIN_CTAS)
 msda_bwd_kernel(const __grid_constant__ Params p) {
@@ -30,7 +88,9 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
     constexpr bool FUSED = MODE == kModeFused;
     constexpr int VEC = SCALAR ? 1 : Elem<T>::kVec;
     constexpr int RPI = 32 / LPR;
-    constexpr int PART = (LPR < kPartMax) ? LPR : kPartMax;  // partials per slot
+    using Dot = DotT<T>;
+    constexpr int PART_MAX = (sizeof(T) == 4) ? kPartMaxF64 : kPartMax;
+    constexpr int PART = (LPR < PART_MAX) ? LPR : PART_MAX;  // partials per slot
     constexpr int SSTRIDE = CPS * PART + 1;                    // per-sample stride (bank spread)
     // 16-bit rows of <= 128 bytes: an instruction already covers >= 4 rows, and the fp32
     // accumulation path carries a second copy of grad_out; two instructions in flight keep
@@ -54,7 +114,7 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
 
     unsigned char* wb = smem + static_cast<size_t>(warp) * p.warp_smem;
     uint2* s_slot = reinterpret_cast<uint2*>(wb);
-    float* s_part = reinterpret_cast<float*>(wb + kSlotBytes);
+    Dot* s_part = reinterpret_cast<Dot*>(wb + kSlotBytes);
     init_unused_slots<CPS>(s_slot, lane);
     WarpStage<T> st = warp_stage_init<T>(p, wb + kSlotBytes + kPartBytes, lane);
 
@@ -140,6 +200,12 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                         go[k][0] = (c < D) ? Elem<T>::to_f(gout[obase + c]) : 0.f;
                     }
                 }
+                // the same piece in the type of the dot products (converted once per task)
+                Dot god[NV][VEC];
+#pragma unroll
+                for (int k = 0; k < NV; ++k)
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) god[k][e] = static_cast<Dot>(go[k][e]);
                 float gred[2][4];
                 if constexpr (SPLIT_RED) {
 #pragma unroll
@@ -163,12 +229,12 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                     constexpr bool GUARDED = decltype(guarded_tag)::value;
                     const uint2* sp = s_slot + base + g;
                     uint2 rec[U];
-                    float part[U];
+                    Dot part[U];
 #pragma unroll
                     for (int u = 0; u < U; ++u) {
                         rec[u] = sp[u * RPI];
                         if (GUARDED && base + u * RPI + g >= slot_end) rec[u].x = kNoRow;
-                        part[u] = 0.f;
+                        part[u] = 0;
                     }
                     if constexpr (!SCALAR) {
                         // A missing corner loads row 0 instead of branching around the load;
@@ -212,7 +278,7 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                                     unpack16<T>(raw[u][k], f);
 #pragma unroll
                                     for (int e = 0; e < VEC; ++e)
-                                        part[u] = fmaf(f[e], go[k][e], part[u]);
+                                        part[u] = dot_fma(f[e], god[k][e], part[u]);
                                 }
                             }
                         }
@@ -227,7 +293,7 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                                     const size_t idx = static_cast<size_t>(rec[u].x) + c;
                                     const float v = Elem<T>::to_f(__ldg(value + idx));
                                     red_add_scalar(gval + idx, w * go[k][0]);
-                                    part[u] = fmaf(v, go[k][0], part[u]);
+                                    part[u] = dot_fma(v, god[k][0], part[u]);
                                 }
                             }
                         }
@@ -258,32 +324,14 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
             // ---- phase 3: lane = sample -----------------------------------------
             if constexpr (!FUSED) {
                 if (active) {
-                    float S[CPS];
-#pragma unroll
-                    for (int c = 0; c < CPS; ++c) {
-                        float acc = 0.f;
-#pragma unroll
-                        for (int q = 0; q < PART; ++q)
-                            acc += s_part[lane * SSTRIDE + c * PART + q];
-                        S[c] = acc;
-                    }
+                    const SampleGrad sg = sample_grad<T, CPS, PART>(s_part + lane * SSTRIDE, geom);
                     if constexpr (CPS == 4) {
-                        float g_attn = 0.f, g_x = 0.f, g_y = 0.f;
-                        if (geom.valid) {
-                            // a corner that does not exist left a zero partial sum behind
-                            const float lw = geom.lw, lh = geom.lh;
-                            const float hw = 1.f - lw, hh = 1.f - lh;
-                            g_attn = hh * hw * S[0] + hh * lw * S[1] + lh * hw * S[2] +
-                                     lh * lw * S[3];
-                            g_x = geom.wf * geom.a * (hh * (S[1] - S[0]) + lh * (S[3] - S[2]));
-                            g_y = geom.hf * geom.a * (hw * (S[2] - S[0]) + lw * (S[3] - S[1]));
-                        }
-                        store_pair(static_cast<T*>(p.grad_loc) + 2 * gi, g_x, g_y);
-                        static_cast<T*>(p.grad_attn)[gi] = Elem<T>::from_f(g_attn);
+                        store_pair(static_cast<T*>(p.grad_loc) + 2 * gi, sg.x, sg.y);
+                        static_cast<T*>(p.grad_attn)[gi] = Elem<T>::from_f(sg.attn);
                     } else {
                         // nearest-pixel operator: d out / d attention = <value row, grad_out>;
                         // the integer locations have no gradient
-                        static_cast<T*>(p.grad_attn)[gi] = Elem<T>::from_f(S[0]);
+                        static_cast<T*>(p.grad_attn)[gi] = Elem<T>::from_f(sg.attn);
                     }
                 }
             } else {
@@ -291,20 +339,10 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                 //   location = reference point + offset / (W, H)   and   weight = softmax(logits).
                 float g_attn = 0.f, g_x = 0.f, g_y = 0.f;
                 if (active && geom.valid) {
-                    float S[4];
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        float acc = 0.f;
-#pragma unroll
-                        for (int q = 0; q < PART; ++q)
-                            acc += s_part[lane * SSTRIDE + c * PART + q];
-                        S[c] = acc;
-                    }
-                    const float lw = geom.lw, lh = geom.lh;
-                    const float hw = 1.f - lw, hh = 1.f - lh;
-                    g_attn = hh * hw * S[0] + hh * lw * S[1] + lh * hw * S[2] + lh * lw * S[3];
-                    g_x = geom.wf * geom.a * (hh * (S[1] - S[0]) + lh * (S[3] - S[2]));
-                    g_y = geom.hf * geom.a * (hw * (S[2] - S[0]) + lw * (S[3] - S[1]));
+                    const SampleGrad sg = sample_grad<T, 4, PART>(s_part + lane * SSTRIDE, geom);
+                    g_attn = sg.attn;
+                    g_x = sg.x;
+                    g_y = sg.y;
                 }
                 int tl, s;
                 lane_sample_index(p, chunk, lane, tl, s);

@@ -313,6 +313,7 @@ struct SampleGeom {
     float a;       // attention weight (0 when the sample is dropped)
     float wf, hf;  // level width / height as floats
     float prob;    // fused variant: the sample's softmax probability, kept for dropped samples too
+    int x0, y0;    // top-left pixel of the sample's cell (0 for a dropped sample)
     bool valid;
 };
 
@@ -368,6 +369,8 @@ __device__ __forceinline__ void sample_setup(float lx, float ly, float a, int Wl
     g.prob = a;
     g.wf = wf;
     g.hf = hf;
+    g.x0 = x0;
+    g.y0 = y0;
     g.valid = valid;
 }
 
@@ -391,6 +394,8 @@ __device__ __forceinline__ void sample_setup_nearest(float lx, float ly, float a
     g.prob = a;
     g.wf = static_cast<float>(Wl);
     g.hf = static_cast<float>(Hl);
+    g.x0 = x;
+    g.y0 = y;
     g.valid = true;
 }
 

@@ -227,13 +227,28 @@ int msda_sm100_device_status(int clear);
  *   MSDA_TUNE_SPIN_LIMIT     polls of a staging barrier before a warp gives the staged tile
  *                            up, sets status bit 0 and carries on with direct loads (default
  *                            262144). 0 makes every wait run out at once: the way to exercise
- *                            that path without any fault; results stay correct. */
+ *                            that path without any fault; results stay correct.
+ *   MSDA_TUNE_RESIDENT       1 = the backward keeps the grad_value accumulators of each head's
+ *                            small pyramid levels in shared memory and adds them to global
+ *                            memory once per (batch entry, head, query chunk) (default, rows of
+ *                            16 * 2^k <= 512 bytes); 0 = every row is reduced in L2
+ *   MSDA_TUNE_RESIDENT_BYTES upper limit on the shared memory used for those accumulators
+ *                            (default 2147483647 = all a CTA can have; 0 = none). Small values
+ *                            make small problems exercise the edges of the resident windows.
+ *   MSDA_TUNE_PRECISE_AMP    fp32 tensors: samples with max(W, H) * |attention| >= this value
+ *                            accumulate their dot products <value row, grad_out> in double
+ *                            from the first product on, the others form the per-lane sums in
+ *                            fp32 (default 8; 0 = all samples in double). The location
+ *                            gradient multiplies those dot products by W * attention. */
 typedef enum msda_tune {
     MSDA_TUNE_STAGE = 0,
     MSDA_TUNE_CTAS_PER_SM = 1,
     MSDA_TUNE_CTAS_PER_SM_BWD = 2,
     MSDA_TUNE_INTERLEAVE = 3,
-    MSDA_TUNE_SPIN_LIMIT = 4
+    MSDA_TUNE_SPIN_LIMIT = 4,
+    MSDA_TUNE_RESIDENT = 5,
+    MSDA_TUNE_RESIDENT_BYTES = 6,
+    MSDA_TUNE_PRECISE_AMP = 7
 } msda_tune;
 int msda_sm100_tune(int knob, int value);
 

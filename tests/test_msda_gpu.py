@@ -337,3 +337,71 @@ def test_staging_wait_that_runs_out_falls_back_to_direct_loads(dtype):
     # with the limit restored the same call completes without the bit
     parity.compare_all(inp, parity.run_c_abi(dev, dtype), dtype)
     assert lib.msda_sm100_device_status(1) == 0
+
+
+@pytest.mark.parametrize("cap", [0, 3000, 20000, 70000])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_resident_windows_of_every_size(cap, dtype):
+    """The backward keeps the accumulators of the small levels in shared memory. Limiting
+    that memory moves the edge of the resident windows through the toy pyramid (nothing
+    resident; the 4x4 level; 4x4 + 8x8 + four pixel rows of 16x16; all but part of 32x32), so
+    samples whose corners straddle a window edge occur; results must not depend on it."""
+    from drivingsdk_b200 import capi
+    lib = capi.load()
+    w = workloads.WORKLOADS["toy"]
+    inp = workloads.make_inputs(w, dtype)
+    dev = parity.to_device(inp, dtype)
+    prev = lib.msda_sm100_tune(capi.TUNE_RESIDENT_BYTES, cap)
+    try:
+        parity.compare_all(inp, parity.run_c_abi(dev, dtype), dtype)
+        parity.compare_all(inp, parity.run_c_abi(dev, dtype, workspace=False), dtype) \
+            if dtype == torch.float32 else None
+    finally:
+        lib.msda_sm100_tune(capi.TUNE_RESIDENT_BYTES, prev)
+    assert lib.msda_sm100_device_status(1) == 0
+
+
+@pytest.mark.parametrize("resident", [0, 1])
+def test_resident_and_l2_backward_agree(resident):
+    """Both routings of the scatter (shared-memory accumulators / reductions in L2 only)
+    against the oracle on a Deformable-DETR-shaped slice."""
+    from drivingsdk_b200 import capi
+    lib = capi.load()
+    w = workloads.WORKLOADS["deformable_detr"].with_batch(1).with_queries(3000)
+    inp = workloads.make_inputs(w, torch.float32)
+    dev = parity.to_device(inp, torch.float32)
+    prev = lib.msda_sm100_tune(capi.TUNE_RESIDENT, resident)
+    try:
+        parity.compare_all(inp, parity.run_c_abi(dev, torch.float32), torch.float32)
+    finally:
+        lib.msda_sm100_tune(capi.TUNE_RESIDENT, prev)
+
+
+def test_bad_level_table_on_the_device_is_reported_not_followed():
+    """Level tables passed as device memory cannot be checked by the host without a
+    synchronisation; the backward kernel checks them itself and, when a level would reach
+    past the K rows of value, sets status bit 2 (value 4) and returns without reading or
+    adding anything out of bounds."""
+    from drivingsdk_b200 import capi
+    lib = capi.load()
+    lib.msda_sm100_device_status(1)
+    w = workloads.WORKLOADS["toy"].with_queries(64)
+    inp = workloads.make_inputs(w, torch.float32)
+    dev = parity.to_device(inp, torch.float32)
+    dev["starts"] = dev["starts"].clone()
+    dev["starts"][-1] += 100            # last level now ends 100 rows past K
+    B, K, H, D = dev["value"].shape
+    _, Q, _, L, P, _ = dev["loc"].shape
+    gv = torch.full_like(dev["value"], 7.0)
+    gl, ga = torch.empty_like(dev["loc"]), torch.empty_like(dev["attn"])
+    shapes = dev["shapes"].to(torch.int32).contiguous()
+    starts = dev["starts"].to(torch.int32).contiguous()
+    rc = lib.msda_sm100_backward(dev["value"].data_ptr(), shapes.data_ptr(), starts.data_ptr(),
+                                 dev["loc"].data_ptr(), dev["attn"].data_ptr(),
+                                 dev["grad_out"].data_ptr(), gv.data_ptr(), gl.data_ptr(),
+                                 ga.data_ptr(), B, K, H, D, L, Q, P, capi.F32,
+                                 torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    status = lib.msda_sm100_device_status(1)
+    assert status >= 0 and (status & 4) == 4, status
+    assert torch.count_nonzero(gv).item() == 0     # zero-filled, then left alone
