@@ -1,12 +1,11 @@
 // Shared pieces of the "resident level" MSDA kernels for sm_100a.
 //
-// Work decomposition. A unit is one (batch entry, head, chunk of consecutive queries); a
-// persistent CTA (one per SM) takes units blockIdx.x, blockIdx.x + gridDim.x, ... Units are
-// numbered batch-major, then chunk, then head, so the CTAs in flight work on the same one or
-// two batch entries (their large levels stay in L2) and the eight heads of a query chunk run
-// side by side (their locations, weights and outputs are neighbours in memory). Inside a
-// unit every task has the same (batch entry, head), which is what lets the CTA keep that
-// head's small pyramid levels in its own shared memory:
+// Work decomposition. One persistent CTA per SM. Batch entries are worked one after the
+// other by all CTAs together (so that one entry's value and grad_value rows are what L2 has
+// to hold); within an entry its tasks, in (head, query) order, are cut into equal contiguous
+// ranges, one per CTA. A unit is the part of a CTA's range that lies in one head: every task
+// of a unit has the same (batch entry, head), which is what lets the CTA keep that head's
+// small pyramid levels in its own shared memory:
 //   backward: fp32 accumulators of grad_value for the resident levels; the scatter into them
 //             is a 16-byte compare-and-swap loop in shared memory instead of a vector
 //             reduction in L2 (L2 retires ~50 G 128-byte row reductions per second on B200,
@@ -43,9 +42,6 @@ struct ResLevel {
 
 struct ResParams {
     Params p;
-    uint32_t chunks;         // query chunks per (batch entry, head)
-    uint32_t unit_q;         // queries per chunk (a multiple of tasks_per_item)
-    uint32_t nunits;         // B * H * chunks
     uint32_t lv_off;         // shared-memory offsets: level table,
     uint32_t warp_off;       //   first warp's private area,
     uint32_t warp_bytes;     //   its size,
@@ -55,44 +51,6 @@ struct ResParams {
     float precise_amp;       // samples with max(W, H) * |attention| >= this take the
                              // double-precision dot products (fp32 tensors only)
 };
-
-// How one launch splits B * H * Q tasks into units: `chunks` query ranges per (batch entry,
-// head), sized so that the number of units fills whole waves of `sms` CTAs and about two
-// batch entries are in flight at a time.
-struct UnitPlan {
-    uint32_t chunks, unit_q, nunits;
-    int grid;
-};
-inline UnitPlan plan_units(int B, int H, int Q, int tasks_per_item, int sms, int warps) {
-    const long long pairs = static_cast<long long>(B) * H;
-    const long long items_per_pair = (Q + tasks_per_item - 1) / tasks_per_item;
-    long long cmin = (sms + 2 * H - 1) / (2 * H);
-    // a unit should give every warp a few items
-    long long cmax = items_per_pair / (2 * warps);
-    if (cmax < 1) cmax = 1;
-    long long lo = cmin > 2 ? cmin - 2 : 1, hi = 2 * cmin + 2;
-    if (hi > cmax) hi = cmax;
-    if (lo > hi) lo = hi;
-    double best_eff = -1.0;
-    long long best_c = lo;
-    for (long long c = lo; c <= hi; ++c) {
-        const long long units = pairs * c;
-        const long long waves = (units + sms - 1) / sms;
-        const double eff = static_cast<double>(units) / (static_cast<double>(waves) * sms);
-        if (eff > best_eff + 0.005) {
-            best_eff = eff;
-            best_c = c;
-        }
-    }
-    UnitPlan up;
-    long long uq = (Q + best_c - 1) / best_c;
-    uq = (uq + tasks_per_item - 1) / tasks_per_item * tasks_per_item;
-    up.unit_q = static_cast<uint32_t>(uq);
-    up.chunks = static_cast<uint32_t>((Q + uq - 1) / uq);
-    up.nunits = static_cast<uint32_t>(pairs * up.chunks);
-    up.grid = static_cast<int>(up.nunits < static_cast<uint32_t>(sms) ? up.nunits : sms);
-    return up;
-}
 
 // ---------------------------------------------------------------------------
 // device side
@@ -185,6 +143,33 @@ __device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y),
                  "r"(v.z), "r"(v.w)
                  : "memory");
+}
+
+// One attempt of acc[0..3] += (a, b, c, d): `old` is what the caller read there before.
+// Returns true when the sum went in; `old` is then unchanged, otherwise it holds what the
+// accumulator holds now. Callers issue the reads of several rows, then these attempts, then
+// deal with the (rare) failures through smem_add_f32x4.
+__device__ __forceinline__ bool smem_cas_add_f32x4(uint32_t addr, uint4& old, float a, float b,
+                                                   float c, float d) {
+    const uint32_t n0 = __float_as_uint(__uint_as_float(old.x) + a);
+    const uint32_t n1 = __float_as_uint(__uint_as_float(old.y) + b);
+    const uint32_t n2 = __float_as_uint(__uint_as_float(old.z) + c);
+    const uint32_t n3 = __float_as_uint(__uint_as_float(old.w) + d);
+    const uint64_t clo = (static_cast<uint64_t>(old.y) << 32) | old.x;
+    const uint64_t chi = (static_cast<uint64_t>(old.w) << 32) | old.z;
+    const uint64_t nlo = (static_cast<uint64_t>(n1) << 32) | n0;
+    const uint64_t nhi = (static_cast<uint64_t>(n3) << 32) | n2;
+    uint64_t olo, ohi;
+    asm volatile(
+        "{\n\t.reg .b128 cc, nn, oo;\n\t"
+        "mov.b128 cc, {%2, %3};\n\t"
+        "mov.b128 nn, {%4, %5};\n\t"
+        "atom.relaxed.cta.shared::cta.cas.b128 oo, [%6], cc, nn;\n\t"
+        "mov.b128 {%0, %1}, oo;\n\t}"
+        : "=l"(olo), "=l"(ohi)
+        : "l"(clo), "l"(chi), "l"(nlo), "l"(nhi), "r"(addr)
+        : "memory");
+    return olo == clo && ohi == chi;
 }
 
 // acc[0..3] += (a, b, c, d) on four consecutive floats of shared memory, atomically with

@@ -25,17 +25,67 @@
 namespace msda {
 
 #ifndef MSDA_RES_BWD_WARPS
-#define MSDA_RES_BWD_WARPS 12
+#define MSDA_RES_BWD_WARPS 16
 #endif
 constexpr int kResBwdWarps = MSDA_RES_BWD_WARPS;
 
 // shared memory of one warp: records (8 B per slot), accumulator addresses (4 B per slot),
-// partial dot products, staging barriers, two staging buffers
-constexpr uint32_t kResRecBytes = kSlots * 8;
-constexpr uint32_t kResSaBytes = kSlots * 4;
-__host__ __device__ inline uint32_t res_bwd_warp_bytes(int samples_per_item, size_t e) {
-    return kResRecBytes + kResSaBytes + kPartBytes + 16 +
-           2 * stage_bytes_per_buffer(samples_per_item, e);
+// dot products (one per slot, 8 B), staging barriers, two staging buffers; the arrays have
+// room for the slots a last trip may touch beyond the 128 of a pass
+constexpr uint32_t kResSlotRoom = kSlots + kSlotPad;
+constexpr uint32_t kResRecBytes = kResSlotRoom * 8;
+constexpr uint32_t kResSaBytes = kResSlotRoom * 4;
+constexpr uint32_t kResDotBytes = kSlots * 8;
+// One staging buffer: locations and weights of the item's tasks (when they are staged), then
+// the tasks' grad_output rows.
+__host__ __device__ inline uint32_t res_bwd_la_bytes(int stage_la, int samples_per_item, size_t e) {
+    return stage_la ? stage_bytes_per_buffer(samples_per_item, e) : 0u;
+}
+__host__ __device__ inline uint32_t res_bwd_stage_bytes(int stage_la, int samples_per_item,
+                                                        int tasks_per_item, int D, size_t e) {
+    return res_bwd_la_bytes(stage_la, samples_per_item, e) +
+           static_cast<uint32_t>(tasks_per_item * D * e);
+}
+__host__ __device__ inline uint32_t res_bwd_warp_bytes(int stage_la, int samples_per_item,
+                                                       int tasks_per_item, int D, size_t e) {
+    return kResRecBytes + kResSaBytes + kResDotBytes + 16 +
+           2 * res_bwd_stage_bytes(stage_la, samples_per_item, tasks_per_item, D, e);
+}
+
+// Sums GS partial dot products (one per row instruction of a group, this lane's piece of each
+// row) over the LPR lanes of a row and parks the result of slot s in dot[s]. With four values
+// and rows of at least four lanes the sums are formed by a transposing reduction: every
+// exchange halves the number of values a lane carries, so four sums cost four exchanges
+// instead of 4 * log2(LPR).
+template <int LPR, int RPI, int GS, typename V, typename DotType>
+__device__ __forceinline__ void park_dots(V (&v)[GS], DotType* dot, int slot0, int g, int j,
+                                          int slot_end) {
+    if constexpr (GS == 4) {
+        static_assert(LPR >= 4, "transposing reduction needs four lanes per row");
+        const bool hi_a = (j & (LPR / 2)) != 0;
+        const bool hi_b = (j & (LPR / 4)) != 0;
+        V k0 = hi_a ? v[2] : v[0], k1 = hi_a ? v[3] : v[1];
+        const V s0 = hi_a ? v[0] : v[2], s1 = hi_a ? v[1] : v[3];
+        k0 += __shfl_xor_sync(0xffffffffu, s0, LPR / 2);
+        k1 += __shfl_xor_sync(0xffffffffu, s1, LPR / 2);
+        V k = hi_b ? k1 : k0;
+        const V s = hi_b ? k0 : k1;
+        k += __shfl_xor_sync(0xffffffffu, s, LPR / 4);
+#pragma unroll
+        for (int off = LPR / 8; off >= 1; off >>= 1) k += __shfl_xor_sync(0xffffffffu, k, off);
+        const int u = (hi_a ? 2 : 0) + (hi_b ? 1 : 0);
+        const int slot = slot0 + u * RPI + g;
+        if ((j & (LPR / 4 - 1)) == 0 && slot < slot_end) dot[slot] = static_cast<DotType>(k);
+    } else {
+#pragma unroll
+        for (int u = 0; u < GS; ++u) {
+            V k = v[u];
+#pragma unroll
+            for (int off = LPR / 2; off >= 1; off >>= 1) k += __shfl_xor_sync(0xffffffffu, k, off);
+            const int slot = slot0 + u * RPI + g;
+            if (j == 0 && slot < slot_end) dot[slot] = static_cast<DotType>(k);
+        }
+    }
 }
 
 template <typename T, typename TG, int LPR>
@@ -46,11 +96,8 @@ msda_bwd_res_kernel(const __grid_constant__ ResParams rp) {
     constexpr int RPI = 32 / LPR;
     using Dot = DotT<T>;
     constexpr bool F32 = sizeof(T) == 4;
-    constexpr int PART_MAX = F32 ? kPartMaxF64 : kPartMax;
-    constexpr int PART = (LPR < PART_MAX) ? LPR : PART_MAX;
-    constexpr int SSTRIDE = 4 * PART + 1;
-    constexpr int UNROLL = (RPI >= 16) ? 2 : 4;
-    constexpr int STEP = RPI * UNROLL;
+    constexpr int UBIG = (RPI >= 16) ? 2 : 8;     // row instructions per trip
+    constexpr int USMALL = (RPI >= 16) ? 2 : 4;   //   ... for what is left of a task
     constexpr bool SPLIT_RED = sizeof(T) == 2 && sizeof(TG) == 4;
     constexpr int NW = kResBwdWarps;
 
@@ -65,7 +112,7 @@ msda_bwd_res_kernel(const __grid_constant__ ResParams rp) {
     unsigned char* wb = smem + rp.warp_off + static_cast<size_t>(warp) * rp.warp_bytes;
     uint2* s_rec = reinterpret_cast<uint2*>(wb);
     uint32_t* s_sa = reinterpret_cast<uint32_t*>(wb + kResRecBytes);
-    Dot* s_part = reinterpret_cast<Dot*>(wb + kResRecBytes + kResSaBytes);
+    Dot* s_dot = reinterpret_cast<Dot*>(wb + kResRecBytes + kResSaBytes);   // one per slot
     const uint32_t map_saddr = smem_u32(smem + rp.map_off);
 
     if (!res_plan_levels(rp, s_lv, s_ctl)) return;
@@ -76,9 +123,24 @@ msda_bwd_res_kernel(const __grid_constant__ ResParams rp) {
     for (uint32_t i = threadIdx.x * 16u; i < rp.map_bytes; i += NW * 32 * 16u)
         sts128(map_saddr + i, make_uint4(0u, 0u, 0u, 0u));
 
-    WarpStage<T> st =
-        warp_stage_init<T>(p, wb + kResRecBytes + kResSaBytes + kPartBytes, lane);
+    // Staging (bulk copies into one of two per-warp buffers, one item ahead): the item's
+    // locations and weights when p.stage is set, and always its grad_output rows.
+    WarpStage<T> st;
+    st.bar = reinterpret_cast<uint64_t*>(wb + kResRecBytes + kResSaBytes + kResDotBytes);
+    st.ok = true;
+    if (lane == 0) {
+        mbar_init(st.bar, 1);
+        mbar_init(st.bar + 1, 1);
+        mbar_fence_init();
+    }
+    __syncwarp();
     int stage_uses = 0;   // how many staged items this warp has consumed (barrier parity)
+    const uint32_t la_bytes = res_bwd_la_bytes(p.stage, p.tasks_per_item * p.LP, sizeof(T));
+    const uint32_t buf_bytes =
+        res_bwd_stage_bytes(p.stage, p.tasks_per_item * p.LP, p.tasks_per_item, p.D, sizeof(T));
+    auto stage_buffer = [&](int bi) {
+        return reinterpret_cast<unsigned char*>(st.bar) + 16 + bi * buf_bytes;
+    };
 
     const unsigned char* vlane = static_cast<const unsigned char*>(p.value) + j * 16;
     const T* __restrict__ gout = static_cast<const T*>(p.grad_out);
@@ -88,34 +150,45 @@ msda_bwd_res_kernel(const __grid_constant__ ResParams rp) {
     const int LP = p.LP;
     const int D = p.D;
     const int nchunks = (TPC == 1) ? (LP + kChunk - 1) / kChunk : 1;
-    const uint32_t units_per_b = rp.chunks * static_cast<uint32_t>(p.H);
+    // Units: per batch entry, the H * ceil(Q / TPC) items in (head, query) order are cut into
+    // gridDim.x equal ranges, one per CTA; a range that crosses a head boundary is worked as
+    // two units. All CTAs are on the same batch entry at (about) the same time, so that
+    // entry's value rows and grad_value rows - twice the pyramid - are what L2 has to hold.
+    const long long items_per_head = (p.Q + TPC - 1) / TPC;
+    const long long items_per_b = items_per_head * p.H;
 
     __syncthreads();
 
-    for (uint32_t unit = blockIdx.x; unit < rp.nunits; unit += gridDim.x) {
-        const uint32_t b = unit / units_per_b;
-        const uint32_t r = unit - b * units_per_b;
-        const uint32_t chunk_q = r / static_cast<uint32_t>(p.H);
-        const uint32_t h = r - chunk_q * static_cast<uint32_t>(p.H);
-        const int q0 = static_cast<int>(chunk_q * rp.unit_q);
-        const int q1 = min(p.Q, q0 + static_cast<int>(rp.unit_q));
-        const int nitems = (q1 - q0 + TPC - 1) / TPC;
+    for (uint32_t b = 0; b < static_cast<uint32_t>(p.B); ++b)
+    for (long long lo = items_per_b * blockIdx.x / gridDim.x,
+                   hi = items_per_b * (blockIdx.x + 1) / gridDim.x; lo < hi;) {
+        const uint32_t h = static_cast<uint32_t>(lo / items_per_head);
+        const long long ia = lo - static_cast<long long>(h) * items_per_head;
+        const long long ib = min(items_per_head, ia + (hi - lo));
+        lo += ib - ia;
+        const int q0 = static_cast<int>(ia) * TPC;
+        const int q1 = min(p.Q, static_cast<int>(ib) * TPC);
+        const int nitems = static_cast<int>(ib - ia);
         // task number of query q of this unit: (b * Q + q) * H + h
         const long long task0 = (static_cast<long long>(b) * p.Q) * p.H + h;
 
-        // issues the bulk copies of one item's locations and weights (lane 0)
+        // issues the bulk copies of one item (lane 0)
         auto issue = [&](int item, int buf) {
             const int qa = q0 + item * TPC;
             const int nt = min(TPC, q1 - qa);
             const uint32_t ab = static_cast<uint32_t>(LP * sizeof(T));   // weights of one task
-            unsigned char* dst = st.buffer(p, buf);
-            mbar_expect_tx(st.bar + buf, 3u * ab * nt);
+            const uint32_t gb = static_cast<uint32_t>(D * sizeof(T));    // one grad_output row
+            unsigned char* dst = stage_buffer(buf);
+            mbar_expect_tx(st.bar + buf, (p.stage ? 3u * ab : 0u) * nt + gb * nt);
             for (int tl = 0; tl < nt; ++tl) {
                 const long long t = task0 + static_cast<long long>(qa + tl) * p.H;
-                bulk_g2s(dst + 2u * ab * tl, static_cast<const T*>(p.loc) + t * LP * 2, 2u * ab,
-                         st.bar + buf);
-                bulk_g2s(dst + 2u * ab * TPC + ab * tl, static_cast<const T*>(p.attn) + t * LP,
-                         ab, st.bar + buf);
+                if (p.stage) {
+                    bulk_g2s(dst + 2u * ab * tl, static_cast<const T*>(p.loc) + t * LP * 2,
+                             2u * ab, st.bar + buf);
+                    bulk_g2s(dst + 2u * ab * TPC + ab * tl,
+                             static_cast<const T*>(p.attn) + t * LP, ab, st.bar + buf);
+                }
+                bulk_g2s(dst + la_bytes + gb * tl, gout + t * D, gb, st.bar + buf);
             }
         };
 
@@ -126,6 +199,7 @@ msda_bwd_res_kernel(const __grid_constant__ ResParams rp) {
             const int buf = stage_uses & 1;
             const T* sloc = nullptr;
             const T* sattn = nullptr;
+            const T* sgo = nullptr;
             if (st.ok) {
                 const bool next_issued = item + NW < nitems;
                 if (lane == 0 && next_issued) issue(item + NW, buf ^ 1);
@@ -133,9 +207,12 @@ msda_bwd_res_kernel(const __grid_constant__ ResParams rp) {
                     __all_sync(0xffffffffu, mbar_wait(st.bar + buf, (stage_uses >> 1) & 1,
                                                       p.spin_limit) ? 1 : 0) != 0;
                 if (arrived) {
-                    sloc = reinterpret_cast<const T*>(st.buffer(p, buf));
-                    sattn = reinterpret_cast<const T*>(st.buffer(p, buf) +
-                                                       2u * TPC * LP * sizeof(T));
+                    if (p.stage) {
+                        sloc = reinterpret_cast<const T*>(stage_buffer(buf));
+                        sattn = reinterpret_cast<const T*>(stage_buffer(buf) +
+                                                           2u * TPC * LP * sizeof(T));
+                    }
+                    sgo = reinterpret_cast<const T*>(stage_buffer(buf) + la_bytes);
                 } else {
                     st.ok = false;
                     if (lane == 0) atomicOr(p.status, kStatusStageTimeout);
@@ -207,18 +284,19 @@ msda_bwd_res_kernel(const __grid_constant__ ResParams rp) {
                         slot_begin = tl2 * 4 * LP;
                         slot_end = slot_begin + 4 * LP;
                     }
+                    // this lane's piece of grad_out[b, q, h, :] (from the staged row)
                     float go[VEC];
-                    const size_t obase =
-                        static_cast<size_t>(task0 + static_cast<long long>(qa + tl2) * p.H) * D;
-                    unpack16<T>(*reinterpret_cast<const uint4*>(gout + obase + j * VEC), go);
-                    Dot god[VEC];
-#pragma unroll
-                    for (int e = 0; e < VEC; ++e) god[e] = static_cast<Dot>(go[e]);
+                    const T* grow =
+                        sgo != nullptr
+                            ? sgo + tl2 * D
+                            : gout + static_cast<size_t>(task0 +
+                                                         static_cast<long long>(qa + tl2) * p.H) * D;
+                    unpack16<T>(*reinterpret_cast<const uint4*>(grow + j * VEC), go);
                     float gred[2][4];
                     if constexpr (SPLIT_RED) {
 #pragma unroll
                         for (int half = 0; half < 2; ++half) {
-                            const T* src = gout + obase + (half * LPR + j) * 4;
+                            const T* src = grow + (half * LPR + j) * 4;
                             const uint2 raw = *reinterpret_cast<const uint2*>(src);
                             const uint32_t wds[2] = {raw.x, raw.y};
 #pragma unroll
@@ -233,39 +311,110 @@ msda_bwd_res_kernel(const __grid_constant__ ResParams rp) {
                         }
                     }
 
-#pragma unroll 1
-                    for (int base = slot_begin; base < slot_end; base += STEP) {
-                        uint2 rec[UNROLL];
-                        uint32_t sa[UNROLL];
-                        uint4 raw[UNROLL];
+                    // One trip: U row instructions (U * RPI slots). Loads first, then the dot
+                    // products (reduced over a row's lanes and parked per slot), then the
+                    // scatter, whose shared-memory reads, compare-and-swaps and checks are
+                    // each issued for all rows before the next step, so their latencies overlap.
+                    auto trip = [&](int base, auto unroll_tag) {
+                        constexpr int U = decltype(unroll_tag)::value;
+                        uint2 rec[U];
+                        uint32_t sa[U];
+                        uint4 raw[U];
 #pragma unroll
-                        for (int u = 0; u < UNROLL; ++u) {
+                        for (int u = 0; u < U; ++u) {
                             const int slot = base + u * RPI + g;
                             rec[u] = s_rec[slot];
                             sa[u] = s_sa[slot];
                             if (slot >= slot_end) rec[u].x = kNoRow;
                         }
 #pragma unroll
-                        for (int u = 0; u < UNROLL; ++u) {
+                        for (int u = 0; u < U; ++u) {
                             // a missing corner loads row 0 instead of branching around the load
                             const uint32_t off = (rec[u].x != kNoRow) ? rec[u].x : 0u;
                             raw[u] = ldg16(vlane + static_cast<size_t>(off) * 16);
                         }
+                        // ---- dot products, GS row instructions at a time ----
+                        constexpr int GS = (U >= 4 && LPR >= 4) ? 4 : 1;
 #pragma unroll
-                        for (int u = 0; u < UNROLL; ++u) {
-                            const int slot = base + u * RPI + g;
-                            Dot part = 0;
-                            if (rec[u].x != kNoRow) {
-                                const float w = __uint_as_float(rec[u].y);
-                                const uint32_t acc_row = sa[u] & ~15u;
+                        for (int ub = 0; ub < U; ub += GS) {
+                            bool precise = false;
+                            if constexpr (F32) {
+                                uint32_t fl = 0;
+#pragma unroll
+                                for (int u = 0; u < GS; ++u)
+                                    fl |= (rec[ub + u].x != kNoRow) ? (sa[ub + u] & 1u) : 0u;
+                                precise = __any_sync(0xffffffffu, fl) != 0;
+                            }
+                            if (precise) {
+                                if constexpr (F32) {
+                                    double pd[GS];
+#pragma unroll
+                                    for (int u = 0; u < GS; ++u) {
+                                        float f[VEC];
+                                        unpack16<T>(raw[ub + u], f);
+                                        double acc = 0.0;
+                                        if (rec[ub + u].x != kNoRow) {
+#pragma unroll
+                                            for (int e = 0; e < VEC; ++e)
+                                                acc = fma(static_cast<double>(f[e]),
+                                                          static_cast<double>(go[e]), acc);
+                                        }
+                                        pd[u] = acc;
+                                    }
+                                    park_dots<LPR, RPI, GS>(pd, s_dot, base + ub * RPI, g, j,
+                                                            slot_end);
+                                }
+                            } else {
+                                float pf[GS];
+#pragma unroll
+                                for (int u = 0; u < GS; ++u) {
+                                    float f[VEC];
+                                    unpack16<T>(raw[ub + u], f);
+                                    float acc = 0.f;
+                                    if (rec[ub + u].x != kNoRow) {
+#pragma unroll
+                                        for (int e = 0; e < VEC; ++e) acc = fmaf(f[e], go[e], acc);
+                                    }
+                                    pf[u] = acc;
+                                }
+                                park_dots<LPR, RPI, GS>(pf, s_dot, base + ub * RPI, g, j, slot_end);
+                            }
+                        }
+                        // ---- scatter, SB row instructions at a time ----
+                        constexpr int NP = VEC / 4;   // 16-byte pieces of accumulator per lane
+                        constexpr int SB = (U >= 4) ? (NP == 1 ? 4 : 2) : 1;
+#pragma unroll
+                        for (int ub = 0; ub < U; ub += SB) {
+                            uint4 old[SB][NP];
+#pragma unroll
+                            for (int v = 0; v < SB; ++v) {
+                                const int u = ub + v;
+                                const uint32_t acc_row =
+                                    (rec[u].x != kNoRow) ? (sa[u] & ~15u) : 0u;
+                                sa[u] = acc_row;
                                 if (acc_row != 0u) {
-                                    // resident: fp32 accumulators in shared memory
 #pragma unroll
-                                    for (int v4 = 0; v4 < VEC / 4; ++v4)
-                                        smem_add_f32x4(acc_row + (j * VEC + v4 * 4) * 4,
-                                                       w * go[v4 * 4], w * go[v4 * 4 + 1],
-                                                       w * go[v4 * 4 + 2], w * go[v4 * 4 + 3],
-                                                       p.status);
+                                    for (int v4 = 0; v4 < NP; ++v4)
+                                        old[v][v4] = lds128(acc_row + (j * VEC + v4 * 4) * 4);
+                                }
+                            }
+#pragma unroll
+                            for (int v = 0; v < SB; ++v) {
+                                const int u = ub + v;
+                                if (rec[u].x == kNoRow) continue;
+                                const float w = __uint_as_float(rec[u].y);
+                                if (sa[u] != 0u) {
+#pragma unroll
+                                    for (int v4 = 0; v4 < NP; ++v4) {
+                                        const uint32_t a16 = sa[u] + (j * VEC + v4 * 4) * 4;
+                                        const bool ok = smem_cas_add_f32x4(
+                                            a16, old[v][v4], w * go[v4 * 4], w * go[v4 * 4 + 1],
+                                            w * go[v4 * 4 + 2], w * go[v4 * 4 + 3]);
+                                        if (!ok)
+                                            smem_add_f32x4(a16, w * go[v4 * 4], w * go[v4 * 4 + 1],
+                                                           w * go[v4 * 4 + 2], w * go[v4 * 4 + 3],
+                                                           p.status);
+                                    }
                                 } else if constexpr (SPLIT_RED) {
                                     float* row = reinterpret_cast<float*>(
                                         glane + static_cast<size_t>(rec[u].x) * 32);
@@ -282,31 +431,23 @@ msda_bwd_res_kernel(const __grid_constant__ ResParams rp) {
                                             glane + static_cast<size_t>(rec[u].x) * 16),
                                         contrib);
                                 }
-                                float f[VEC];
-                                unpack16<T>(raw[u], f);
-                                if (!F32 || (sa[u] & 1u)) {
-#pragma unroll
-                                    for (int e = 0; e < VEC; ++e) part = dot_fma(f[e], god[e], part);
-                                } else {
-                                    float pf = 0.f;
-#pragma unroll
-                                    for (int e = 0; e < VEC; ++e) pf = fmaf(f[e], go[e], pf);
-                                    part = static_cast<Dot>(pf);
-                                }
                             }
-#pragma unroll
-                            for (int off = LPR / 2; off >= PART; off >>= 1)
-                                part += __shfl_xor_sync(0xffffffffu, part, off);
-                            if (slot < slot_end && j < PART)
-                                s_part[(slot >> 2) * SSTRIDE + (slot & 3) * PART + j] = part;
                         }
-                    }
+                    };
+
+                    int base = slot_begin;
+#pragma unroll 1
+                    for (; base + UBIG * RPI <= slot_end; base += UBIG * RPI)
+                        trip(base, std::integral_constant<int, UBIG>{});
+#pragma unroll 1
+                    for (; base < slot_end; base += USMALL * RPI)
+                        trip(base, std::integral_constant<int, USMALL>{});
                 }
                 __syncwarp();
 
                 // ---- phase 3: lane = sample --------------------------------------
                 if (active) {
-                    const SampleGrad sg = sample_grad<T, 4, PART>(s_part + lane * SSTRIDE, geom);
+                    const SampleGrad sg = sample_grad<T, 4, 1>(s_dot + lane * 4, geom);
                     store_pair(static_cast<T*>(p.grad_loc) + 2 * gi, sg.x, sg.y);
                     static_cast<T*>(p.grad_attn)[gi] = Elem<T>::from_f(sg.attn);
                 }
@@ -405,18 +546,17 @@ cudaError_t launch_backward_resident(const Params& p_in, int dtype, int acc_f32,
     Params& p = rp.p;
     const size_t e = dtype == 0 ? 4 : 2;
     const int spi = p.tasks_per_item * p.LP;
-    // staging: one bulk copy per task and array, so a task's weights must be whole 16-byte
-    // pieces; with many tiny tasks per item direct loads are cheaper than tiny copies
-    if (!(p.stage && (static_cast<size_t>(p.LP) * e) % 16 == 0 && p.tasks_per_item <= 2))
-        p.stage = 0;
-    const UnitPlan up =
-        plan_units(p.B, p.H, p.Q, p.tasks_per_item, ls.sm_count, kResBwdWarps);
-    rp.chunks = up.chunks;
-    rp.unit_q = up.unit_q;
-    rp.nunits = up.nunits;
+    // staging of locations/weights: one bulk copy per task and array, so a task's weights
+    // must be whole 16-byte pieces (grad_output rows always are on this path)
+    if (!(p.stage && (static_cast<size_t>(p.LP) * e) % 16 == 0)) p.stage = 0;
+    // one CTA per SM (shared memory allows no more), fewer when a batch entry has fewer items
+    const long long items_per_b =
+        static_cast<long long>((p.Q + p.tasks_per_item - 1) / p.tasks_per_item) * p.H;
+    const int grid = static_cast<int>(items_per_b < ls.sm_count ? items_per_b : ls.sm_count);
     rp.lv_off = 128;
     rp.warp_off = rp.lv_off + ((static_cast<uint32_t>(p.L) * sizeof(ResLevel) + 127u) & ~127u);
-    rp.warp_bytes = (res_bwd_warp_bytes(spi, e) + 127u) & ~127u;
+    rp.warp_bytes =
+        (res_bwd_warp_bytes(p.stage, spi, p.tasks_per_item, p.D, e) + 127u) & ~127u;
     rp.map_off = rp.warp_off + kResBwdWarps * rp.warp_bytes;
     rp.map_row_bytes = static_cast<uint32_t>(p.D) * 4u;
     if (rp.map_off + rp.map_row_bytes > static_cast<uint32_t>(kResMaxSmem))
@@ -427,15 +567,15 @@ cudaError_t launch_backward_resident(const Params& p_in, int dtype, int acc_f32,
     rp.map_bytes = cap;
     rp.precise_amp = tune.precise_amp;
     switch (dtype) {
-        case 0: return launch_res_bwd_typed<float, float>(rp, rowplan.lpr, up.grid, stream);
+        case 0: return launch_res_bwd_typed<float, float>(rp, rowplan.lpr, grid, stream);
         case 1:
-            return acc_f32 ? launch_res_bwd_typed<__half, float>(rp, rowplan.lpr, up.grid, stream)
-                           : launch_res_bwd_typed<__half, __half>(rp, rowplan.lpr, up.grid, stream);
+            return acc_f32 ? launch_res_bwd_typed<__half, float>(rp, rowplan.lpr, grid, stream)
+                           : launch_res_bwd_typed<__half, __half>(rp, rowplan.lpr, grid, stream);
         case 2:
-            return acc_f32 ? launch_res_bwd_typed<__nv_bfloat16, float>(rp, rowplan.lpr, up.grid,
+            return acc_f32 ? launch_res_bwd_typed<__nv_bfloat16, float>(rp, rowplan.lpr, grid,
                                                                         stream)
                            : launch_res_bwd_typed<__nv_bfloat16, __nv_bfloat16>(
-                                 rp, rowplan.lpr, up.grid, stream);
+                                 rp, rowplan.lpr, grid, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -20,6 +20,7 @@ from .reporting import PatchResult, PatchStatus
 from .patch import AtomicPatch, BasePatch, LegacyPatch, Patch
 from .patcher import Patcher, replace_with
 from .mmcv_patch import DeformConv, ModulatedDeformConv, MultiScaleDeformableAttention
+from .version import check_version, get_version, is_mmcv_v1x, is_mmcv_v2x, mmcv_version
 from .mmdet_patch import ResNetAddRelu, ResNetMaxPool
 
 MSDA = MultiScaleDeformableAttention  # alias

@@ -100,6 +100,12 @@ class Patcher:
                 out.append((patch, group))
         return out
 
+    def _collect_all_patches(self, force_refresh: bool = False) -> List[Tuple[BasePatch, str]]:
+        """The reference's name for ``collect`` (mx_driving/patcher/patcher.py:796-832), which
+        its tests call. The list is rebuilt on every call (adding or disabling a patch takes
+        effect at once), so ``force_refresh`` has nothing left to do."""
+        return self.collect()
+
     @property
     def is_applied(self) -> bool:
         return self._applied
