@@ -45,6 +45,9 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--repeats", type=int, default=10,
+                    help="how many times the timed region of exactly --steps steps is run; "
+                         "ms_per_step is the median over these runs")
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--op", default="msda", choices=["msda", "fused", "gka", "da", "dcn", "addrelu", "maxpool"],
                     help="msda (the headline path, default); fused: MSDA with its callers' softmax and "
@@ -63,6 +66,8 @@ def parse_args():
     ap.add_argument("--ctas-per-sm-bwd", type=int, default=None, help="tuning: backward kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-strong", action="store_true",
+                    help="N > 1: skip the planned splits of one batch (strong scaling, stress shapes)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0,
                     help="budget of the CPU baseline sample")
     return ap.parse_args()
@@ -295,13 +300,6 @@ def run_native(args):
         step_c_abi(sets[i % NSETS])
     barrier()
     K_steps = args.steps
-    # CUDA events the library records immediately around its forward and backward kernel
-    # launches (on the launch stream), one quadruple per timed step.
-    kev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(K_steps)]
-    for quad in kev:
-        for e in quad:
-            e.record(stream)  # materialise the underlying cudaEvent_t
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     # The timed region is short (K steps of ~0.5 ms), so the clock sampler would mostly see an
     # idle GPU. Untimed steps of the same work run for ~0.4 s before and ~0.2 s after the timed
     # region while the sampler is on, so that its samples are taken under this load.
@@ -319,29 +317,51 @@ def run_native(args):
     if rank == 0:
         sampler.start()
     busy(0.4)
+    # The timed region is exactly K steps between two barriers; it is run `repeats` times and
+    # the median region is what the line reports (one region is only ~10 ms at K = 20).
+    R = max(1, args.repeats)
+    kev = [[[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(K_steps)]
+           for _ in range(R)]
+    for rep in kev:
+        for quad in rep:
+            for e in quad:
+                e.record(stream)  # materialise the underlying cudaEvent_t
+    region = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+              for _ in range(R)]
     launches0 = lib.msda_sm100_launch_count()
-    barrier()
-    ev0.record(stream)
-    for i in range(K_steps):
-        lib.msda_sm100_profile_events(*[e.cuda_event for e in kev[i]])
-        step_c_abi(sets[i % NSETS])
-    ev1.record(stream)
-    lib.msda_sm100_profile_events(None, None, None, None)
-    barrier()
-    total_ms = ev0.elapsed_time(ev1)
-    launches = lib.msda_sm100_launch_count() - launches0
+    for r in range(R):
+        barrier()
+        region[r][0].record(stream)
+        for i in range(K_steps):
+            lib.msda_sm100_profile_events(*[e.cuda_event for e in kev[r][i]])
+            step_c_abi(sets[i % NSETS])
+        region[r][1].record(stream)
+        lib.msda_sm100_profile_events(None, None, None, None)
+        barrier()
+    launches = (lib.msda_sm100_launch_count() - launches0) // R
     busy(0.2)
     clocks = sampler.stop() if rank == 0 else None
-    fwd_ms = sum(q[0].elapsed_time(q[1]) for q in kev) / K_steps
-    bwd_ms = sum(q[2].elapsed_time(q[3]) for q in kev) / K_steps
+    region_ms = [a.elapsed_time(b) for a, b in region]
+    fwd_all = sorted(q[0].elapsed_time(q[1]) for rep in kev for q in rep)
+    bwd_all = sorted(q[2].elapsed_time(q[3]) for rep in kev for q in rep)
+    fwd_ms = fwd_all[len(fwd_all) // 2]
+    bwd_ms = bwd_all[len(bwd_all) // 2]
 
-    t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+    t = torch.tensor(region_ms, device=dev, dtype=torch.float64)
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms = float(t.item())
-    ms_per_step = total_ms / K_steps
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)     # per region, the slowest rank
+    per_step = sorted(float(x) / K_steps for x in t.tolist())
+    ms_per_step = per_step[len(per_step) // 2]
+    timing = {"repeats": R, "ms_per_step_median": ms_per_step,
+              "ms_per_step_p10": per_step[max(0, int(0.1 * (R - 1)))],
+              "ms_per_step_min": per_step[0], "ms_per_step_max": per_step[-1]}
     global_samples = w.B if query_shard else w.B * world
     value = global_samples / (ms_per_step * 1e-3)
+
+    # ---------------- one batch spread over the ranks, and the large-head-dim shapes -------
+    extra = {}
+    if world > 1 and not query_shard and not args.no_strong:
+        extra = run_planned_splits(lib, dist, dev, rank, world, w, dtype, ms_per_step, barrier)
 
     # ---------------- end-to-end through the Python API with host operands ----------
     e2e = None
@@ -359,9 +379,11 @@ def run_native(args):
     bwd_gbs = bb / (bwd_ms * 1e-3) / 1e9
     fwd_gbs = fb / (fwd_ms * 1e-3) / 1e9
     step_gbs = (fb + bb) / (ms_per_step * 1e-3) / 1e9
+    bwd_kernel = backward_kernel_name(lib, capi, w.D, esize)
     roofline = {
-        "bound": "hbm", "kernel": "msda_bwd_kernel", "achieved": bwd_gbs, "peak": peak,
-        "unit": "GB/s", "frac": bwd_gbs / peak, "traffic": TRAFFIC_BYTES.get((w.name, args.dtype)),
+        "bound": "hbm", "kernel": bwd_kernel, "achieved": bwd_gbs, "peak": peak,
+        "unit": "GB/s", "frac": bwd_gbs / peak,
+        "traffic": TRAFFIC_BYTES.get((bwd_kernel, w.name, args.dtype)),
         "peak_kind": peak_kind, "algorithmic_bytes": bb, "kernel_ms": bwd_ms,
         "forward": {"kernel": "msda_fwd_kernel", "achieved": fwd_gbs, "frac": fwd_gbs / peak,
                     "algorithmic_bytes": fb, "kernel_ms": fwd_ms},
@@ -375,12 +397,14 @@ def run_native(args):
         "data": "synthetic",
         "config": workload_config(w, w_local, query_shard),
         "roofline": roofline, "clocks": clocks, "gpu_launches": int(launches) * world,
+        "timing": timing,
         "tuning": {"stage": lib.msda_sm100_tune(capi.TUNE_STAGE, -1),
                    "ctas_per_sm": lib.msda_sm100_tune(capi.TUNE_CTAS_PER_SM, -1),
                    "ctas_per_sm_bwd": lib.msda_sm100_tune(capi.TUNE_CTAS_PER_SM_BWD, -1)},
     }
     if e2e is not None:
         line["e2e"] = e2e
+    line.update(extra)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(w, args.cpu_seconds)
     print(json.dumps(line))
@@ -388,9 +412,124 @@ def run_native(args):
         dist.destroy_process_group()
 
 
-# ncu dram__bytes_read.sum + dram__bytes_write.sum of one backward-kernel launch, per
-# (workload, dtype); from the captures summarised under profiles/.
-TRAFFIC_BYTES = {("bevformer_sca", "float32"): 626_346_752}
+# DRAM bytes (ncu: dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the dominant
+# kernel, keyed by (kernel, workload, dtype). An entry applies only while the kernel of that
+# name is the one launched, so a number captured for an older kernel is never reported for a
+# newer one; combinations without a capture report null.
+TRAFFIC_BYTES = {
+    ("msda_bwd_kernel", "bevformer_sca", "float32"): 626_346_752,
+}
+
+
+def backward_kernel_name(lib, capi, D, dtype_size):
+    """Name of the kernel msda_sm100_backward_ws launches for rows of D elements: the
+    resident-level kernel on the 16-byte vector path (rows of 16 * 2^k <= 512 bytes) unless
+    it is switched off, else the all-through-L2 kernel."""
+    row = D * dtype_size
+    vector = row % 16 == 0 and (row // 16) & (row // 16 - 1) == 0 and row <= 512
+    resident = lib.msda_sm100_tune(capi.TUNE_RESIDENT, -1) != 0
+    return "msda_bwd_res_kernel" if (vector and resident) else "msda_bwd_kernel"
+
+
+def run_planned_splits(lib, dist, dev, rank, world, w, dtype, replica_ms_per_step, barrier):
+    """N > 1, after the replica timing: ONE batch spread over the ranks by the planner
+    (drivingsdk_b200.dist.plan with a cost model built from the step time just measured), for
+    the headline workload ("strong") and for the large-head-dim shape with 8 batch entries
+    ("config5a", bf16) and with one entry whose queries are split over all ranks and whose
+    grad_value is summed with NCCL ("config5b", bf16). Every rank draws only the entries it
+    works on (seeded per entry). Timing: CUDA events, max over ranks; the reduction's own
+    time is reported as allreduce_ms. A few steps each, so that the whole thing adds seconds."""
+    import torch
+    from drivingsdk_b200 import capi, workloads
+    from drivingsdk_b200 import dist as sdist
+
+    stream = torch.cuda.current_stream()
+
+    def one(label, wl, dt, force_kind=None):
+        esize = 4 if dt == torch.float32 else 2
+        code = capi.dtype_code(dt)
+        # per-entry cost: scale the measured replica step by the algorithmic bytes
+        fb0, bb0 = workloads.compulsory_bytes(w.with_batch(1), 4 if dtype == torch.float32 else 2)
+        fb1, bb1 = workloads.compulsory_bytes(wl.with_batch(1), esize)
+        entry_s = (replica_ms_per_step * 1e-3 / w.B) * (fb1 + bb1) / (fb0 + bb0)
+        cost = sdist.CostModel(entry_s, float(wl.K * wl.H * wl.D * esize))
+        plan = sdist.plan(wl.B, wl.Q, world, cost=cost)
+        if force_kind == "hybrid" and plan.kind != "hybrid":
+            plan = sdist.candidate_plans(wl.B, wl.Q, world)[1]
+        groups = sdist.make_groups(plan)
+        group = groups.get(plan.group_of(rank))
+        b0, b1 = plan.ranges[rank]
+        if plan.kind == "hybrid":
+            q0, q1 = plan.query_ranges[rank]
+        elif plan.kind == "query":
+            (q0, q1), (b0, b1) = plan.ranges[rank], (0, wl.B)
+        else:
+            q0, q1 = 0, wl.Q
+        nb, nq = max(0, b1 - b0), max(0, q1 - q0)
+        times, red_times = [], []
+        if nb > 0 and nq > 0:
+            ents = [workloads.make_inputs(wl.with_batch(1), dt, seed_offset=50 + b)
+                    for b in range(b0, b1)]
+            cat = lambda k, qs: torch.cat([e[k][:, q0:q1] if qs else e[k] for e in ents]) \
+                .to(dt).to(dev).contiguous()
+            value, loc, attn, go = cat("value", False), cat("loc", True), cat("attn", True), \
+                cat("grad_out", True)
+            shapes = ents[0]["shapes"].to(torch.int32).to(dev)
+            starts = ents[0]["starts"].to(torch.int32).to(dev)
+            dims = (nb, wl.K, wl.H, wl.D, wl.L, nq, wl.P)
+            out = torch.empty(nb, nq, wl.H * wl.D, device=dev, dtype=dt)
+            gv, gl, ga = torch.empty_like(value), torch.empty_like(loc), torch.empty_like(attn)
+            ws_bytes = lib.msda_sm100_backward_workspace_bytes(nb, wl.K, wl.H, wl.D, code)
+            ws = torch.empty(max(ws_bytes, 16), device=dev, dtype=torch.uint8)
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+
+        def step(timed):
+            if timed:
+                e[0].record(stream)
+            if nb > 0 and nq > 0:
+                capi.check(lib.msda_sm100_forward(
+                    value.data_ptr(), shapes.data_ptr(), starts.data_ptr(), loc.data_ptr(),
+                    attn.data_ptr(), out.data_ptr(), *dims, code, stream.cuda_stream), "forward")
+                capi.check(lib.msda_sm100_backward_ws(
+                    value.data_ptr(), shapes.data_ptr(), starts.data_ptr(), loc.data_ptr(),
+                    attn.data_ptr(), go.data_ptr(), gv.data_ptr(), gl.data_ptr(), ga.data_ptr(),
+                    ws.data_ptr(), ws_bytes, *dims, code, stream.cuda_stream), "backward")
+            if timed:
+                e[1].record(stream)
+            if plan.needs_allreduce and nb > 0:
+                dist.all_reduce(gv, group=group)
+            if timed:
+                e[2].record(stream)
+
+        for _ in range(3):
+            step(False)
+        STEPS = 8
+        for _ in range(STEPS):
+            barrier()
+            step(True)
+            barrier()
+            times.append(e[0].elapsed_time(e[2]))
+            red_times.append(e[1].elapsed_time(e[2]))
+        t = torch.tensor([times, red_times], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        step_ms = sorted(t[0].tolist())[STEPS // 2]
+        red_ms = sorted(t[1].tolist())[STEPS // 2]
+        return {"workload": wl.name, "B": wl.B, "dtype": str(dt)[6:], "plan": plan.kind,
+                "ranges": [list(r) for r in plan.ranges],
+                "query_ranges": [list(r) for r in plan.query_ranges],
+                "idle_ranks": sum(plan.is_idle(r) for r in range(world)),
+                "ms_per_step": step_ms, "allreduce_ms": red_ms if plan.needs_allreduce else 0.0,
+                "value": wl.B / (step_ms * 1e-3), "unit": UNIT, "scaling": "strong",
+                "predicted_ms": None if plan.predicted_seconds is None
+                else plan.predicted_seconds * 1e3,
+                "single_gpu_ms": entry_s * wl.B * 1e3,
+                "efficiency_ceiling": plan.efficiency_ceiling()}
+
+    stress = workloads.WORKLOADS["stress_d128"]
+    out = {"strong": one("strong", w, dtype)}
+    out["config5a"] = one("config5a", stress, torch.bfloat16)
+    out["config5b"] = one("config5b", stress.with_batch(1), torch.bfloat16, force_kind="hybrid")
+    return out
 
 
 def run_e2e(sdk, host_sets, shapes_i32, starts_i32, dev, dtype, world, query_shard, steps,

@@ -1,6 +1,9 @@
 """In-tree build of the native pieces (run by ``__graft_entry__.build()``).
 
     drivingsdk_b200/libmsda_sm100.so   the C-ABI library: hand-written CUDA for sm_100a
+    drivingsdk_b200/libmsda_sm100_dbg.so  the same sources with -DMSDA_DEBUG_BOUNDS: every row
+                                       offset the MSDA kernels compute is checked before use
+                                       (what the tests run in place of a memory checker)
     drivingsdk_b200/_C.so              the torch extension that calls it
 
 Both are plain ``nvcc`` / ``g++`` command lines so the result sits next to the
@@ -17,6 +20,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 ROOT = os.path.dirname(PKG)
 LIB = os.path.join(PKG, "libmsda_sm100.so")
+DEBUG_LIB = os.path.join(PKG, "libmsda_sm100_dbg.so")
 EXT = os.path.join(PKG, "_C.so")
 
 CUDA_SOURCES = ["msda_capi.cu", "msda_fwd_sm100.cu", "msda_bwd_sm100.cu", "msda_res_bwd_sm100.cu",
@@ -51,19 +55,23 @@ def _run(cmd, log_name):
     return proc.stdout
 
 
-def build_library(force=False, verbose_ptxas=False) -> str:
+def build_library(force=False, verbose_ptxas=False, debug_bounds=False) -> str:
     """nvcc each .cu to an object (in parallel: the kernel files hold many template
-    instantiations), then link the shared library."""
+    instantiations), then link the shared library. ``debug_bounds`` builds the
+    bounds-checking variant next to the normal one."""
     from concurrent.futures import ThreadPoolExecutor
+    target = DEBUG_LIB if debug_bounds else LIB
+    obj_dir = OBJ_DIR + ("_dbg" if debug_bounds else "")
     srcs = [os.path.join(CSRC, s) for s in CUDA_SOURCES]
     deps = srcs + [os.path.join(CSRC, h) for h in CUDA_HEADERS] + [
         os.path.join(ROOT, "include", "msda_sm100.h"),
         os.path.join(ROOT, "include", "conv_ops_sm100.h")]
-    if not (force or _stale(LIB, deps)):
-        return LIB
-    os.makedirs(OBJ_DIR, exist_ok=True)
-    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if verbose_ptxas else [])
-    objs = [os.path.join(OBJ_DIR, os.path.basename(s)[:-3] + ".o") for s in srcs]
+    if not (force or _stale(target, deps)):
+        return target
+    os.makedirs(obj_dir, exist_ok=True)
+    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if verbose_ptxas else []) + (
+        ["-DMSDA_DEBUG_BOUNDS"] if debug_bounds else [])
+    objs = [os.path.join(obj_dir, os.path.basename(s)[:-3] + ".o") for s in srcs]
 
     def compile_one(pair):
         src, obj = pair
@@ -73,9 +81,9 @@ def build_library(force=False, verbose_ptxas=False) -> str:
         logs = list(pool.map(compile_one, zip(srcs, objs)))
     if verbose_ptxas:
         sys.stdout.write("".join(logs))
-    _run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared"] + objs + ["-o", LIB],
+    _run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared"] + objs + ["-o", target],
          "nvcc link")
-    return LIB
+    return target
 
 
 def build_extension(force=False) -> str:
@@ -105,12 +113,15 @@ def build_extension(force=False) -> str:
 
 
 def build_all(force=False):
-    return build_library(force), build_extension(force)
+    return (build_library(force), build_library(force, debug_bounds=True),
+            build_extension(force))
 
 
 if __name__ == "__main__":
     force = "--force" in sys.argv
     lib = build_library(force, verbose_ptxas="--ptxas" in sys.argv)
+    dbg = build_library(force, debug_bounds=True)
     ext = build_extension(force)
     print(lib)
+    print(dbg)
     print(ext)

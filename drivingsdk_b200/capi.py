@@ -11,6 +11,8 @@ import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libmsda_sm100.so")
+# the same library compiled with -DMSDA_DEBUG_BOUNDS (every computed row offset checked)
+DEBUG_LIB_PATH = os.path.join(_HERE, "libmsda_sm100_dbg.so")
 
 F32, F16, BF16 = 0, 1, 2
 TUNE_STAGE, TUNE_CTAS_PER_SM, TUNE_CTAS_PER_SM_BWD, TUNE_INTERLEAVE, TUNE_SPIN_LIMIT = 0, 1, 2, 3, 4
@@ -58,6 +60,7 @@ SIGNATURES = {
     "msda_sm100_strerror": (ctypes.c_char_p, [_i]),
     "msda_sm100_last_cuda_error": (_i, []),
     "msda_sm100_abi_version": (_i, []),
+    "msda_sm100_debug_bounds": (_i, []),
 }
 
 
@@ -70,23 +73,36 @@ class DcnShape(ctypes.Structure):
 
 
 _lib = None
+_debug_lib = None
+
+
+def _open(path):
+    if not os.path.exists(path):
+        raise ImportError(
+            f"{path} is not built; run `python -m drivingsdk_b200.build`. "
+            "There is no CPU fallback.")
+    lib = ctypes.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
 
 
 def load():
     """Returns the loaded library with argument types set; raises if it is not built."""
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
-            raise ImportError(
-                f"{LIB_PATH} is not built; run `python -m drivingsdk_b200.build`. "
-                "There is no CPU fallback.")
-        lib = ctypes.CDLL(LIB_PATH)
-        for name, (res, args) in SIGNATURES.items():
-            fn = getattr(lib, name)
-            fn.restype = res
-            fn.argtypes = args
-        _lib = lib
+        _lib = _open(LIB_PATH)
     return _lib
+
+
+def load_debug():
+    """The bounds-checking build of the same library (its own status word and knobs)."""
+    global _debug_lib
+    if _debug_lib is None:
+        _debug_lib = _open(DEBUG_LIB_PATH)
+    return _debug_lib
 
 
 def dtype_code(torch_dtype) -> int:

@@ -120,6 +120,7 @@ int set_row_units(Params& p, const RowPlan& rp, int dtype) {
     const unsigned long long rows = static_cast<unsigned long long>(p.B) * p.K * p.H;
     if (rows * units >= 0xffffffffull) return MSDA_ERR_LIMIT;
     p.row_units = static_cast<uint32_t>(units);
+    p.limit_units = static_cast<uint32_t>(rows * units);
     return MSDA_OK;
 }
 
@@ -484,5 +485,13 @@ const char* msda_sm100_strerror(int status) {
 int msda_sm100_last_cuda_error(void) { return t_last_cuda_error; }
 
 int msda_sm100_abi_version(void) { return kAbiVersion; }
+
+int msda_sm100_debug_bounds(void) {
+#ifdef MSDA_DEBUG_BOUNDS
+    return 1;
+#else
+    return 0;
+#endif
+}
 
 }  // extern "C"

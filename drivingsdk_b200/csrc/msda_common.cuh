@@ -34,6 +34,8 @@ constexpr int kDrainLimit = 1 << 20; // bound on waiting for copies already issu
 
 // Device status bits, sticky until read by msda_sm100_device_status().
 constexpr int kStatusStageTimeout = 1;  // a staged tile never arrived
+constexpr int kStatusOutOfBounds = 16;  // MSDA_DEBUG_BOUNDS build: a computed row offset fell outside
+                                        // value / grad_value; the access was skipped
 
 // Division by a runtime constant without a divide: q = (n * mul) >> shift, exact
 // for 0 <= n < 2^31 (round-up method with a 31 + ceil(log2 d) bit shift).
@@ -101,6 +103,7 @@ struct Params {
     long long nitems;   // ceil(ntasks / tasks_per_item)
     int* status;        // device status word
     uint32_t row_units;      // offset units per value row: 16-byte pieces, or elements (scalar path)
+    uint32_t limit_units;    // B * K * H * row_units: one past the last valid row offset + row
     uint32_t warp_smem;      // bytes of dynamic shared memory per warp
     FastDiv fd_qh, fd_h, fd_lp;  // division by Q*H, H, L*P
     // walk order of the items: 0 = memory order; B > 0 = batch entries interleaved (walk
@@ -372,6 +375,31 @@ __device__ __forceinline__ void sample_setup(float lx, float ly, float a, int Wl
     g.x0 = x0;
     g.y0 = y0;
     g.valid = valid;
+}
+
+// MSDA_DEBUG_BOUNDS build (the stand-in for a memory checker where none can be run): every
+// row offset a sample produced is checked against the extent of value / grad_value before
+// anything is loaded from it or added to it. A violation sets kStatusOutOfBounds in the
+// status word and turns the record into "no row", so the access never happens. A correct
+// kernel on a consistent level table never trips it; the int32 offset arithmetic is the
+// place the reference itself marks as hazardous (op_kernel/msda.h:428).
+__device__ __forceinline__ void debug_check_rows(const Params& p, uint4& rec01, uint4& rec23) {
+#ifdef MSDA_DEBUG_BOUNDS
+    bool bad = false;
+    auto check = [&](uint32_t& off) {
+        if (off != kNoRow && (off >= p.limit_units || p.limit_units - off < p.row_units)) {
+            bad = true;
+            off = kNoRow;
+        }
+    };
+    check(rec01.x);
+    check(rec01.z);
+    check(rec23.x);
+    check(rec23.z);
+    if (bad) atomicOr(p.status, kStatusOutOfBounds);
+#else
+    (void)p; (void)rec01; (void)rec23;
+#endif
 }
 
 // Nearest-pixel variant (geometric kernel attention): the location holds pixel coordinates;

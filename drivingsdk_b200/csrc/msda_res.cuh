@@ -45,6 +45,7 @@ struct ResParams {
     uint32_t lv_off;         // shared-memory offsets: level table,
     uint32_t warp_off;       //   first warp's private area,
     uint32_t warp_bytes;     //   its size,
+    uint32_t trash_off;      //   one scratch accumulator row (stays zero),
     uint32_t map_off;        //   resident area,
     uint32_t map_bytes;      //   its capacity
     uint32_t map_row_bytes;  // bytes of one resident pixel (fp32 accumulator row: 4 * D)

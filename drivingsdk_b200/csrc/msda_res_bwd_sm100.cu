@@ -114,14 +114,16 @@ msda_bwd_res_kernel(const __grid_constant__ ResParams rp) {
     uint32_t* s_sa = reinterpret_cast<uint32_t*>(wb + kResRecBytes);
     Dot* s_dot = reinterpret_cast<Dot*>(wb + kResRecBytes + kResSaBytes);   // one per slot
     const uint32_t map_saddr = smem_u32(smem + rp.map_off);
+    const uint32_t trash_saddr = smem_u32(smem + rp.trash_off);   // one accumulator row of zeros
 
     if (!res_plan_levels(rp, s_lv, s_ctl)) return;
     ResLane lv0, lv1;
     res_lane_levels(p, s_lv, lane, lv0, lv1);
 
-    // clear the accumulators once; every unit leaves them cleared behind
-    for (uint32_t i = threadIdx.x * 16u; i < rp.map_bytes; i += NW * 32 * 16u)
-        sts128(map_saddr + i, make_uint4(0u, 0u, 0u, 0u));
+    // clear the scratch row and the accumulators once; every unit leaves them cleared behind
+    for (uint32_t i = threadIdx.x * 16u; i < rp.map_off - rp.trash_off + rp.map_bytes;
+         i += NW * 32 * 16u)
+        sts128(trash_saddr + i, make_uint4(0u, 0u, 0u, 0u));
 
     // Staging (bulk copies into one of two per-warp buffers, one item ahead): the item's
     // locations and weights when p.stage is set, and always its grad_output rows.
@@ -260,6 +262,23 @@ msda_bwd_res_kernel(const __grid_constant__ ResParams rp) {
                     sample_setup_res(lx, ly, a, lv, row_base, static_cast<uint32_t>(p.H),
                                      p.row_units, map_saddr, rp.map_row_bytes, rec01, rec23, geom,
                                      rc);
+#ifdef MSDA_DEBUG_BOUNDS
+                    {
+                        // resident accumulator rows must lie inside the resident area
+                        bool bad = false;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const uint32_t a16 = rc.sa[c];
+                            if (a16 != 0u && (a16 < map_saddr ||
+                                              a16 + rp.map_row_bytes > map_saddr + rp.map_bytes)) {
+                                bad = true;
+                                rc.sa[c] = 0u;
+                            }
+                        }
+                        if (bad) atomicOr(p.status, kStatusOutOfBounds);
+                    }
+                    debug_check_rows(p, rec01, rec23);
+#endif
                     if (F32 && fmaxf(geom.wf, geom.hf) * fabsf(geom.a) >= rp.precise_amp) {
                         // accumulator addresses are multiples of 16: bit 0 carries the flag
                         rc.sa[0] |= 1u; rc.sa[1] |= 1u; rc.sa[2] |= 1u; rc.sa[3] |= 1u;
@@ -292,6 +311,11 @@ msda_bwd_res_kernel(const __grid_constant__ ResParams rp) {
                             : gout + static_cast<size_t>(task0 +
                                                          static_cast<long long>(qa + tl2) * p.H) * D;
                     unpack16<T>(*reinterpret_cast<const uint4*>(grow + j * VEC), go);
+                    double god[F32 ? VEC : 1];
+                    if constexpr (F32) {
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) god[e] = static_cast<double>(go[e]);
+                    }
                     float gred[2][4];
                     if constexpr (SPLIT_RED) {
 #pragma unroll
@@ -311,59 +335,58 @@ msda_bwd_res_kernel(const __grid_constant__ ResParams rp) {
                         }
                     }
 
-                    // One trip: U row instructions (U * RPI slots). Loads first, then the dot
+                    // One trip: U row instructions (U * RPI slots): loads first, then the dot
                     // products (reduced over a row's lanes and parked per slot), then the
-                    // scatter, whose shared-memory reads, compare-and-swaps and checks are
-                    // each issued for all rows before the next step, so their latencies overlap.
-                    auto trip = [&](int base, auto unroll_tag) {
+                    // scatter. A trip is compiled in several forms and the form is picked per
+                    // trip by warp votes, so that the common cases run without per-row
+                    // branches: KIND 0 = no resident row (reductions in L2 only), 1 = every row
+                    // that exists is resident (compare-and-swap in shared memory only; rows
+                    // that do not exist add zero to a scratch row), 2 = both kinds.
+                    // PRECISE = dot products in double. GUARDED = slots past the task's last
+                    // one are skipped.
+                    auto trip = [&](int base, auto unroll_tag, auto kind_tag, auto precise_tag,
+                                    auto guarded_tag) {
                         constexpr int U = decltype(unroll_tag)::value;
+                        constexpr int KIND = decltype(kind_tag)::value;
+                        constexpr bool PRECISE = decltype(precise_tag)::value;
+                        constexpr bool GUARDED = decltype(guarded_tag)::value;
                         uint2 rec[U];
                         uint32_t sa[U];
                         uint4 raw[U];
+                        bool exists[U];
 #pragma unroll
                         for (int u = 0; u < U; ++u) {
                             const int slot = base + u * RPI + g;
                             rec[u] = s_rec[slot];
-                            sa[u] = s_sa[slot];
-                            if (slot >= slot_end) rec[u].x = kNoRow;
+                            sa[u] = (KIND != 0) ? (s_sa[slot] & ~15u) : 0u;
+                            exists[u] = rec[u].x != kNoRow && (!GUARDED || slot < slot_end);
+                            if (GUARDED && slot >= slot_end) sa[u] = 0u;
+                            // KIND 1: a corner that does not exist adds zero to the scratch row
+                            if (KIND == 1 && !exists[u]) sa[u] = trash_saddr;
                         }
 #pragma unroll
                         for (int u = 0; u < U; ++u) {
                             // a missing corner loads row 0 instead of branching around the load
-                            const uint32_t off = (rec[u].x != kNoRow) ? rec[u].x : 0u;
+                            const uint32_t off = exists[u] ? rec[u].x : 0u;
                             raw[u] = ldg16(vlane + static_cast<size_t>(off) * 16);
                         }
                         // ---- dot products, GS row instructions at a time ----
                         constexpr int GS = (U >= 4 && LPR >= 4) ? 4 : 1;
 #pragma unroll
                         for (int ub = 0; ub < U; ub += GS) {
-                            bool precise = false;
-                            if constexpr (F32) {
-                                uint32_t fl = 0;
+                            if constexpr (PRECISE) {
+                                double pd[GS];
 #pragma unroll
-                                for (int u = 0; u < GS; ++u)
-                                    fl |= (rec[ub + u].x != kNoRow) ? (sa[ub + u] & 1u) : 0u;
-                                precise = __any_sync(0xffffffffu, fl) != 0;
-                            }
-                            if (precise) {
-                                if constexpr (F32) {
-                                    double pd[GS];
+                                for (int u = 0; u < GS; ++u) {
+                                    float f[VEC];
+                                    unpack16<T>(raw[ub + u], f);
+                                    double acc = 0.0;
 #pragma unroll
-                                    for (int u = 0; u < GS; ++u) {
-                                        float f[VEC];
-                                        unpack16<T>(raw[ub + u], f);
-                                        double acc = 0.0;
-                                        if (rec[ub + u].x != kNoRow) {
-#pragma unroll
-                                            for (int e = 0; e < VEC; ++e)
-                                                acc = fma(static_cast<double>(f[e]),
-                                                          static_cast<double>(go[e]), acc);
-                                        }
-                                        pd[u] = acc;
-                                    }
-                                    park_dots<LPR, RPI, GS>(pd, s_dot, base + ub * RPI, g, j,
-                                                            slot_end);
+                                    for (int e = 0; e < VEC; ++e)
+                                        acc = fma(static_cast<double>(f[e]), god[e], acc);
+                                    pd[u] = exists[ub + u] ? acc : 0.0;
                                 }
+                                park_dots<LPR, RPI, GS>(pd, s_dot, base + ub * RPI, g, j, slot_end);
                             } else {
                                 float pf[GS];
 #pragma unroll
@@ -371,77 +394,168 @@ msda_bwd_res_kernel(const __grid_constant__ ResParams rp) {
                                     float f[VEC];
                                     unpack16<T>(raw[ub + u], f);
                                     float acc = 0.f;
-                                    if (rec[ub + u].x != kNoRow) {
 #pragma unroll
-                                        for (int e = 0; e < VEC; ++e) acc = fmaf(f[e], go[e], acc);
-                                    }
-                                    pf[u] = acc;
+                                    for (int e = 0; e < VEC; ++e) acc = fmaf(f[e], go[e], acc);
+                                    pf[u] = exists[ub + u] ? acc : 0.f;
                                 }
                                 park_dots<LPR, RPI, GS>(pf, s_dot, base + ub * RPI, g, j, slot_end);
                             }
                         }
-                        // ---- scatter, SB row instructions at a time ----
+                        // ---- scatter ----
                         constexpr int NP = VEC / 4;   // 16-byte pieces of accumulator per lane
-                        constexpr int SB = (U >= 4) ? (NP == 1 ? 4 : 2) : 1;
+                        auto global_red = [&](int u, float w) {
+                            if constexpr (SPLIT_RED) {
+                                float* row = reinterpret_cast<float*>(
+                                    glane + static_cast<size_t>(rec[u].x) * 32);
+                                red_add_f32x4(row, w * gred[0][0], w * gred[0][1], w * gred[0][2],
+                                              w * gred[0][3]);
+                                red_add_f32x4(row + LPR * 4, w * gred[1][0], w * gred[1][1],
+                                              w * gred[1][2], w * gred[1][3]);
+                            } else {
+                                float contrib[VEC];
 #pragma unroll
-                        for (int ub = 0; ub < U; ub += SB) {
-                            uint4 old[SB][NP];
+                                for (int e = 0; e < VEC; ++e) contrib[e] = w * go[e];
+                                red_add_vec<TG, VEC>(
+                                    reinterpret_cast<TG*>(glane +
+                                                          static_cast<size_t>(rec[u].x) * 16),
+                                    contrib);
+                            }
+                        };
+                        if constexpr (KIND == 0) {
 #pragma unroll
-                            for (int v = 0; v < SB; ++v) {
-                                const int u = ub + v;
-                                const uint32_t acc_row =
-                                    (rec[u].x != kNoRow) ? (sa[u] & ~15u) : 0u;
-                                sa[u] = acc_row;
-                                if (acc_row != 0u) {
+                            for (int u = 0; u < U; ++u)
+                                if (exists[u]) global_red(u, __uint_as_float(rec[u].y));
+                        } else if constexpr (KIND == 1) {
+                            // every slot has an accumulator row (the scratch row for corners
+                            // that do not exist, which get weight 0): no branches until a
+                            // compare-and-swap is lost
+                            constexpr int SB = (U >= 4) ? (NP == 1 ? 4 : 2) : 1;
+#pragma unroll
+                            for (int ub = 0; ub < U; ub += SB) {
+                                uint4 old[SB][NP];
+#pragma unroll
+                                for (int v = 0; v < SB; ++v)
 #pragma unroll
                                     for (int v4 = 0; v4 < NP; ++v4)
-                                        old[v][v4] = lds128(acc_row + (j * VEC + v4 * 4) * 4);
+                                        old[v][v4] = lds128(sa[ub + v] + (j * VEC + v4 * 4) * 4);
+                                bool lost = false;
+                                bool ok[SB][NP];
+#pragma unroll
+                                for (int v = 0; v < SB; ++v) {
+                                    const int u = ub + v;
+                                    const float w = exists[u] ? __uint_as_float(rec[u].y) : 0.f;
+#pragma unroll
+                                    for (int v4 = 0; v4 < NP; ++v4) {
+                                        ok[v][v4] = smem_cas_add_f32x4(
+                                            sa[u] + (j * VEC + v4 * 4) * 4, old[v][v4],
+                                            w * go[v4 * 4], w * go[v4 * 4 + 1], w * go[v4 * 4 + 2],
+                                            w * go[v4 * 4 + 3]);
+                                        lost |= !ok[v][v4];
+                                    }
+                                }
+                                if (__any_sync(0xffffffffu, lost)) {
+#pragma unroll
+                                    for (int v = 0; v < SB; ++v) {
+                                        const int u = ub + v;
+                                        const float w =
+                                            exists[u] ? __uint_as_float(rec[u].y) : 0.f;
+#pragma unroll
+                                        for (int v4 = 0; v4 < NP; ++v4)
+                                            if (!ok[v][v4])
+                                                smem_add_f32x4(sa[u] + (j * VEC + v4 * 4) * 4,
+                                                               w * go[v4 * 4], w * go[v4 * 4 + 1],
+                                                               w * go[v4 * 4 + 2],
+                                                               w * go[v4 * 4 + 3], p.status);
+                                    }
                                 }
                             }
+                        } else {
 #pragma unroll
-                            for (int v = 0; v < SB; ++v) {
-                                const int u = ub + v;
-                                if (rec[u].x == kNoRow) continue;
+                            for (int u = 0; u < U; ++u) {
+                                if (!exists[u]) continue;
                                 const float w = __uint_as_float(rec[u].y);
                                 if (sa[u] != 0u) {
 #pragma unroll
-                                    for (int v4 = 0; v4 < NP; ++v4) {
-                                        const uint32_t a16 = sa[u] + (j * VEC + v4 * 4) * 4;
-                                        const bool ok = smem_cas_add_f32x4(
-                                            a16, old[v][v4], w * go[v4 * 4], w * go[v4 * 4 + 1],
-                                            w * go[v4 * 4 + 2], w * go[v4 * 4 + 3]);
-                                        if (!ok)
-                                            smem_add_f32x4(a16, w * go[v4 * 4], w * go[v4 * 4 + 1],
-                                                           w * go[v4 * 4 + 2], w * go[v4 * 4 + 3],
-                                                           p.status);
-                                    }
-                                } else if constexpr (SPLIT_RED) {
-                                    float* row = reinterpret_cast<float*>(
-                                        glane + static_cast<size_t>(rec[u].x) * 32);
-                                    red_add_f32x4(row, w * gred[0][0], w * gred[0][1],
-                                                  w * gred[0][2], w * gred[0][3]);
-                                    red_add_f32x4(row + LPR * 4, w * gred[1][0], w * gred[1][1],
-                                                  w * gred[1][2], w * gred[1][3]);
+                                    for (int v4 = 0; v4 < NP; ++v4)
+                                        smem_add_f32x4(sa[u] + (j * VEC + v4 * 4) * 4,
+                                                       w * go[v4 * 4], w * go[v4 * 4 + 1],
+                                                       w * go[v4 * 4 + 2], w * go[v4 * 4 + 3],
+                                                       p.status);
                                 } else {
-                                    float contrib[VEC];
-#pragma unroll
-                                    for (int e = 0; e < VEC; ++e) contrib[e] = w * go[e];
-                                    red_add_vec<TG, VEC>(
-                                        reinterpret_cast<TG*>(
-                                            glane + static_cast<size_t>(rec[u].x) * 16),
-                                        contrib);
+                                    global_red(u, w);
                                 }
                             }
+                        }
+                    };
+
+                    // which form a trip takes: votes over its slots
+                    auto classify = [&](int base, int nrow, int& kind, bool& precise) {
+                        uint32_t any_res = 0, any_glob = 0, any_prec = 0;
+                        for (int u = 0; u < nrow; ++u) {
+                            const int slot = base + u * RPI + g;
+                            if (slot < slot_end) {
+                                const uint32_t a = s_sa[slot];
+                                const bool ex = s_rec[slot].x != kNoRow;
+                                any_res |= (a & ~15u);
+                                any_glob |= (ex && (a & ~15u) == 0u) ? 1u : 0u;
+                                any_prec |= ex ? (a & 1u) : 0u;
+                            }
+                        }
+                        const bool r = __any_sync(0xffffffffu, any_res != 0u);
+                        const bool gl = __any_sync(0xffffffffu, any_glob != 0u);
+                        precise = F32 && __any_sync(0xffffffffu, any_prec != 0u);
+                        kind = r ? (gl ? 2 : 1) : 0;
+                    };
+                    using std::integral_constant;
+                    using std::false_type;
+                    using std::true_type;
+                    auto run = [&](int base, auto unroll_tag, auto guarded_tag) {
+                        constexpr int U = decltype(unroll_tag)::value;
+                        int kind;
+                        bool precise;
+                        classify(base, U, kind, precise);
+                        if constexpr (decltype(guarded_tag)::value) {
+                            // the odd trip at a task's end: one general form per precision
+                            if (precise) {
+                                if constexpr (F32)
+                                    trip(base, unroll_tag, integral_constant<int, 2>{},
+                                         true_type{}, true_type{});
+                            } else {
+                                trip(base, unroll_tag, integral_constant<int, 2>{}, false_type{},
+                                     true_type{});
+                            }
+                        } else if (precise) {
+                            if constexpr (F32) {
+                                if (kind == 0)
+                                    trip(base, unroll_tag, integral_constant<int, 0>{},
+                                         true_type{}, false_type{});
+                                else if (kind == 1)
+                                    trip(base, unroll_tag, integral_constant<int, 1>{},
+                                         true_type{}, false_type{});
+                                else
+                                    trip(base, unroll_tag, integral_constant<int, 2>{},
+                                         true_type{}, false_type{});
+                            }
+                        } else {
+                            if (kind == 0)
+                                trip(base, unroll_tag, integral_constant<int, 0>{}, false_type{},
+                                     false_type{});
+                            else if (kind == 1)
+                                trip(base, unroll_tag, integral_constant<int, 1>{}, false_type{},
+                                     false_type{});
+                            else
+                                trip(base, unroll_tag, integral_constant<int, 2>{}, false_type{},
+                                     false_type{});
                         }
                     };
 
                     int base = slot_begin;
 #pragma unroll 1
                     for (; base + UBIG * RPI <= slot_end; base += UBIG * RPI)
-                        trip(base, std::integral_constant<int, UBIG>{});
+                        run(base, integral_constant<int, UBIG>{}, false_type{});
 #pragma unroll 1
                     for (; base < slot_end; base += USMALL * RPI)
-                        trip(base, std::integral_constant<int, USMALL>{});
+                        run(base, integral_constant<int, USMALL>{}, true_type{});
                 }
                 __syncwarp();
 
@@ -557,8 +671,9 @@ cudaError_t launch_backward_resident(const Params& p_in, int dtype, int acc_f32,
     rp.warp_off = rp.lv_off + ((static_cast<uint32_t>(p.L) * sizeof(ResLevel) + 127u) & ~127u);
     rp.warp_bytes =
         (res_bwd_warp_bytes(p.stage, spi, p.tasks_per_item, p.D, e) + 127u) & ~127u;
-    rp.map_off = rp.warp_off + kResBwdWarps * rp.warp_bytes;
     rp.map_row_bytes = static_cast<uint32_t>(p.D) * 4u;
+    rp.trash_off = rp.warp_off + kResBwdWarps * rp.warp_bytes;
+    rp.map_off = rp.trash_off + ((rp.map_row_bytes + 127u) & ~127u);
     if (rp.map_off + rp.map_row_bytes > static_cast<uint32_t>(kResMaxSmem))
         return cudaErrorInvalidConfiguration;
     uint32_t cap = (static_cast<uint32_t>(kResMaxSmem) - rp.map_off) & ~15u;

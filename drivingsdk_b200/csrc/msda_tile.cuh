@@ -292,6 +292,7 @@ __device__ __forceinline__ bool phase1(const Params& p, const LaneLevels& lv, in
             sample_setup_nearest(lx, ly, a, lv.w(c), lv.h(c), row_base,
                                  static_cast<uint32_t>(p.H), p.row_units, rec01, geom);
         }
+        debug_check_rows(p, rec01, rec23);
     }
     if constexpr (CPS == 4) {
         uint4* dst = reinterpret_cast<uint4*>(s_slot) + 2 * lane;

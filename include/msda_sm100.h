@@ -205,7 +205,10 @@ size_t msda_sm100_backward_bytes(int B, int K, int H, int D, int L, int Q, int P
  * location/weight tile did not arrive within the polling limit and the kernel
  * fell back to direct loads (results are still correct). Bit 1 (value 2): a
  * pipeline barrier of the tensor-core matrix product (conv_ops_sm100.h) timed
- * out and the CTA stopped early (that call's results are undefined).
+ * out and the CTA stopped early (that call's results are undefined). Bit 2 (value 4): the
+ * backward kernel found the level table (device memory) inconsistent with K and did nothing.
+ * Bit 3 (value 8): a shared-memory accumulate gave up after its retry limit (not expected).
+ * Bit 4 (value 16): debug-bounds build only, see msda_sm100_debug_bounds().
  * Synchronises the device. clear != 0 resets it. Returns the status word
  * (>= 0) or a negative msda_status. */
 int msda_sm100_device_status(int clear);
@@ -268,6 +271,13 @@ const char* msda_sm100_strerror(int status);
 int msda_sm100_last_cuda_error(void);
 /* ABI version of this header: bumps on any signature change. */
 int msda_sm100_abi_version(void);
+/* 1 when this build of the library was compiled with -DMSDA_DEBUG_BOUNDS: the MSDA and
+ * geometric-kernel-attention kernels then check every row offset they compute against the
+ * extent of value / grad_value (and every shared-memory accumulator address against its
+ * area) before using it; a violation sets bit 4 (value 16) of the device status word and the
+ * access is skipped. The reference has no such switch; it flags the same offset arithmetic
+ * as hazardous (kernels/multi_scale_deformable_attn/op_kernel/msda.h:428). */
+int msda_sm100_debug_bounds(void);
 
 #ifdef __cplusplus
 }

@@ -46,10 +46,12 @@ def run_python_api(dev):
     return out.detach(), value.grad, loc.grad, attn.grad
 
 
-def run_c_abi(dev, dtype, workspace=True, host_levels=False):
-    """Forward + backward through the C ABI with raw device pointers."""
+def run_c_abi(dev, dtype, workspace=True, host_levels=False, lib=None):
+    """Forward + backward through the C ABI with raw device pointers (``lib``: which build of
+    the library, default the normal one)."""
     from drivingsdk_b200 import capi
-    lib = capi.load()
+    if lib is None:
+        lib = capi.load()
     value, loc, attn, go = dev["value"], dev["loc"], dev["attn"], dev["grad_out"]
     B, K, H, D = value.shape
     _, Q, _, L, P, _ = loc.shape
