@@ -422,13 +422,8 @@ TRAFFIC_BYTES = {
 
 
 def backward_kernel_name(lib, capi, D, dtype_size):
-    """Name of the kernel msda_sm100_backward_ws launches for rows of D elements: the
-    resident-level kernel on the 16-byte vector path (rows of 16 * 2^k <= 512 bytes) unless
-    it is switched off, else the all-through-L2 kernel."""
-    row = D * dtype_size
-    vector = row % 16 == 0 and (row // 16) & (row // 16 - 1) == 0 and row <= 512
-    resident = lib.msda_sm100_tune(capi.TUNE_RESIDENT, -1) != 0
-    return "msda_bwd_res_kernel" if (vector and resident) else "msda_bwd_kernel"
+    """Name of the kernel msda_sm100_backward_ws launches (one template, msda_bwd_kernel)."""
+    return "msda_bwd_kernel"
 
 
 def run_planned_splits(lib, dist, dev, rank, world, w, dtype, replica_ms_per_step, barrier):

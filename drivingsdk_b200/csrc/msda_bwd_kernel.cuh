@@ -41,9 +41,13 @@ using DotT = typename std::conditional<sizeof(T) == 4, double, float>::type;
 // and are then multiplied by W * attn (up to ~200), which turns the fp32 rounding of the
 // S_c themselves into errors beyond 1e-4 on wide levels (measured on 200-pixel-wide levels
 // with N(0,1) values: fp32 dot products miss rtol = atol = 1e-4 on a few samples per million,
-// fp32 partial sums added in double still on one). So for fp32 tensors the dot products are
-// accumulated in double from the first product on (phase 2) and stay double through here.
-// 16-bit tensors (tolerance 1e-2) keep fp32 arithmetic.
+// fp32 partial sums added in double still on one). So for fp32 tensors the partial sums are
+// doubles from phase 2 on: samples whose amplification max(W, H) * |attention| reaches
+// Params::precise_amp accumulate in double from the first product on (phase 2 takes that
+// form for the trips they are in; fp32 -> fp64 conversions run at 16 per clock per SM, so
+// doing it for every sample costs a quarter more time), the others sum a lane's four to
+// eight products in fp32 and widen the result. 16-bit tensors (tolerance 1e-2) keep fp32
+// arithmetic throughout.
 __device__ __forceinline__ float dot_fma(float v, float g, float acc) { return fmaf(v, g, acc); }
 __device__ __forceinline__ double dot_fma(float v, double g, double acc) {
     return fma(static_cast<double>(v), g, acc);
@@ -89,6 +93,8 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
     constexpr int VEC = SCALAR ? 1 : Elem<T>::kVec;
     constexpr int RPI = 32 / LPR;
     using Dot = DotT<T>;
+    // fp32 bilinear operator: dot products may need double precision (see sample_grad)
+    constexpr bool WIDE = sizeof(T) == 4 && CPS == 4;
     constexpr int PART_MAX = (sizeof(T) == 4) ? kPartMaxF64 : kPartMax;
     constexpr int PART = (LPR < PART_MAX) ? LPR : PART_MAX;  // partials per slot
     constexpr int SSTRIDE = CPS * PART + 1;                    // per-sample stride (bank spread)
@@ -106,6 +112,7 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
     // channels — it only needs grad_out for those channels (gred below).
     constexpr bool SPLIT_RED = !SCALAR && sizeof(T) == 2 && sizeof(TG) == 4;
 
+    if (!device_level_table_ok(p)) return;
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -172,6 +179,14 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
             const bool active =
                 phase1<T, CPS, FUSED>(p, lv, chunk, lane, item, ntask_here, sloc, sattn, s_slot,
                                       geom, gi);
+            // which samples (bit = lane) want their dot products in double: the location
+            // gradient multiplies them by W * attention (H * attention)
+            uint32_t m_precise = 0u;
+            if constexpr (WIDE) {
+                m_precise = __ballot_sync(
+                    0xffffffffu, active && geom.valid &&
+                                     fmaxf(geom.wf, geom.hf) * fabsf(geom.a) >= p.precise_amp);
+            }
             __syncwarp();
 
             // ---- phase 2: lane = (row slot, piece of row) -----------------------
@@ -200,12 +215,6 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                         go[k][0] = (c < D) ? Elem<T>::to_f(gout[obase + c]) : 0.f;
                     }
                 }
-                // the same piece in the type of the dot products (converted once per task)
-                Dot god[NV][VEC];
-#pragma unroll
-                for (int k = 0; k < NV; ++k)
-#pragma unroll
-                    for (int e = 0; e < VEC; ++e) god[k][e] = static_cast<Dot>(go[k][e]);
                 float gred[2][4];
                 if constexpr (SPLIT_RED) {
 #pragma unroll
@@ -224,12 +233,17 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                     }
                 }
 
-                auto scatter_gather = [&](int base, auto unroll_tag, auto guarded_tag) {
+                auto scatter_gather = [&](int base, auto unroll_tag, auto guarded_tag,
+                                          auto precise_tag) {
                     constexpr int U = decltype(unroll_tag)::value;   // rows in flight per lane
                     constexpr bool GUARDED = decltype(guarded_tag)::value;
+                    // PRECISE: the trip's dot products are accumulated in double from the first
+                    // product on; otherwise in the lane's fp32 registers, widened afterwards
+                    constexpr bool PRECISE = decltype(precise_tag)::value;
+                    using Part = typename std::conditional<PRECISE, double, float>::type;
                     const uint2* sp = s_slot + base + g;
                     uint2 rec[U];
-                    Dot part[U];
+                    Part part[U];
 #pragma unroll
                     for (int u = 0; u < U; ++u) {
                         rec[u] = sp[u * RPI];
@@ -278,7 +292,7 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                                     unpack16<T>(raw[u][k], f);
 #pragma unroll
                                     for (int e = 0; e < VEC; ++e)
-                                        part[u] = dot_fma(f[e], god[k][e], part[u]);
+                                        part[u] = dot_fma(f[e], static_cast<Part>(go[k][e]), part[u]);
                                 }
                             }
                         }
@@ -293,7 +307,7 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                                     const size_t idx = static_cast<size_t>(rec[u].x) + c;
                                     const float v = Elem<T>::to_f(__ldg(value + idx));
                                     red_add_scalar(gval + idx, w * go[k][0]);
-                                    part[u] = dot_fma(v, god[k][0], part[u]);
+                                    part[u] = dot_fma(v, static_cast<Part>(go[k][0]), part[u]);
                                 }
                             }
                         }
@@ -306,18 +320,36 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                             part[u] += __shfl_xor_sync(0xffffffffu, part[u], off);
                         const int slot = base + u * RPI + g;
                         if ((!GUARDED || slot < slot_end) && j < PART) {
-                            s_part[(slot / CPS) * SSTRIDE + (slot % CPS) * PART + j] = part[u];
+                            s_part[(slot / CPS) * SSTRIDE + (slot % CPS) * PART + j] =
+                                static_cast<Dot>(part[u]);
                         }
                     }
                 };
 
+                // a trip takes the double-precision form when one of its samples asked for it
+                auto trip = [&](int base, auto guarded_tag) {
+                    bool precise = false;
+                    if constexpr (WIDE) {
+                        const int s0 = base / CPS;
+                        const int s1 = min(32, (base + STEP + CPS - 1) / CPS);
+                        const uint32_t bits =
+                            (s1 - s0 >= 32 ? 0xffffffffu : ((1u << (s1 - s0)) - 1u)) << s0;
+                        precise = (m_precise & bits) != 0u;
+                    }
+                    if (precise) {
+                        if constexpr (WIDE)
+                            scatter_gather(base, std::integral_constant<int, UNROLL>{}, guarded_tag,
+                                           std::true_type{});
+                    } else {
+                        scatter_gather(base, std::integral_constant<int, UNROLL>{}, guarded_tag,
+                                       std::false_type{});
+                    }
+                };
                 int base = slot_begin;
 #pragma unroll 1
-                for (; base < unguarded_end; base += STEP)
-                    scatter_gather(base, std::integral_constant<int, UNROLL>{}, std::false_type{});
+                for (; base < unguarded_end; base += STEP) trip(base, std::false_type{});
 #pragma unroll 1
-                for (; base < slot_end; base += STEP)
-                    scatter_gather(base, std::integral_constant<int, UNROLL>{}, std::true_type{});
+                for (; base < slot_end; base += STEP) trip(base, std::true_type{});
             }
             __syncwarp();
 

@@ -25,9 +25,8 @@ std::atomic<int> g_tune_interleave{1};
 std::atomic<int> g_tune_cps_fwd{0};
 std::atomic<int> g_tune_cps_bwd{0};
 std::atomic<int> g_tune_spin{msda::kSpinLimit};
-std::atomic<int> g_tune_resident{1};
-std::atomic<int> g_tune_resident_bytes{0x7fffffff};
 std::atomic<int> g_tune_precise_amp{8};
+std::atomic<int> g_tune_debug_rows{0};
 std::atomic<long long> g_launches{0};
 thread_local int t_last_cuda_error = 0;
 thread_local cudaEvent_t t_prof[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -121,6 +120,11 @@ int set_row_units(Params& p, const RowPlan& rp, int dtype) {
     if (rows * units >= 0xffffffffull) return MSDA_ERR_LIMIT;
     p.row_units = static_cast<uint32_t>(units);
     p.limit_units = static_cast<uint32_t>(rows * units);
+#ifdef MSDA_DEBUG_BOUNDS
+    // test hook of the bounds-checking build: pretend value / grad_value end after this many rows
+    const unsigned long long pretend = static_cast<unsigned long long>(g_tune_debug_rows.load());
+    if (pretend > 0 && pretend < rows) p.limit_units = static_cast<uint32_t>(pretend * units);
+#endif
     return MSDA_OK;
 }
 
@@ -186,6 +190,7 @@ int fill_common(Params& p, const DeviceInfo* dev, const void* value, const int32
                   ? 1
                   : 0;
     p.spin_limit = g_tune_spin.load();
+    p.precise_amp = static_cast<float>(g_tune_precise_amp.load());
     if (!aligned_to(value, e) || !aligned_to(loc, e) || !aligned_to(attn, e)) return MSDA_ERR_ALIGN;
     return MSDA_OK;
 }
@@ -253,11 +258,6 @@ int backward_impl(const void* value, const int32_t* shapes, const int32_t* start
         ce = msda::launch_fused_backward(p, dtype, acc_f32 ? 1 : 0, rp, shape, stream);
     } else if (nearest) {
         ce = msda::launch_gka_backward(p, dtype, acc_f32 ? 1 : 0, rp, shape, stream);
-    } else if (g_tune_resident.load() != 0 && msda::resident_backward_applies(p, rp)) {
-        const int cap = g_tune_resident_bytes.load();
-        const msda::ResTune tune{cap == 0x7fffffff ? -1 : cap,
-                                 static_cast<float>(g_tune_precise_amp.load())};
-        ce = msda::launch_backward_resident(p, dtype, acc_f32 ? 1 : 0, rp, shape, tune, stream);
     } else {
         ce = msda::launch_backward(p, dtype, acc_f32 ? 1 : 0, rp, shape, stream);
     }
@@ -450,9 +450,8 @@ int msda_sm100_tune(int knob, int value) {
         case MSDA_TUNE_CTAS_PER_SM_BWD: target = &g_tune_cps_bwd; break;
         case MSDA_TUNE_INTERLEAVE: target = &g_tune_interleave; break;
         case MSDA_TUNE_SPIN_LIMIT: target = &g_tune_spin; break;
-        case MSDA_TUNE_RESIDENT: target = &g_tune_resident; break;
-        case MSDA_TUNE_RESIDENT_BYTES: target = &g_tune_resident_bytes; break;
         case MSDA_TUNE_PRECISE_AMP: target = &g_tune_precise_amp; break;
+        case MSDA_TUNE_DEBUG_ROW_LIMIT: target = &g_tune_debug_rows; break;
         default: return MSDA_ERR_DIMS;
     }
     if (value < 0) return target->load();

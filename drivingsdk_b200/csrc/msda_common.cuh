@@ -34,6 +34,7 @@ constexpr int kDrainLimit = 1 << 20; // bound on waiting for copies already issu
 
 // Device status bits, sticky until read by msda_sm100_device_status().
 constexpr int kStatusStageTimeout = 1;  // a staged tile never arrived
+constexpr int kStatusBadLevels = 4;     // device-resident level table inconsistent with K: kernel did nothing
 constexpr int kStatusOutOfBounds = 16;  // MSDA_DEBUG_BOUNDS build: a computed row offset fell outside
                                         // value / grad_value; the access was skipped
 
@@ -97,6 +98,8 @@ struct Params {
     int use_table;
     int stage;          // 1: each warp bulk-copies its next item's locations/weights to shared
                         // memory while it works on the current one; 0: direct loads
+    float precise_amp;  // fp32 backward: samples with max(W, H) * |attention| >= this value
+                        // accumulate their dot products in double from the first product on
     int spin_limit;     // polls of a staging barrier before the warp gives up on it (0: every
                         // wait times out at once, which is how the fall-back path is tested)
     long long ntasks;   // B * Q * H

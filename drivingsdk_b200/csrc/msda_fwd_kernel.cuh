@@ -33,6 +33,7 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
     constexpr int STEP = RPI * UNROLL;             // slots per trip of the gather loop
     static_assert(kSlots % STEP == 0 && STEP <= kSlotPad, "slot loop must tile the slots");
 
+    if (!device_level_table_ok(p)) return;
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;

@@ -63,19 +63,6 @@ cudaError_t launch_fused_forward(const Params& p, int dtype, const RowPlan& rp,
 cudaError_t launch_fused_backward(const Params& p, int dtype, int acc_f32, const RowPlan& rp,
                                   const LaunchShape& ls, cudaStream_t stream);
 
-// Resident-level kernels (msda_res_*.cu): the accumulators of a head's small pyramid levels
-// live in shared memory. `max_resident_bytes` < 0 means all the shared memory a CTA can
-// have; smaller values shrink the resident windows (0: everything goes through L2), which is
-// how tests reach the window edges on small problems. `precise_amp`: see ResParams.
-struct ResTune {
-    int max_resident_bytes;
-    float precise_amp;
-};
-bool resident_backward_applies(const Params& p, const RowPlan& rp);
-cudaError_t launch_backward_resident(const Params& p, int dtype, int acc_f32, const RowPlan& rp,
-                                     const LaunchShape& ls, const ResTune& tune,
-                                     cudaStream_t stream);
-
 // Adds to the library-wide kernel launch counter (msda_sm100_launch_count).
 void count_launches(int n);
 

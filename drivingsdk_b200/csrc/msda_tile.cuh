@@ -75,6 +75,23 @@ __device__ __forceinline__ LaneLevels load_lane_levels(const Params& p, int lane
     return lv;
 }
 
+// Level tables passed in device memory cannot be checked by the host without a
+// synchronisation, so every CTA checks them before it touches anything (L <= 64 entries): a
+// size <= 0, a negative start or start + h*w > K sets kStatusBadLevels and makes the kernel
+// return. All threads of the CTA must call it.
+__device__ __forceinline__ bool device_level_table_ok(const Params& p) {
+    if (p.use_table) return true;   // host tables were validated by the entry point
+    bool bad = false;
+    for (int l = threadIdx.x; l < p.L; l += blockDim.x) {
+        const int hh = p.shapes_dev[2 * l], ww = p.shapes_dev[2 * l + 1], ss = p.start_dev[l];
+        bad |= hh <= 0 || ww <= 0 || ss < 0 ||
+               static_cast<long long>(ss) + static_cast<long long>(hh) * ww > p.K;
+    }
+    const bool any = __syncthreads_or(bad ? 1 : 0) != 0;
+    if (any && threadIdx.x == 0) atomicOr(p.status, kStatusBadLevels);
+    return !any;
+}
+
 // The sequence of items one warp walks through: warp w of CTA c takes items c*8 + w, then
 // + gridDim*8, ... (a CTA's eight warps hold eight consecutive tasks, i.e. with eight heads all
 // heads of one query).

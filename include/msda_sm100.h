@@ -205,10 +205,11 @@ size_t msda_sm100_backward_bytes(int B, int K, int H, int D, int L, int Q, int P
  * location/weight tile did not arrive within the polling limit and the kernel
  * fell back to direct loads (results are still correct). Bit 1 (value 2): a
  * pipeline barrier of the tensor-core matrix product (conv_ops_sm100.h) timed
- * out and the CTA stopped early (that call's results are undefined). Bit 2 (value 4): the
- * backward kernel found the level table (device memory) inconsistent with K and did nothing.
- * Bit 3 (value 8): a shared-memory accumulate gave up after its retry limit (not expected).
- * Bit 4 (value 16): debug-bounds build only, see msda_sm100_debug_bounds().
+ * out and the CTA stopped early (that call's results are undefined). Bit 2 (value 4): a
+ * kernel found the level table it was given in DEVICE memory inconsistent with K (a size
+ * <= 0, a negative start, or start + h*w > K) and returned without reading value or writing
+ * any result (tables passed in host memory are checked by the entry point, which returns
+ * MSDA_ERR_DIMS). Bit 4 (value 16): debug-bounds build only, see msda_sm100_debug_bounds().
  * Synchronises the device. clear != 0 resets it. Returns the status word
  * (>= 0) or a negative msda_status. */
 int msda_sm100_device_status(int clear);
@@ -231,27 +232,23 @@ int msda_sm100_device_status(int clear);
  *                            up, sets status bit 0 and carries on with direct loads (default
  *                            262144). 0 makes every wait run out at once: the way to exercise
  *                            that path without any fault; results stay correct.
- *   MSDA_TUNE_RESIDENT       1 = the backward keeps the grad_value accumulators of each head's
- *                            small pyramid levels in shared memory and adds them to global
- *                            memory once per (batch entry, head, query chunk) (default, rows of
- *                            16 * 2^k <= 512 bytes); 0 = every row is reduced in L2
- *   MSDA_TUNE_RESIDENT_BYTES upper limit on the shared memory used for those accumulators
- *                            (default 2147483647 = all a CTA can have; 0 = none). Small values
- *                            make small problems exercise the edges of the resident windows.
  *   MSDA_TUNE_PRECISE_AMP    fp32 tensors: samples with max(W, H) * |attention| >= this value
  *                            accumulate their dot products <value row, grad_out> in double
  *                            from the first product on, the others form the per-lane sums in
  *                            fp32 (default 8; 0 = all samples in double). The location
- *                            gradient multiplies those dot products by W * attention. */
+ *                            gradient multiplies those dot products by W * attention.
+ *   MSDA_TUNE_DEBUG_ROW_LIMIT  bounds-checking build only (see msda_sm100_debug_bounds): when
+ *                            > 0 the checks behave as if value / grad_value had only this many
+ *                            (key, head) rows, so that a test can see them fire on a
+ *                            correct problem. Ignored by the normal build. */
 typedef enum msda_tune {
     MSDA_TUNE_STAGE = 0,
     MSDA_TUNE_CTAS_PER_SM = 1,
     MSDA_TUNE_CTAS_PER_SM_BWD = 2,
     MSDA_TUNE_INTERLEAVE = 3,
     MSDA_TUNE_SPIN_LIMIT = 4,
-    MSDA_TUNE_RESIDENT = 5,
-    MSDA_TUNE_RESIDENT_BYTES = 6,
-    MSDA_TUNE_PRECISE_AMP = 7
+    MSDA_TUNE_PRECISE_AMP = 5,
+    MSDA_TUNE_DEBUG_ROW_LIMIT = 6
 } msda_tune;
 int msda_sm100_tune(int knob, int value);
 

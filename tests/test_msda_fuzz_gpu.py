@@ -48,8 +48,7 @@ def test_random_shapes(index):
 @pytest.mark.parametrize("index", range(36))
 def test_random_shapes_in_the_bounds_checking_build(index):
     """The same seeded shapes through the library compiled with -DMSDA_DEBUG_BOUNDS, where
-    every row offset (and every shared-memory accumulator address) is checked before it is
-    used: results must agree with the oracle and no check may have fired (status 0). This is
+    every row offset is checked before it is used: results must agree with the oracle and no check may have fired (status 0). This is
     what stands in for a memory checker."""
     from drivingsdk_b200 import capi
     dbg = capi.load_debug()
@@ -62,36 +61,32 @@ def test_random_shapes_in_the_bounds_checking_build(index):
     dbg.msda_sm100_device_status(1)
     parity.compare_all(inp, parity.run_c_abi(dev, dtype, host_levels=bool(index % 3 == 0), lib=dbg),
                        dtype)
-    # small resident area: window edges inside the small maps
-    prev = dbg.msda_sm100_tune(capi.TUNE_RESIDENT_BYTES, 4096)
-    try:
-        parity.compare_all(inp, parity.run_c_abi(dev, dtype, lib=dbg), dtype)
-    finally:
-        dbg.msda_sm100_tune(capi.TUNE_RESIDENT_BYTES, prev)
+    parity.compare_all(inp, parity.run_c_abi(dev, dtype, workspace=False, lib=dbg), dtype) \
+        if dtype == torch.float32 else None
     assert dbg.msda_sm100_device_status(1) == 0
 
 
-def test_bounds_checking_build_catches_a_level_that_reaches_past_value():
-    """A level table in device memory whose last level ends past the K rows of value: the
-    bounds-checking build's forward kernel must flag it (status bit 4, value 16) and skip the
-    rows instead of reading them."""
+def test_bounds_checks_fire_when_the_tensor_is_declared_shorter_than_it_is():
+    """The checks of the bounds-checking build must actually fire. Its test hook makes them
+    behave as if value / grad_value ended after 100 (key, head) rows of the toy problem's
+    10880: every row beyond is then "out of bounds" — flagged (status bit 4, value 16) and
+    skipped, never read or added to, in forward and backward."""
     from drivingsdk_b200 import capi
     dbg = capi.load_debug()
     dbg.msda_sm100_device_status(1)
-    w = workloads.Workload("oob", 1, 64, 2, 32, ((6, 6), (3, 3)), 4, (0.0, 1.0), 3)
+    w = workloads.WORKLOADS["toy"].with_queries(64)
     inp = workloads.make_inputs(w, torch.float32)
     dev = parity.to_device(inp, torch.float32)
-    shapes = dev["shapes"].to(torch.int32).contiguous()
-    starts = dev["starts"].to(torch.int32).clone()
-    starts[-1] += 40                      # the 3x3 level now starts 4 rows before the end of value
-    B, K, H, D = dev["value"].shape
-    _, Q, _, L, P, _ = dev["loc"].shape
-    out = torch.empty(B, Q, H * D, device="cuda")
-    rc = dbg.msda_sm100_forward(dev["value"].data_ptr(), shapes.data_ptr(), starts.data_ptr(),
-                                dev["loc"].data_ptr(), dev["attn"].data_ptr(), out.data_ptr(),
-                                B, K, H, D, L, Q, P, capi.F32,
-                                torch.cuda.current_stream().cuda_stream)
-    assert rc == 0
-    status = dbg.msda_sm100_device_status(1)
+    prev = dbg.msda_sm100_tune(capi.TUNE_DEBUG_ROW_LIMIT, 100)
+    try:
+        out, gv, gl, ga = parity.run_c_abi(dev, torch.float32, lib=dbg)
+        status = dbg.msda_sm100_device_status(1)
+    finally:
+        dbg.msda_sm100_tune(capi.TUNE_DEBUG_ROW_LIMIT, prev)
     assert status >= 0 and (status & 16) == 16, status
-    assert torch.isfinite(out).all()
+    assert torch.isfinite(out).all() and torch.isfinite(gv).all()
+    # nothing was added beyond the pretended end of grad_value
+    assert torch.count_nonzero(gv.reshape(-1, gv.shape[-1])[100:]).item() == 0
+    # and with the hook off the same call is clean
+    parity.compare_all(inp, parity.run_c_abi(dev, torch.float32, lib=dbg), torch.float32)
+    assert dbg.msda_sm100_device_status(1) == 0

@@ -339,49 +339,29 @@ def test_staging_wait_that_runs_out_falls_back_to_direct_loads(dtype):
     assert lib.msda_sm100_device_status(1) == 0
 
 
-@pytest.mark.parametrize("cap", [0, 3000, 20000, 70000])
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_resident_windows_of_every_size(cap, dtype):
-    """The backward keeps the accumulators of the small levels in shared memory. Limiting
-    that memory moves the edge of the resident windows through the toy pyramid (nothing
-    resident; the 4x4 level; 4x4 + 8x8 + four pixel rows of 16x16; all but part of 32x32), so
-    samples whose corners straddle a window edge occur; results must not depend on it."""
+@pytest.mark.parametrize("amp", [0, 8, 1000000])
+def test_backward_precision_threshold_does_not_change_results_beyond_tolerance(amp):
+    """fp32 backward: samples above the amplification threshold accumulate their dot products
+    in double. Everything in double (0), the default (8) and nothing in double (a huge
+    threshold) must all meet the tolerance on the toy configuration (its levels are at most
+    32 pixels wide, where fp32 dot products are accurate enough)."""
     from drivingsdk_b200 import capi
     lib = capi.load()
     w = workloads.WORKLOADS["toy"]
-    inp = workloads.make_inputs(w, dtype)
-    dev = parity.to_device(inp, dtype)
-    prev = lib.msda_sm100_tune(capi.TUNE_RESIDENT_BYTES, cap)
-    try:
-        parity.compare_all(inp, parity.run_c_abi(dev, dtype), dtype)
-        parity.compare_all(inp, parity.run_c_abi(dev, dtype, workspace=False), dtype) \
-            if dtype == torch.float32 else None
-    finally:
-        lib.msda_sm100_tune(capi.TUNE_RESIDENT_BYTES, prev)
-    assert lib.msda_sm100_device_status(1) == 0
-
-
-@pytest.mark.parametrize("resident", [0, 1])
-def test_resident_and_l2_backward_agree(resident):
-    """Both routings of the scatter (shared-memory accumulators / reductions in L2 only)
-    against the oracle on a Deformable-DETR-shaped slice."""
-    from drivingsdk_b200 import capi
-    lib = capi.load()
-    w = workloads.WORKLOADS["deformable_detr"].with_batch(1).with_queries(3000)
     inp = workloads.make_inputs(w, torch.float32)
     dev = parity.to_device(inp, torch.float32)
-    prev = lib.msda_sm100_tune(capi.TUNE_RESIDENT, resident)
+    prev = lib.msda_sm100_tune(capi.TUNE_PRECISE_AMP, amp)
     try:
         parity.compare_all(inp, parity.run_c_abi(dev, torch.float32), torch.float32)
     finally:
-        lib.msda_sm100_tune(capi.TUNE_RESIDENT, prev)
+        lib.msda_sm100_tune(capi.TUNE_PRECISE_AMP, prev)
 
 
 def test_bad_level_table_on_the_device_is_reported_not_followed():
     """Level tables passed as device memory cannot be checked by the host without a
-    synchronisation; the backward kernel checks them itself and, when a level would reach
-    past the K rows of value, sets status bit 2 (value 4) and returns without reading or
-    adding anything out of bounds."""
+    synchronisation; the kernels check them themselves and, when a level would reach past
+    the K rows of value, set status bit 2 (value 4) and return without reading or adding
+    anything out of bounds (forward and backward)."""
     from drivingsdk_b200 import capi
     lib = capi.load()
     lib.msda_sm100_device_status(1)
@@ -405,3 +385,11 @@ def test_bad_level_table_on_the_device_is_reported_not_followed():
     status = lib.msda_sm100_device_status(1)
     assert status >= 0 and (status & 4) == 4, status
     assert torch.count_nonzero(gv).item() == 0     # zero-filled, then left alone
+    out = torch.full((B, Q, H * D), 3.0, device="cuda")
+    rc = lib.msda_sm100_forward(dev["value"].data_ptr(), shapes.data_ptr(), starts.data_ptr(),
+                                dev["loc"].data_ptr(), dev["attn"].data_ptr(), out.data_ptr(),
+                                B, K, H, D, L, Q, P, capi.F32,
+                                torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert (lib.msda_sm100_device_status(1) & 4) == 4
+    assert bool((out == 3.0).all())                # nothing was written
