@@ -380,6 +380,22 @@ def run_native(args):
     fwd_gbs = fb / (fwd_ms * 1e-3) / 1e9
     step_gbs = (fb + bb) / (ms_per_step * 1e-3) / 1e9
     bwd_kernel = backward_kernel_name(lib, capi, w.D, esize)
+    # what actually bounds the two kernels: rows moved between L2 and the SMs, against the
+    # rates the library's probe measures on this device in this run
+    rows = count_corner_rows(sets[0]["loc"], shapes_i32)
+    ceil = measured_row_ceilings(lib, capi, dev, w_local.D, esize)
+    fwd_rows_s = rows / (fwd_ms * 1e-3)
+    bwd_rows_s = rows / (bwd_ms * 1e-3)
+    row_roofline = {
+        "rows_per_launch": rows, "measured": ceil,
+        "forward": {"bound": "16-byte vector loads of gathered value rows (L2 -> SM)",
+                    "achieved_rows_per_s": fwd_rows_s,
+                    "frac": fwd_rows_s / ceil["gather_rows_per_s"]},
+        "backward": {"bound": "vector reductions of grad_value rows in L2 (it also gathers "
+                              "as many value rows)",
+                     "achieved_rows_per_s": bwd_rows_s,
+                     "frac": bwd_rows_s / ceil["red_rows_per_s"]},
+    }
     roofline = {
         "bound": "hbm", "kernel": bwd_kernel, "achieved": bwd_gbs, "peak": peak,
         "unit": "GB/s", "frac": bwd_gbs / peak,
@@ -388,6 +404,7 @@ def run_native(args):
         "forward": {"kernel": "msda_fwd_kernel", "achieved": fwd_gbs, "frac": fwd_gbs / peak,
                     "algorithmic_bytes": fb, "kernel_ms": fwd_ms},
         "step": {"achieved": step_gbs, "frac": step_gbs / peak, "algorithmic_bytes": fb + bb},
+        "rows": row_roofline,
     }
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K_steps,
@@ -419,6 +436,40 @@ def run_native(args):
 TRAFFIC_BYTES = {
     ("msda_bwd_kernel", "bevformer_sca", "float32"): 626_346_752,
 }
+
+
+def count_corner_rows(loc, shapes):
+    """How many value rows one forward gathers (and one backward gathers and reduces): the
+    bilinear corners that exist, over all samples (kernels/multi_scale_deformable_attn/
+    op_kernel/msda.h:367-390 for which samples count; a corner outside the level is skipped).
+    loc [B,Q,H,L,P,2] on the device, shapes [L,2] (H, W)."""
+    import torch
+    hw = shapes.to(loc.device).to(torch.float32)
+    Hl = hw[:, 0].view(1, 1, 1, -1, 1)
+    Wl = hw[:, 1].view(1, 1, 1, -1, 1)
+    x = loc[..., 0].float() * Wl - 0.5
+    y = loc[..., 1].float() * Hl - 0.5
+    valid = (x > -1) & (y > -1) & (x < Wl) & (y < Hl)
+    x0, y0 = torch.floor(x), torch.floor(y)
+    cx = (x0 >= 0).int() + (x0 + 1 <= Wl - 1).int()
+    cy = (y0 >= 0).int() + (y0 + 1 <= Hl - 1).int()
+    return int((valid.int() * cx * cy).sum().item())
+
+
+def measured_row_ceilings(lib, capi, dev, D, esize):
+    """L2 <-> SM row rates measured on this device right now by the library's own probe:
+    (gathers of value rows, reductions of fp32 accumulation rows) in rows per second."""
+    import ctypes
+    import torch
+    pow2 = lambda b: max(64, min(512, 1 << (max(1, b) - 1).bit_length()))
+    g_row, r_row = pow2(D * esize), pow2(D * 4)
+    buf = torch.empty(32 << 20, device=dev, dtype=torch.uint8)
+    g, r = ctypes.c_double(0), ctypes.c_double(0)
+    capi.check(lib.msda_sm100_probe_row_rates(buf.data_ptr(), buf.numel(), g_row, r_row,
+                                              ctypes.byref(g), ctypes.byref(r),
+                                              torch.cuda.current_stream().cuda_stream), "probe")
+    return {"gather_row_bytes": g_row, "gather_rows_per_s": g.value,
+            "red_row_bytes": r_row, "red_rows_per_s": r.value}
 
 
 def backward_kernel_name(lib, capi, D, dtype_size):

@@ -25,7 +25,7 @@ EXT = os.path.join(PKG, "_C.so")
 
 CUDA_SOURCES = ["msda_capi.cu", "msda_fwd_sm100.cu", "msda_bwd_sm100.cu", "gka_fwd_sm100.cu",
                 "gka_bwd_sm100.cu", "msda_fused_fwd_sm100.cu", "msda_fused_bwd_sm100.cu", "da_sm100.cu",
-                "msda_static_scratch.cu", "resnet_ops_sm100.cu", "dcn_sm100.cu",
+                "msda_static_scratch.cu", "hw_probe_sm100.cu", "resnet_ops_sm100.cu", "dcn_sm100.cu",
                 "gemm_simt_sm100.cu", "gemm_tc_sm100.cu"]
 CUDA_HEADERS = ["msda_common.cuh", "msda_tile.cuh", "msda_launch.h", "msda_fwd_kernel.cuh",
                 "msda_bwd_kernel.cuh", "gemm_sm100.h"]

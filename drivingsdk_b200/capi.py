@@ -53,6 +53,8 @@ SIGNATURES = {
                                ctypes.c_longlong, _vp, _i, _i, _i, _i, _vp]),
     "msda_sm100_forward_bytes": (_sz, _DIMS7 + [_i]),
     "msda_sm100_backward_bytes": (_sz, _DIMS7 + [_i]),
+    "msda_sm100_probe_row_rates": (_i, [_vp, _sz, _i, _i, ctypes.POINTER(ctypes.c_double),
+                                        ctypes.POINTER(ctypes.c_double), _vp]),
     "msda_sm100_device_status": (_i, [_i]),
     "msda_sm100_tune": (_i, [_i, _i]),
     "msda_sm100_profile_events": (None, [_vp, _vp, _vp, _vp]),

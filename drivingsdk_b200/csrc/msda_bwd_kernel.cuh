@@ -10,15 +10,11 @@
 
 namespace msda {
 
-// Partial dot products <value row, grad_out> kept per (sample, corner): 8 floats for 16-bit
-// tensors, 4 doubles for fp32 tensors (see sample_grad for why those are doubles).
+// Partial dot products <value row, grad_out> kept per (sample, corner): room for 8 floats; a
+// trip that runs in double (see sample_grad) leaves 4 doubles in the same 32 bytes.
 constexpr int kPartMax = 8;
 constexpr int kPartMaxF64 = 4;
-constexpr int kPartBytes = ((kChunk * (4 * kPartMaxF64 + 1) * 8 + 15) / 16) * 16;
-static_assert(kPartBytes >= kChunk * (4 * kPartMax + 1) * 4, "partials of either type must fit");
-// Type of the dot products: double for fp32 tensors, float for 16-bit tensors.
-template <typename T>
-using DotT = typename std::conditional<sizeof(T) == 4, double, float>::type;
+constexpr int kPartBytes = ((kChunk * (4 * kPartMax + 2) * 4 + 15) / 16) * 16;
 
 // Compile-time tuning, chosen by measurement on B200: three resident CTAs per SM (80
 // registers per thread) and four rows in flight per lane; the kernel is bound by the rate
@@ -56,16 +52,32 @@ __device__ __forceinline__ double dot_fma(float v, double g, double acc) {
 struct SampleGrad {
     float attn, x, y;
 };
-template <typename T, int CPS, int PART>
-__device__ __forceinline__ SampleGrad sample_grad(const DotT<T>* part, const SampleGeom& geom) {
-    using Acc = DotT<T>;
+// `part`: this sample's partials, CSTR floats per corner: PART_F fp32 partials, or — when the
+// sample's trip ran in double (`wide`) — PART_D doubles in the same place. Acc: the type the
+// gradients are formed in (double for the fp32 bilinear operator, else float).
+template <typename Acc, int CPS, int PART_F, int PART_D, int CSTR>
+__device__ __forceinline__ SampleGrad sample_grad(const float* part, const SampleGeom& geom,
+                                                  bool wide) {
     Acc S[CPS];
+    if (sizeof(Acc) == 8 && wide) {
 #pragma unroll
-    for (int c = 0; c < CPS; ++c) {
-        Acc acc = 0;
+        for (int c = 0; c < CPS; ++c) {
+            double acc = 0.0;
 #pragma unroll
-        for (int q = 0; q < PART; ++q) acc += part[c * PART + q];
-        S[c] = acc;
+            for (int q = 0; q < PART_D; ++q)
+                acc += *reinterpret_cast<const double*>(part + c * CSTR + 2 * q);
+            S[c] = static_cast<Acc>(acc);
+        }
+    } else {
+        // fp32 partials: summed in fp32 (as accurate as the partials themselves) and widened
+        // once per corner — conversions to double are a scarce resource (16 per clock per SM)
+#pragma unroll
+        for (int c = 0; c < CPS; ++c) {
+            float acc = 0.f;
+#pragma unroll
+            for (int q = 0; q < PART_F; ++q) acc += part[c * CSTR + q];
+            S[c] = static_cast<Acc>(acc);
+        }
     }
     SampleGrad r{0.f, 0.f, 0.f};
     if constexpr (CPS == 4) {
@@ -92,12 +104,14 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
     constexpr bool FUSED = MODE == kModeFused;
     constexpr int VEC = SCALAR ? 1 : Elem<T>::kVec;
     constexpr int RPI = 32 / LPR;
-    using Dot = DotT<T>;
     // fp32 bilinear operator: dot products may need double precision (see sample_grad)
     constexpr bool WIDE = sizeof(T) == 4 && CPS == 4;
-    constexpr int PART_MAX = (sizeof(T) == 4) ? kPartMaxF64 : kPartMax;
-    constexpr int PART = (LPR < PART_MAX) ? LPR : PART_MAX;  // partials per slot
-    constexpr int SSTRIDE = CPS * PART + 1;                    // per-sample stride (bank spread)
+    using Acc = typename std::conditional<WIDE, double, float>::type;
+    constexpr int PART_F = (LPR < kPartMax) ? LPR : kPartMax;        // fp32 partials per slot
+    constexpr int PART_D = (LPR < kPartMaxF64) ? LPR : kPartMaxF64;  // double partials per slot
+    constexpr int CSTR = WIDE ? ((PART_F > 2 * PART_D) ? PART_F : 2 * PART_D) : PART_F;
+    // per-sample stride in floats: odd spreads the banks; even where doubles are stored
+    constexpr int SSTRIDE = CPS * CSTR + (WIDE ? 2 : 1);
     // 16-bit rows of <= 128 bytes: an instruction already covers >= 4 rows, and the fp32
     // accumulation path carries a second copy of grad_out; two instructions in flight keep
     // the kernel free of register spills (which cost ~15 % when present).
@@ -121,7 +135,7 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
 
     unsigned char* wb = smem + static_cast<size_t>(warp) * p.warp_smem;
     uint2* s_slot = reinterpret_cast<uint2*>(wb);
-    Dot* s_part = reinterpret_cast<Dot*>(wb + kSlotBytes);
+    float* s_part = reinterpret_cast<float*>(wb + kSlotBytes);
     init_unused_slots<CPS>(s_slot, lane);
     WarpStage<T> st = warp_stage_init<T>(p, wb + kSlotBytes + kPartBytes, lane);
 
@@ -187,6 +201,19 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                     0xffffffffu, active && geom.valid &&
                                      fmaxf(geom.wf, geom.hf) * fabsf(geom.a) >= p.precise_amp);
             }
+            // did the trip that holds this lane's sample run in double? (same rule as `trip`
+            // below: trips start at the task's first slot and cover STEP slots)
+            auto lane_trip_wide = [&]() -> bool {
+                if constexpr (!WIDE) return false;   // fp32 partials
+                const int slot = lane * CPS;
+                const int begin = (TPC == 1) ? 0 : (slot / (CPS * LP)) * (CPS * LP);
+                const int base = begin + ((slot - begin) / STEP) * STEP;
+                const int s0 = base / CPS;
+                const int s1 = min(32, (base + STEP + CPS - 1) / CPS);
+                const uint32_t bits =
+                    (s1 - s0 >= 32 ? 0xffffffffu : ((1u << (s1 - s0)) - 1u)) << s0;
+                return (m_precise & bits) != 0u;
+            };
             __syncwarp();
 
             // ---- phase 2: lane = (row slot, piece of row) -----------------------
@@ -313,6 +340,7 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                         }
                     }
                     // fold to PART partials per slot, then park them in shared memory
+                    constexpr int PART = PRECISE ? PART_D : PART_F;
 #pragma unroll
                     for (int u = 0; u < U; ++u) {
 #pragma unroll
@@ -320,8 +348,12 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                             part[u] += __shfl_xor_sync(0xffffffffu, part[u], off);
                         const int slot = base + u * RPI + g;
                         if ((!GUARDED || slot < slot_end) && j < PART) {
-                            s_part[(slot / CPS) * SSTRIDE + (slot % CPS) * PART + j] =
-                                static_cast<Dot>(part[u]);
+                            float* dst = s_part + (slot / CPS) * SSTRIDE + (slot % CPS) * CSTR;
+                            if constexpr (PRECISE) {
+                                reinterpret_cast<double*>(dst)[j] = part[u];
+                            } else {
+                                dst[j] = part[u];
+                            }
                         }
                     }
                 };
@@ -356,7 +388,8 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
             // ---- phase 3: lane = sample -----------------------------------------
             if constexpr (!FUSED) {
                 if (active) {
-                    const SampleGrad sg = sample_grad<T, CPS, PART>(s_part + lane * SSTRIDE, geom);
+                    const SampleGrad sg = sample_grad<Acc, CPS, PART_F, PART_D, CSTR>(
+                        s_part + lane * SSTRIDE, geom, lane_trip_wide());
                     if constexpr (CPS == 4) {
                         store_pair(static_cast<T*>(p.grad_loc) + 2 * gi, sg.x, sg.y);
                         static_cast<T*>(p.grad_attn)[gi] = Elem<T>::from_f(sg.attn);
@@ -371,7 +404,8 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                 //   location = reference point + offset / (W, H)   and   weight = softmax(logits).
                 float g_attn = 0.f, g_x = 0.f, g_y = 0.f;
                 if (active && geom.valid) {
-                    const SampleGrad sg = sample_grad<T, 4, PART>(s_part + lane * SSTRIDE, geom);
+                    const SampleGrad sg = sample_grad<Acc, 4, PART_F, PART_D, CSTR>(
+                        s_part + lane * SSTRIDE, geom, lane_trip_wide());
                     g_attn = sg.attn;
                     g_x = sg.x;
                     g_y = sg.y;

@@ -201,6 +201,17 @@ int da_sm100_last_cuda_error(void);
 size_t msda_sm100_forward_bytes(int B, int K, int H, int D, int L, int Q, int P, int dtype);
 size_t msda_sm100_backward_bytes(int B, int K, int H, int D, int L, int Q, int P, int dtype);
 
+/* Measured ceilings for the operations that bound these kernels (no counterpart in the
+ * reference). Times, on the current device, (a) gathers of random rows of gather_row_bytes
+ * with 16-byte vector loads and (b) red.global.add.v4.f32 reductions of random rows of
+ * red_row_bytes (each 64, 128, 256 or 512) over `buffer` (caller-owned device memory, 16-byte
+ * aligned, >= 1 MiB; it is zero-filled and left zero; a size that fits in L2, e.g. 32 MiB,
+ * gives the L2 <-> SM rates the MSDA kernels run against) and returns rows per second.
+ * Launches a handful of short kernels on `stream` and waits for them. */
+int msda_sm100_probe_row_rates(void* buffer, size_t buffer_bytes, int gather_row_bytes,
+                               int red_row_bytes, double* gather_rows_per_s,
+                               double* red_rows_per_s, void* stream);
+
 /* Sticky device-side status of the current device. Bit 0 (value 1): a staged
  * location/weight tile did not arrive within the polling limit and the kernel
  * fell back to direct loads (results are still correct). Bit 1 (value 2): a
