@@ -479,7 +479,7 @@ def backward_kernel_name(lib, capi, D, dtype_size):
 
 def run_planned_splits(lib, dist, dev, rank, world, w, dtype, replica_ms_per_step, barrier):
     """N > 1, after the replica timing: ONE batch spread over the ranks by the planner
-    (drivingsdk_b200.dist.plan with a cost model built from the step time just measured), for
+    (drivingsdk_b200.dist.plan with a cost model built from one entry's time measured here), for
     the headline workload ("strong") and for the large-head-dim shape with 8 batch entries
     ("config5a", bf16) and with one entry whose queries are split over all ranks and whose
     grad_value is summed with NCCL ("config5b", bf16). Every rank draws only the entries it
@@ -494,10 +494,37 @@ def run_planned_splits(lib, dist, dev, rank, world, w, dtype, replica_ms_per_ste
     def one(label, wl, dt, force_kind=None):
         esize = 4 if dt == torch.float32 else 2
         code = capi.dtype_code(dt)
-        # per-entry cost: scale the measured replica step by the algorithmic bytes
-        fb0, bb0 = workloads.compulsory_bytes(w.with_batch(1), 4 if dtype == torch.float32 else 2)
-        fb1, bb1 = workloads.compulsory_bytes(wl.with_batch(1), esize)
-        entry_s = (replica_ms_per_step * 1e-3 / w.B) * (fb1 + bb1) / (fb0 + bb0)
+        # per-entry cost for the planner: ONE batch entry of this workload, forward + backward,
+        # timed here on every rank (median of 3 after a warm-up; the slowest rank counts)
+        e1 = workloads.make_inputs(wl.with_batch(1), dt, seed_offset=49)
+        dv = {k: e1[k].to(dt).to(dev).contiguous() for k in ("value", "loc", "attn", "grad_out")}
+        sh1 = e1["shapes"].to(torch.int32).to(dev)
+        st1 = e1["starts"].to(torch.int32).to(dev)
+        d1 = (1, wl.K, wl.H, wl.D, wl.L, wl.Q, wl.P)
+        o1 = torch.empty(1, wl.Q, wl.H * wl.D, device=dev, dtype=dt)
+        g1 = [torch.empty_like(dv[k]) for k in ("value", "loc", "attn")]
+        wsb = lib.msda_sm100_backward_workspace_bytes(1, wl.K, wl.H, wl.D, code)
+        ws1 = torch.empty(max(wsb, 16), device=dev, dtype=torch.uint8)
+        ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        single = []
+        for it in range(4):
+            ea.record(stream)
+            capi.check(lib.msda_sm100_forward(
+                dv["value"].data_ptr(), sh1.data_ptr(), st1.data_ptr(), dv["loc"].data_ptr(),
+                dv["attn"].data_ptr(), o1.data_ptr(), *d1, code, stream.cuda_stream), "forward")
+            capi.check(lib.msda_sm100_backward_ws(
+                dv["value"].data_ptr(), sh1.data_ptr(), st1.data_ptr(), dv["loc"].data_ptr(),
+                dv["attn"].data_ptr(), dv["grad_out"].data_ptr(), g1[0].data_ptr(),
+                g1[1].data_ptr(), g1[2].data_ptr(), ws1.data_ptr(), wsb, *d1, code,
+                stream.cuda_stream), "backward")
+            eb.record(stream)
+            eb.synchronize()
+            if it > 0:
+                single.append(ea.elapsed_time(eb))
+        tt = torch.tensor([sorted(single)[1]], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        entry_s = float(tt.item()) * 1e-3
+        del dv, o1, g1, ws1
         cost = sdist.CostModel(entry_s, float(wl.K * wl.H * wl.D * esize))
         plan = sdist.plan(wl.B, wl.Q, world, cost=cost)
         if force_kind == "hybrid" and plan.kind != "hybrid":
@@ -568,6 +595,7 @@ def run_planned_splits(lib, dist, dev, rank, world, w, dtype, replica_ms_per_ste
                 "value": wl.B / (step_ms * 1e-3), "unit": UNIT, "scaling": "strong",
                 "predicted_ms": None if plan.predicted_seconds is None
                 else plan.predicted_seconds * 1e3,
+                "one_entry_one_gpu_ms": entry_s * 1e3,
                 "single_gpu_ms": entry_s * wl.B * 1e3,
                 "efficiency_ceiling": plan.efficiency_ceiling()}
 
