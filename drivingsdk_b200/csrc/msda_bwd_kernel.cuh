@@ -269,6 +269,12 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                     // product on; otherwise in the lane's fp32 registers, widened afterwards
                     constexpr bool PRECISE = decltype(precise_tag)::value;
                     using Part = typename std::conditional<PRECISE, double, float>::type;
+                    // grad_out in the type of the products (converted once per trip)
+                    Part gop[NV][VEC];
+#pragma unroll
+                    for (int k = 0; k < NV; ++k)
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) gop[k][e] = static_cast<Part>(go[k][e]);
                     const uint2* sp = s_slot + base + g;
                     uint2 rec[U];
                     Part part[U];
@@ -320,7 +326,7 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                                     unpack16<T>(raw[u][k], f);
 #pragma unroll
                                     for (int e = 0; e < VEC; ++e)
-                                        part[u] = dot_fma(f[e], static_cast<Part>(go[k][e]), part[u]);
+                                        part[u] = dot_fma(f[e], gop[k][e], part[u]);
                                 }
                             }
                         }
@@ -335,7 +341,7 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                                     const size_t idx = static_cast<size_t>(rec[u].x) + c;
                                     const float v = Elem<T>::to_f(__ldg(value + idx));
                                     red_add_scalar(gval + idx, w * go[k][0]);
-                                    part[u] = dot_fma(v, static_cast<Part>(go[k][0]), part[u]);
+                                    part[u] = dot_fma(v, gop[k][0], part[u]);
                                 }
                             }
                         }
@@ -363,11 +369,10 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                 auto trip = [&](int base, auto guarded_tag) {
                     bool precise = false;
                     if constexpr (WIDE) {
-                        const int s0 = base / CPS;
-                        const int s1 = min(32, (base + STEP + CPS - 1) / CPS);
-                        const uint32_t bits =
-                            (s1 - s0 >= 32 ? 0xffffffffu : ((1u << (s1 - s0)) - 1u)) << s0;
-                        precise = (m_precise & bits) != 0u;
+                        // samples base/CPS .. of this trip (STEP / CPS of them)
+                        constexpr int NS = (STEP / CPS > 0) ? STEP / CPS : 1;
+                        constexpr uint32_t kBits = NS >= 32 ? 0xffffffffu : ((1u << NS) - 1u);
+                        precise = ((m_precise >> (base / CPS)) & kBits) != 0u;
                     }
                     if (precise) {
                         if constexpr (WIDE)
