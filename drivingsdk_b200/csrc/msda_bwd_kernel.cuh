@@ -137,6 +137,9 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
     unsigned char* wb = smem + static_cast<size_t>(warp) * p.warp_smem;
     uint2* s_slot = reinterpret_cast<uint2*>(wb);
     float* s_part = reinterpret_cast<float*>(wb + kSlotBytes);
+    // where this lane's row slot sits inside the partials of its sample (used when an
+    // instruction covers whole samples)
+    const int part_lane = (g / CPS) * SSTRIDE + (g % CPS) * CSTR;
     init_unused_slots<CPS>(s_slot, lane);
     WarpStage<T> st = warp_stage_init<T>(p, wb + kSlotBytes + kPartBytes, lane);
 
@@ -298,37 +301,45 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                         }
 #pragma unroll
                         for (int u = 0; u < U; ++u) {
-                            if (rec[u].x != kNoRow) {
-                                const float w = __uint_as_float(rec[u].y);
-                                if constexpr (SPLIT_RED) {
-                                    float* row = reinterpret_cast<float*>(
-                                        glane + static_cast<size_t>(rec[u].x) * 32);
+                            // Straight-line code: the products are formed for every slot and
+                            // only the reduction itself is predicated on the row existing
+                            // (a branch per row costs more than the wasted multiplies).
+                            const bool has_row = rec[u].x != kNoRow;
+                            const float w = __uint_as_float(rec[u].y);
+                            if constexpr (SPLIT_RED) {
+                                float* row = reinterpret_cast<float*>(
+                                    glane + static_cast<size_t>(rec[u].x) * 32);
+                                if (has_row) {
                                     red_add_f32x4(row, w * gred[0][0], w * gred[0][1],
                                                   w * gred[0][2], w * gred[0][3]);
                                     red_add_f32x4(row + LPR * 4, w * gred[1][0], w * gred[1][1],
                                                   w * gred[1][2], w * gred[1][3]);
-                                } else {
+                                }
+                            } else {
 #pragma unroll
-                                    for (int k = 0; k < NV; ++k) {
-                                        float contrib[VEC];
+                                for (int k = 0; k < NV; ++k) {
+                                    float contrib[VEC];
 #pragma unroll
-                                        for (int e = 0; e < VEC; ++e) contrib[e] = w * go[k][e];
+                                    for (int e = 0; e < VEC; ++e) contrib[e] = w * go[k][e];
+                                    if (has_row)
                                         red_add_vec<TG, VEC>(
                                             reinterpret_cast<TG*>(
                                                 glane + static_cast<size_t>(rec[u].x) * 16 +
                                                 k * (LPR * 16)),
                                             contrib);
-                                    }
-                                }
-#pragma unroll
-                                for (int k = 0; k < NV; ++k) {
-                                    float f[VEC];
-                                    unpack16<T>(raw[u][k], f);
-#pragma unroll
-                                    for (int e = 0; e < VEC; ++e)
-                                        part[u] = dot_fma(f[e], gop[k][e], part[u]);
                                 }
                             }
+                            Part acc = 0;
+#pragma unroll
+                            for (int k = 0; k < NV; ++k) {
+                                float f[VEC];
+                                unpack16<T>(raw[u][k], f);
+#pragma unroll
+                                for (int e = 0; e < VEC; ++e) acc = dot_fma(f[e], gop[k][e], acc);
+                            }
+                            // a select, not a multiplication by zero: row 0 (loaded in place of
+                            // a missing row) may hold anything
+                            part[u] = has_row ? acc : Part(0);
                         }
                     } else {
 #pragma unroll
@@ -355,7 +366,15 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                             part[u] += __shfl_xor_sync(0xffffffffu, part[u], off);
                         const int slot = base + u * RPI + g;
                         if ((!GUARDED || slot < slot_end) && j < PART) {
-                            float* dst = s_part + (slot / CPS) * SSTRIDE + (slot % CPS) * CSTR;
+                            float* dst;
+                            if constexpr (RPI % CPS == 0) {
+                                // whole samples per instruction: the lane's place inside a
+                                // sample's partials never changes (part_lane), the sample
+                                // advances by RPI / CPS per instruction
+                                dst = s_part + (base / CPS + u * (RPI / CPS)) * SSTRIDE + part_lane;
+                            } else {
+                                dst = s_part + (slot / CPS) * SSTRIDE + (slot % CPS) * CSTR;
+                            }
                             if constexpr (PRECISE) {
                                 reinterpret_cast<double*>(dst)[j] = part[u];
                             } else {
