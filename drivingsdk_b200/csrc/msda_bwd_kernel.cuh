@@ -320,7 +320,12 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                                 for (int k = 0; k < NV; ++k) {
                                     float contrib[VEC];
 #pragma unroll
-                                    for (int e = 0; e < VEC; ++e) contrib[e] = w * go[k][e];
+                                    for (int e = 0; e < VEC; e += 2) {
+                                        const float2 c2 = fmul2(make_float2(w, w),
+                                                                make_float2(go[k][e], go[k][e + 1]));
+                                        contrib[e] = c2.x;
+                                        contrib[e + 1] = c2.y;
+                                    }
                                     if (has_row)
                                         red_add_vec<TG, VEC>(
                                             reinterpret_cast<TG*>(
@@ -330,12 +335,29 @@ msda_bwd_kernel(const __grid_constant__ Params p) {
                                 }
                             }
                             Part acc = 0;
+                            if constexpr (PRECISE) {
 #pragma unroll
-                            for (int k = 0; k < NV; ++k) {
-                                float f[VEC];
-                                unpack16<T>(raw[u][k], f);
+                                for (int k = 0; k < NV; ++k) {
+                                    float f[VEC];
+                                    unpack16<T>(raw[u][k], f);
 #pragma unroll
-                                for (int e = 0; e < VEC; ++e) acc = dot_fma(f[e], gop[k][e], acc);
+                                    for (int e = 0; e < VEC; ++e)
+                                        acc = dot_fma(f[e], gop[k][e], acc);
+                                }
+                            } else {
+                                // even and odd channels in the two halves of packed fp32x2
+                                // multiply-adds, added at the end
+                                float2 a2 = make_float2(0.f, 0.f);
+#pragma unroll
+                                for (int k = 0; k < NV; ++k) {
+                                    float f[VEC];
+                                    unpack16<T>(raw[u][k], f);
+#pragma unroll
+                                    for (int e = 0; e < VEC; e += 2)
+                                        a2 = ffma2(make_float2(f[e], f[e + 1]),
+                                                   make_float2(go[k][e], go[k][e + 1]), a2);
+                                }
+                                acc = a2.x + a2.y;
                             }
                             // a select, not a multiplication by zero: row 0 (loaded in place of
                             // a missing row) may hold anything

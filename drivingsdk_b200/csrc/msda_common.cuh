@@ -247,6 +247,29 @@ __device__ __forceinline__ void red_add_vec<__nv_bfloat16, 8>(__nv_bfloat16* row
     red_add_16x8(row, pack16<__nv_bfloat16>(c));
 }
 
+// Two fp32 multiply-adds in one instruction (Blackwell's packed fma.rn.f32x2):
+// (a.x * b.x + c.x, a.y * b.y + c.y), each rounded once like fmaf.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+    uint64_t ra, rb, rc, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+    uint64_t ra, rb, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+
 // Stores two adjacent elements (x at p[0], y at p[1]) with one instruction.
 __device__ __forceinline__ void store_pair(float* p, float x, float y) {
     *reinterpret_cast<float2*>(p) = make_float2(x, y);

@@ -152,7 +152,13 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
                                 float f[VEC];
                                 unpack16<T>(raw[u][k], f);
 #pragma unroll
-                                for (int e = 0; e < VEC; ++e) acc[k][e] = fmaf(w, f[e], acc[k][e]);
+                                for (int e = 0; e < VEC; e += 2) {
+                                    const float2 r =
+                                        ffma2(make_float2(w, w), make_float2(f[e], f[e + 1]),
+                                              make_float2(acc[k][e], acc[k][e + 1]));
+                                    acc[k][e] = r.x;
+                                    acc[k][e + 1] = r.y;
+                                }
                             }
                         }
                     } else {
