@@ -60,6 +60,8 @@ def parse_args():
                          "TF32 product, 0 = fp32 FMA kernel")
     ap.add_argument("--workload", default="bevformer_sca")
     ap.add_argument("--dtype", default="float32", choices=["float32", "float16", "bfloat16"])
+    ap.add_argument("--batch", type=int, default=None,
+                    help="override the workload's batch size (smaller cases for profiler captures)")
     ap.add_argument("--shard", default="batch", choices=["batch", "query"])
     ap.add_argument("--stage", type=int, default=None, help="tuning: 0/1 bulk-copy staging")
     ap.add_argument("--ctas-per-sm", type=int, default=None, help="tuning: forward kernel")
@@ -201,6 +203,8 @@ def run_reference_arm(args):
     if rank != 0:
         return
     w = workloads.WORKLOADS[args.workload]
+    if args.batch:
+        w = w.with_batch(args.batch)
     seconds = max(4.0, min(60.0, 2.0 * (args.steps + args.warmup)))
     base = cpu_baseline(w, seconds)
     line = {
@@ -247,6 +251,8 @@ def run_native(args):
     code = capi.dtype_code(dtype)
     esize = 4 if dtype == torch.float32 else 2
     w = workloads.WORKLOADS[args.workload]
+    if args.batch:
+        w = w.with_batch(args.batch)
     query_shard = args.shard == "query" and world > 1
     if query_shard:
         from drivingsdk_b200 import dist as sdist
