@@ -440,7 +440,7 @@ def run_native(args):
 # name is the one launched, so a number captured for an older kernel is never reported for a
 # newer one; combinations without a capture report null.
 TRAFFIC_BYTES = {
-    ("msda_bwd_kernel", "bevformer_sca", "float32"): 626_346_752,
+    ("msda_bwd_kernel", "bevformer_sca", "float32"): 630_341_376,
 }
 
 
