@@ -25,6 +25,11 @@ Public surface, same names as the reference package exports for this path
                                deformable_groups)   ModulatedDeformConv2dFunction
                                (mx_driving/ops/modulated_deform_conv2d.py:24-132)
 
+    set_status_checks(on) -> previous         debugging: every operator call synchronises, reads
+                               the device's status word and raises if a kernel refused or
+                               abandoned work (also MSDA_CHECK_STATUS=1 in the environment)
+    device_status(clear=True) -> int           the sticky status bits (synchronises)
+
 The operator names are resolved on first use, so that the patcher (pure Python)
 can be imported on a machine without the compiled extension. Using an operator
 without the extension raises ImportError: there is no CPU or eager fallback.
@@ -52,7 +57,8 @@ _CONV_SIDE = {
 }
 
 __all__ = (list(_OP_NAMES) + list(_FUSED_NAMES) + list(_GKA_NAMES) + list(_DA_NAMES)
-           + list(_CONV_SIDE) + ["patcher", "default_patcher", "dist"])
+           + list(_CONV_SIDE)
+           + ["patcher", "default_patcher", "dist", "set_status_checks", "device_status"])
 
 
 def __getattr__(name):
@@ -71,6 +77,8 @@ def __getattr__(name):
     if name in _CONV_SIDE:
         mod = importlib.import_module(__name__ + ".ops." + _CONV_SIDE[name])
         return getattr(mod, name)
+    if name in ("set_status_checks", "device_status"):
+        return getattr(importlib.import_module(__name__ + "._C"), name)
     if name == "_C":
         return importlib.import_module(__name__ + "._C")
     if name in ("patcher", "dist", "capi", "ops"):

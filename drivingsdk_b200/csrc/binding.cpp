@@ -22,6 +22,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <atomic>
+#include <cstdlib>
 #include <tuple>
 
 #include "../../include/conv_ops_sm100.h"
@@ -103,14 +105,38 @@ Dims check_inputs(const at::Tensor& value, const at::Tensor& shapes, const at::T
     return d;
 }
 
+// Debugging switch: read the device's sticky status word after every operator call. That
+// costs a device synchronisation per call, so it is off unless set_status_checks(true) was
+// called or the process started with MSDA_CHECK_STATUS=1.
+std::atomic<bool> g_check_status{[] {
+    const char* e = std::getenv("MSDA_CHECK_STATUS");
+    return e != nullptr && e[0] != '\0' && e[0] != '0';
+}()};
+
 void raise_on_error(int rc, const char* what) {
-    if (rc == MSDA_OK) return;
+    if (rc == MSDA_OK) {
+        if (!g_check_status.load(std::memory_order_relaxed)) return;
+        const int status = msda_sm100_device_status(1);
+        TORCH_CHECK(status >= 0, what, ": reading the device status failed: ",
+                    cudaGetErrorString(static_cast<cudaError_t>(msda_sm100_last_cuda_error())));
+        // bit 0 (a staged tile timed out and was fetched with plain loads) leaves the
+        // results correct; every other bit means a kernel refused or abandoned work
+        TORCH_CHECK((status & ~1) == 0, what, ": device status ", status,
+                    " (2: a tensor-core pipeline wait ran out, 4: level table in device memory "
+                    "inconsistent with the number of keys, 16: bounds check of the debug build)");
+        if (status & 1)
+            TORCH_WARN(what, ": a staged tile did not arrive within the poll limit; the kernel "
+                             "used plain loads instead");
+        return;
+    }
     if (rc == MSDA_ERR_CUDA) {
         const auto ce = static_cast<cudaError_t>(msda_sm100_last_cuda_error());
         TORCH_CHECK(false, what, ": CUDA error: ", cudaGetErrorString(ce));
     }
     TORCH_CHECK(false, what, ": ", msda_sm100_strerror(rc));
 }
+
+bool set_status_checks(bool on) { return g_check_status.exchange(on); }
 
 }  // namespace
 
@@ -795,6 +821,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           "dilation, groups, deformable_groups, with_bias) -> (out, offset_output)");
     m.def("modulated_deformable_conv2d_backward", &modulated_deformable_conv2d_backward,
           "-> (grad_x, grad_weight, grad_bias, grad_offset, grad_mask)");
+    m.def("set_status_checks", &set_status_checks,
+          "(on) -> previous setting; when on, every operator call synchronises, reads the "
+          "device status word and raises if a kernel refused or abandoned work");
+    m.def("device_status", [](bool clear) { return msda_sm100_device_status(clear ? 1 : 0); },
+          "(clear) -> the device's sticky status bits (synchronises)");
     m.def("dcn_use_tensor_cores", &dcn_use_tensor_cores,
           "1 / 0 selects the tcgen05 / fp32 FMA product kernels; returns the previous setting");
     m.def("npu_add_relu", &npu_add_relu, "x = relu(x + y) in place; returns x");

@@ -226,7 +226,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t* empty = bars + 2 * kStages;           // the MMAs that read the stage have finished
     uint64_t* accum_full = bars + 3 * kStages;      // [2] every MMA of the item has finished
     uint64_t* accum_empty = bars + 3 * kStages + 2; // [2] the epilogue has read the accumulator
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 4);
+    static_assert((3 * kStages + 5) * 8 + 8 <= 256, "barrier area");
+    uint64_t* drained = bars + 3 * kStages + 4;     // abort path only: the issued MMAs have retired
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 5);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -242,6 +244,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(&accum_full[a], 1);
             mbar_init(&accum_empty[a], 4);
         }
+        mbar_init(drained, 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -354,6 +357,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     mma_commit(&empty[s]);   // arrives when these MMAs no longer read the stage
                 }
                 if (ok) mma_commit(&accum_full[acc]);
+            }
+            if (!ok || *abort_flag) {
+                // Abandoning work: the MMAs already issued still write tensor memory and read
+                // the stages. Wait (bounded) until they have retired, so that the tensor
+                // memory is not handed back underneath them.
+                mma_commit(drained);
+                gemm_wait(drained, 0u);
             }
         }
     } else if (warp < 6) {

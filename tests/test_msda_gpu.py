@@ -393,3 +393,33 @@ def test_bad_level_table_on_the_device_is_reported_not_followed():
     assert rc == 0
     assert (lib.msda_sm100_device_status(1) & 4) == 4
     assert bool((out == 3.0).all())                # nothing was written
+
+
+def test_status_checks_turn_a_refused_launch_into_an_exception():
+    """With set_status_checks(True) the torch operators read the device status after every
+    call: a level table in device memory that reaches past value's rows then raises instead
+    of returning an untouched output; with the switch off (the default, no synchronisation)
+    the same call returns and the status word carries the bit."""
+    import drivingsdk_b200 as sdk
+    w = workloads.WORKLOADS["toy"].with_queries(64)
+    inp = workloads.make_inputs(w, torch.float32)
+    dev = parity.to_device(inp, torch.float32)
+    bad = dev["starts"].clone()
+    bad[-1] += 100
+    sdk.device_status(True)
+    prev = sdk.set_status_checks(True)
+    try:
+        with pytest.raises(RuntimeError, match="device status"):
+            sdk.multi_scale_deformable_attn(dev["value"], dev["shapes"], bad, dev["loc"],
+                                            dev["attn"])
+        assert sdk.device_status(True) == 0          # the failed check cleared it
+        good = sdk.multi_scale_deformable_attn(dev["value"], dev["shapes"], dev["starts"],
+                                               dev["loc"], dev["attn"])
+    finally:
+        sdk.set_status_checks(prev)
+    assert not prev
+    sdk.multi_scale_deformable_attn(dev["value"], dev["shapes"], bad, dev["loc"], dev["attn"])
+    assert sdk.device_status(True) & 4
+    again = sdk.multi_scale_deformable_attn(dev["value"], dev["shapes"], dev["starts"],
+                                            dev["loc"], dev["attn"])
+    assert torch.equal(good, again)
