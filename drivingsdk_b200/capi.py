@@ -16,7 +16,7 @@ DEBUG_LIB_PATH = os.path.join(_HERE, "libmsda_sm100_dbg.so")
 
 F32, F16, BF16 = 0, 1, 2
 TUNE_STAGE, TUNE_CTAS_PER_SM, TUNE_CTAS_PER_SM_BWD, TUNE_INTERLEAVE, TUNE_SPIN_LIMIT = 0, 1, 2, 3, 4
-TUNE_PRECISE_AMP, TUNE_DEBUG_ROW_LIMIT = 5, 6
+TUNE_PRECISE_AMP, TUNE_DEBUG_ROW_LIMIT, TUNE_PACK_ROWS = 5, 6, 7
 
 # name -> (restype, argtypes); kept in step with the headers under include/
 _vp, _ip, _i, _sz = ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t

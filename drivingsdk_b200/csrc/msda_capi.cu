@@ -27,6 +27,7 @@ std::atomic<int> g_tune_cps_bwd{0};
 std::atomic<int> g_tune_spin{msda::kSpinLimit};
 std::atomic<int> g_tune_precise_amp{8};
 std::atomic<int> g_tune_debug_rows{0};
+std::atomic<int> g_tune_pack{1};
 std::atomic<long long> g_launches{0};
 thread_local int t_last_cuda_error = 0;
 thread_local cudaEvent_t t_prof[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -190,6 +191,7 @@ int fill_common(Params& p, const DeviceInfo* dev, const void* value, const int32
                   ? 1
                   : 0;
     p.spin_limit = g_tune_spin.load();
+    p.pack_rows = g_tune_pack.load() != 0 ? 1 : 0;
     p.precise_amp = static_cast<float>(g_tune_precise_amp.load());
     if (!aligned_to(value, e) || !aligned_to(loc, e) || !aligned_to(attn, e)) return MSDA_ERR_ALIGN;
     return MSDA_OK;
@@ -452,6 +454,7 @@ int msda_sm100_tune(int knob, int value) {
         case MSDA_TUNE_SPIN_LIMIT: target = &g_tune_spin; break;
         case MSDA_TUNE_PRECISE_AMP: target = &g_tune_precise_amp; break;
         case MSDA_TUNE_DEBUG_ROW_LIMIT: target = &g_tune_debug_rows; break;
+        case MSDA_TUNE_PACK_ROWS: target = &g_tune_pack; break;
         default: return MSDA_ERR_DIMS;
     }
     if (value < 0) return target->load();

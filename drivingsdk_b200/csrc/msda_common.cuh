@@ -96,6 +96,7 @@ struct Params {
     int LP;             // L * P
     int tasks_per_item; // consecutive (b, q, h) tasks one warp pass covers
     int use_table;
+    int pack_rows;      // 1: the forward kernels keep records only for the corners that exist
     int stage;          // 1: each warp bulk-copies its next item's locations/weights to shared
                         // memory while it works on the current one; 0: direct loads
     float precise_amp;  // fp32 backward: samples with max(W, H) * |attention| >= this value

@@ -21,9 +21,14 @@
 
 namespace msda {
 
-template <typename T, int LPR, int NV, bool SCALAR, int MODE>
+// PACK (bilinear sampling, vector rows): phase 1 leaves records only for the corners that
+// exist, so the gather loop neither issues nor predicates anything for the others
+// (BEVFormer shape, 18 % of the corners outside the image: 146 -> 132 us).
+template <typename T, int LPR, int NV, bool SCALAR, int MODE, bool PACK>
 __global__ void __launch_bounds__(kThreadsPerCta, (SCALAR || NV > 1) ? 2 : MSDA_FWD_MIN_CTAS)
 msda_fwd_kernel(const __grid_constant__ Params p) {
+    static_assert(!PACK || (MODE != kModeNearest && !SCALAR),
+                  "packing is for the bilinear vector kernels");
     constexpr int CPS = (MODE == kModeFused) ? 4 : MODE;   // rows (corners) per sample
     constexpr bool FUSED = MODE == kModeFused;
     constexpr int VEC = SCALAR ? 1 : Elem<T>::kVec;
@@ -95,14 +100,30 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
             // ---- phase 1: lane = sample -----------------------------------------
             SampleGeom geom;
             long long gi;
+            Compaction packed;
+            packed.rows = 0;
             phase1<T, CPS, FUSED>(p, lv, chunk, lane, item, ntask_here, sloc, sattn, s_slot, geom,
-                                  gi);
+                                  gi, PACK ? &packed : nullptr);
             __syncwarp();
 
             // ---- phase 2: lane = (row slot, piece of row) -----------------------
             for (int tl2 = 0; tl2 < ntask_here; ++tl2) {
                 int slot_begin, slot_end, unguarded_end;
-                if (TPC == 1) {
+                if constexpr (PACK) {
+                    // only existing rows have records: a task's begin where its first
+                    // sample's would, and end where the next task's begin; what follows them
+                    // is another task's or stale, so the last trip is guarded
+                    if (TPC == 1) {
+                        slot_begin = 0;
+                        slot_end = packed.rows;
+                    } else {
+                        const int next = (tl2 + 1) * LP;   // first lane of the next task
+                        slot_begin = __shfl_sync(0xffffffffu, packed.first, tl2 * LP);
+                        const int e = __shfl_sync(0xffffffffu, packed.first, min(next, 31));
+                        slot_end = next < 32 ? e : packed.rows;
+                    }
+                    unguarded_end = slot_end - STEP + 1;
+                } else if (TPC == 1) {
                     // slots past the last sample hold "no row" records: no guard needed
                     slot_begin = 0;
                     slot_end = CPS * min(kChunk, LP - chunk * kChunk);
@@ -120,15 +141,19 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
                         for (int e = 0; e < VEC; ++e) acc[k][e] = 0.f;
                 }
 
-                auto gather = [&](int base, auto unroll_tag, auto guarded_tag) {
+                auto gather = [&](int base, auto unroll_tag, auto guarded_tag, auto present_tag) {
                     constexpr int U = decltype(unroll_tag)::value;   // rows in flight per lane
                     constexpr bool GUARDED = decltype(guarded_tag)::value;
+                    constexpr bool PRESENT = decltype(present_tag)::value;   // every record has a row
                     const uint2* sp = s_slot + base + g;
                     uint2 rec[U];
 #pragma unroll
                     for (int u = 0; u < U; ++u) {
                         rec[u] = sp[u * RPI];
-                        if (GUARDED && base + u * RPI + g >= slot_end) rec[u].x = kNoRow;
+                        // (with packed records what lies behind the last one is stale, weight
+                        // included)
+                        if (GUARDED && base + u * RPI + g >= slot_end)
+                            rec[u] = make_uint2(kNoRow, 0u);
                     }
                     if constexpr (!SCALAR) {
                         // A missing corner loads nothing and reads as zeros (its weight is
@@ -138,10 +163,16 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
                         for (int u = 0; u < U; ++u) {
 #pragma unroll
                             for (int k = 0; k < NV; ++k) {
-                                raw[u][k] = make_uint4(0u, 0u, 0u, 0u);
-                                if (rec[u].x != kNoRow)
+                                if constexpr (PRESENT) {
                                     raw[u][k] = ldg16(vlane + static_cast<size_t>(rec[u].x) * 16 +
                                                       k * (LPR * 16));
+                                } else {
+                                    raw[u][k] = make_uint4(0u, 0u, 0u, 0u);
+                                    if (rec[u].x != kNoRow)
+                                        raw[u][k] = ldg16(vlane +
+                                                          static_cast<size_t>(rec[u].x) * 16 +
+                                                          k * (LPR * 16));
+                                }
                             }
                         }
 #pragma unroll
@@ -189,21 +220,25 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
                 int base = slot_begin;
 #pragma unroll 1
                 for (; base < unguarded_end; base += STEP)
-                    gather(base, std::integral_constant<int, UNROLL>{}, std::false_type{});
+                    gather(base, std::integral_constant<int, UNROLL>{}, std::false_type{},
+                           std::integral_constant<bool, PACK>{});
                 if (slot_end - base > 2 * RPI) {
                     // more than two instructions' worth left: one guarded trip at full width
                     // keeps them all in flight (a chain of short trips is latency-bound)
-                    gather(base, std::integral_constant<int, UNROLL>{}, std::true_type{});
+                    gather(base, std::integral_constant<int, UNROLL>{}, std::true_type{},
+                           std::false_type{});
                 } else {
                     if constexpr (UNROLL > 2) {
                         if (base + 2 * RPI <= slot_end) {
-                            gather(base, std::integral_constant<int, 2>{}, std::false_type{});
+                            gather(base, std::integral_constant<int, 2>{}, std::false_type{},
+                                   std::integral_constant<bool, PACK>{});
                             base += 2 * RPI;
                         }
                     }
 #pragma unroll 1
                     for (; base < slot_end; base += RPI)
-                        gather(base, std::integral_constant<int, 1>{}, std::true_type{});
+                        gather(base, std::integral_constant<int, 1>{}, std::true_type{},
+                               std::false_type{});
                 }
 
                 // ---- epilogue ---------------------------------------------------
@@ -240,10 +275,10 @@ msda_fwd_kernel(const __grid_constant__ Params p) {
 // ---------------------------------------------------------------------------
 // launch table
 // ---------------------------------------------------------------------------
-template <typename T, int LPR, int NV, bool SCALAR, int MODE>
-static cudaError_t launch_fwd_inst(const Params& p, const LaunchShape& ls, size_t smem,
+template <typename T, int LPR, int NV, bool SCALAR, int MODE, bool PACK>
+static cudaError_t launch_fwd_pack(const Params& p, const LaunchShape& ls, size_t smem,
                                    cudaStream_t stream) {
-    auto kern = msda_fwd_kernel<T, LPR, NV, SCALAR, MODE>;
+    auto kern = msda_fwd_kernel<T, LPR, NV, SCALAR, MODE, PACK>;
     if (smem > 48 * 1024) {
         cudaError_t e =
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -254,6 +289,15 @@ static cudaError_t launch_fwd_inst(const Params& p, const LaunchShape& ls, size_
     if (e != cudaSuccess) return e;
     kern<<<grid, kThreadsPerCta, smem, stream>>>(p);
     return cudaGetLastError();
+}
+
+template <typename T, int LPR, int NV, bool SCALAR, int MODE>
+static cudaError_t launch_fwd_inst(const Params& p, const LaunchShape& ls, size_t smem,
+                                   cudaStream_t stream) {
+    if constexpr (MODE != kModeNearest && !SCALAR) {
+        if (p.pack_rows) return launch_fwd_pack<T, LPR, NV, SCALAR, MODE, true>(p, ls, smem, stream);
+    }
+    return launch_fwd_pack<T, LPR, NV, SCALAR, MODE, false>(p, ls, smem, stream);
 }
 
 template <typename T, int MODE>

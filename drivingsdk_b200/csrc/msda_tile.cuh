@@ -244,6 +244,12 @@ __device__ __forceinline__ float* fused_scratch(uint2* s_slot) {
     return reinterpret_cast<float*>(s_slot + kSlots);
 }
 
+// Where this lane's records start and how many records the chunk has, when phase 1 packs
+// the existing corners' records (see there).
+struct Compaction {
+    int first, rows;
+};
+
 // Phase 1 of one chunk: lane = sample. Obtains (x, y, weight) — from the staged buffer or
 // directly — and leaves the sample's slot records in shared memory: four (bilinear corners)
 // for CPS == 4, one (clamped integer pixel) for CPS == 1. Returns whether this lane holds a
@@ -255,7 +261,7 @@ template <typename T, int CPS, bool FUSED>
 __device__ __forceinline__ bool phase1(const Params& p, const LaneLevels& lv, int chunk, int lane,
                                        long long item, int ntask_here, const T* sloc,
                                        const T* sattn, uint2* s_slot, SampleGeom& geom,
-                                       long long& gi) {
+                                       long long& gi, Compaction* compact = nullptr) {
     int tl, s;
     lane_sample_index(p, chunk, lane, tl, s);
     const bool active = (tl < ntask_here) && (s < p.LP);
@@ -312,9 +318,29 @@ __device__ __forceinline__ bool phase1(const Params& p, const LaneLevels& lv, in
         debug_check_rows(p, rec01, rec23);
     }
     if constexpr (CPS == 4) {
-        uint4* dst = reinterpret_cast<uint4*>(s_slot) + 2 * lane;
-        dst[0] = rec01;
-        dst[1] = rec23;
+        if (compact != nullptr) {
+            // Only the corners that exist get a record, packed from slot 0 on in (sample,
+            // corner) order; the gather loop then walks compact->rows records instead of
+            // 4 per sample (and must not read past them: what follows is stale).
+            const bool c0 = rec01.x != kNoRow, c1 = rec01.z != kNoRow;
+            const bool c2 = rec23.x != kNoRow, c3 = rec23.z != kNoRow;
+            const uint32_t b0 = __ballot_sync(0xffffffffu, c0), b1 = __ballot_sync(0xffffffffu, c1);
+            const uint32_t b2 = __ballot_sync(0xffffffffu, c2), b3 = __ballot_sync(0xffffffffu, c3);
+            const uint32_t below = (1u << lane) - 1u;
+            int pos = __popc(b0 & below) + __popc(b1 & below) + __popc(b2 & below) +
+                      __popc(b3 & below);
+            const int rows = __popc(b0) + __popc(b1) + __popc(b2) + __popc(b3);
+            compact->first = pos;
+            compact->rows = rows;
+            if (c0) s_slot[pos++] = make_uint2(rec01.x, rec01.y);
+            if (c1) s_slot[pos++] = make_uint2(rec01.z, rec01.w);
+            if (c2) s_slot[pos++] = make_uint2(rec23.x, rec23.y);
+            if (c3) s_slot[pos] = make_uint2(rec23.z, rec23.w);
+        } else {
+            uint4* dst = reinterpret_cast<uint4*>(s_slot) + 2 * lane;
+            dst[0] = rec01;
+            dst[1] = rec23;
+        }
     } else {
         s_slot[lane] = make_uint2(rec01.x, rec01.y);
     }

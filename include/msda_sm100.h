@@ -251,7 +251,11 @@ int msda_sm100_device_status(int clear);
  *   MSDA_TUNE_DEBUG_ROW_LIMIT  bounds-checking build only (see msda_sm100_debug_bounds): when
  *                            > 0 the checks behave as if value / grad_value had only this many
  *                            (key, head) rows, so that a test can see them fire on a
- *                            correct problem. Ignored by the normal build. */
+ *                            correct problem. Ignored by the normal build.
+ *   MSDA_TUNE_PACK_ROWS      1 (default): the forward kernels of the bilinear operators keep a
+ *                            record only for the corners that exist and walk those; 0 = one
+ *                            record per (sample, corner), missing ones skipped one by one.
+ *                            Same results either way. */
 typedef enum msda_tune {
     MSDA_TUNE_STAGE = 0,
     MSDA_TUNE_CTAS_PER_SM = 1,
@@ -259,7 +263,8 @@ typedef enum msda_tune {
     MSDA_TUNE_INTERLEAVE = 3,
     MSDA_TUNE_SPIN_LIMIT = 4,
     MSDA_TUNE_PRECISE_AMP = 5,
-    MSDA_TUNE_DEBUG_ROW_LIMIT = 6
+    MSDA_TUNE_DEBUG_ROW_LIMIT = 6,
+    MSDA_TUNE_PACK_ROWS = 7
 } msda_tune;
 int msda_sm100_tune(int knob, int value);
 

@@ -423,3 +423,28 @@ def test_status_checks_turn_a_refused_launch_into_an_exception():
     again = sdk.multi_scale_deformable_attn(dev["value"], dev["shapes"], dev["starts"],
                                             dev["loc"], dev["attn"])
     assert torch.equal(good, again)
+
+
+@pytest.mark.parametrize("name", ["toy", "bevformer_sca", "stress_d128"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_forward_with_and_without_packed_records(name, dtype):
+    """The forward kernels keep records only for the corners that exist (default) or one per
+    (sample, corner) (MSDA_TUNE_PACK_ROWS = 0): both forms must agree with the oracle, with one
+    task per warp pass (BEVFormer) and with several (toy, stress)."""
+    from drivingsdk_b200 import capi
+    lib = capi.load()
+    w = workloads.WORKLOADS[name].with_batch(1)
+    w = w.with_queries(min(w.Q, 700))
+    inp = workloads.make_inputs(w, dtype)
+    dev = parity.to_device(inp, dtype)
+    prev = lib.msda_sm100_tune(capi.TUNE_PACK_ROWS, 0)
+    try:
+        assert prev == 1
+        plain = parity.run_c_abi(dev, dtype)
+        parity.compare_all(inp, plain, dtype)
+    finally:
+        lib.msda_sm100_tune(capi.TUNE_PACK_ROWS, prev)
+    packed = parity.run_c_abi(dev, dtype)
+    parity.compare_all(inp, packed, dtype)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    torch.testing.assert_close(packed[0].float(), plain[0].float(), rtol=tol, atol=tol)
