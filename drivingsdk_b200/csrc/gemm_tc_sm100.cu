@@ -290,12 +290,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                 }
             }
-            if (*abort_flag) {
-                // let the copies that were issued land before the CTA goes away
-                const uint32_t first = it > static_cast<uint32_t>(kStages) ? it - kStages : 0u;
-                for (uint32_t j = first; j < it; ++j)
-                    gemm_wait(&full_raw[j % kStages], (j / kStages) & 1u);
-            }
+            // Let the copies that were issued land before the CTA goes away, whoever gave up
+            // (when nothing went wrong these phases have completed and the waits return at once).
+            const uint32_t first = it > static_cast<uint32_t>(kStages) ? it - kStages : 0u;
+            for (uint32_t j = first; j < it; ++j)
+                gemm_wait(&full_raw[j % kStages], (j / kStages) & 1u);
         }
     } else if (warp == 1) {
         // ---------------- MMA issue ----------------
