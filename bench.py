@@ -63,7 +63,7 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=None,
                     help="override the workload's batch size (smaller cases for profiler captures)")
     ap.add_argument("--shard", default="batch", choices=["batch", "query"])
-    ap.add_argument("--stage", type=int, default=None, help="tuning: 0/1 bulk-copy staging")
+    ap.add_argument("--stage", type=int, default=None, help="tuning: bulk-copy staging 0 off / 1 both directions / 2 backward only (default)")
     ap.add_argument("--ctas-per-sm", type=int, default=None, help="tuning: forward kernel")
     ap.add_argument("--ctas-per-sm-bwd", type=int, default=None, help="tuning: backward kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -20,7 +20,7 @@ constexpr int kMaxDevices = 64;
 
 __device__ int g_status_word;
 
-std::atomic<int> g_tune_stage{1};
+std::atomic<int> g_tune_stage{2};   // 0 never, 1 both directions, 2 backward kernels only
 std::atomic<int> g_tune_interleave{1};
 std::atomic<int> g_tune_cps_fwd{0};
 std::atomic<int> g_tune_cps_bwd{0};
@@ -132,7 +132,7 @@ int set_row_units(Params& p, const RowPlan& rp, int dtype) {
 // Fills the parts of Params common to both directions.
 int fill_common(Params& p, const DeviceInfo* dev, const void* value, const int32_t* shapes,
                 const int32_t* starts, const void* loc, const void* attn, int B, int K, int H,
-                int D, int L, int Q, int P, int dtype) {
+                int D, int L, int Q, int P, int dtype, bool backward) {
     std::memset(&p, 0, sizeof(p));
     p.value = value;
     p.loc = loc;
@@ -186,8 +186,9 @@ int fill_common(Params& p, const DeviceInfo* dev, const void* value, const int32
     // Bulk-copy staging needs 16-byte aligned sources and sizes: per item the weights take
     // samples * e bytes and the locations twice that.
     const size_t item_attn_bytes = static_cast<size_t>(p.tasks_per_item) * p.LP * e;
-    p.stage = (g_tune_stage.load() != 0 && aligned_to(loc, 16) && aligned_to(attn, 16) &&
-               item_attn_bytes % 16 == 0)
+    const int stage_mode = g_tune_stage.load();
+    p.stage = ((stage_mode == 1 || (stage_mode == 2 && backward)) && aligned_to(loc, 16) &&
+               aligned_to(attn, 16) && item_attn_bytes % 16 == 0)
                   ? 1
                   : 0;
     p.spin_limit = g_tune_spin.load();
@@ -218,7 +219,7 @@ int backward_impl(const void* value, const int32_t* shapes, const int32_t* start
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
     Params p;
-    rc = fill_common(p, dev, value, shapes, starts, loc, attn, B, K, H, D, L, Q, P, dtype);
+    rc = fill_common(p, dev, value, shapes, starts, loc, attn, B, K, H, D, L, Q, P, dtype, true);
     if (rc != MSDA_OK) return rc;
     const size_t e = elem_size(dtype);
     if (!aligned_to(grad_out, e) || !aligned_to(grad_value, e) || !aligned_to(grad_attn, e) ||
@@ -291,7 +292,7 @@ int forward_impl(const void* value, const int32_t* spatial_shapes,
 
     Params p;
     rc = fill_common(p, dev, value, spatial_shapes, level_start_index, sampling_locations,
-                     attention_weights, B, K, H, D, L, Q, P, dtype);
+                     attention_weights, B, K, H, D, L, Q, P, dtype, false);
     if (rc != MSDA_OK) return rc;
     if (!aligned_to(output, elem_size(dtype))) return MSDA_ERR_ALIGN;
     p.out = output;

@@ -34,7 +34,7 @@ def test_random_shapes(index):
     dtype = rng.choice([torch.float32, torch.float32, torch.float16, torch.bfloat16])
     inp = workloads.make_inputs(w, dtype)
     dev = parity.to_device(inp, dtype)
-    stage = index % 2
+    stage = index % 3      # 0 no staging, 1 both directions, 2 backward only (the default)
     from drivingsdk_b200 import capi
     prev = capi.load().msda_sm100_tune(capi.TUNE_STAGE, stage)
     try:

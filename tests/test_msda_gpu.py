@@ -29,7 +29,7 @@ def _golden_check(case, results, dtype):
 
 
 @pytest.mark.parametrize("name", NAMES)
-@pytest.mark.parametrize("stage", [0, 1])
+@pytest.mark.parametrize("stage", [0, 1, 2])
 def test_golden_fixture_through_c_abi(name, stage):
     """CUDA kernels, called through the C ABI, against the reference golden's own outputs."""
     from drivingsdk_b200 import capi
@@ -327,11 +327,25 @@ def test_staging_wait_that_runs_out_falls_back_to_direct_loads(dtype):
     inp = workloads.make_inputs(w, dtype)
     dev = parity.to_device(inp, dtype)
     prev = lib.msda_sm100_tune(capi.TUNE_SPIN_LIMIT, 0)
+    prev_stage = lib.msda_sm100_tune(capi.TUNE_STAGE, 1)      # staging in both directions
     try:
+        B, K, H, D = dev["value"].shape
+        _, Q, _, L, P, _ = dev["loc"].shape
+        out = torch.empty(B, Q, H * D, device="cuda", dtype=dtype)
+        shapes = dev["shapes"].to(torch.int32).contiguous()
+        starts = dev["starts"].to(torch.int32).contiguous()
+        rc = lib.msda_sm100_forward(dev["value"].data_ptr(), shapes.data_ptr(), starts.data_ptr(),
+                                    dev["loc"].data_ptr(), dev["attn"].data_ptr(), out.data_ptr(),
+                                    B, K, H, D, L, Q, P, capi.dtype_code(dtype),
+                                    torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        forward_status = lib.msda_sm100_device_status(1)      # the forward kernel alone
         results = parity.run_c_abi(dev, dtype)
         status = lib.msda_sm100_device_status(1)
     finally:
         lib.msda_sm100_tune(capi.TUNE_SPIN_LIMIT, prev)
+        lib.msda_sm100_tune(capi.TUNE_STAGE, prev_stage)
+    assert forward_status >= 0 and (forward_status & 1) == 1, forward_status
     assert status >= 0 and (status & 1) == 1, status
     parity.compare_all(inp, results, dtype)
     # with the limit restored the same call completes without the bit
