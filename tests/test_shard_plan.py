@@ -136,9 +136,13 @@ def _rank_main(rank, world, port, B, mode, out_q):
         shapes, starts = inp["shapes"], inp["starts"]
         op = lambda v, s, st, l, a: golden_torch.msda_forward(v, s, l, a)
         scatter = mode.endswith("+scatter")
-        kind = mode.split("+")[0]
-        # a long kernel and a tiny gradient: splitting queries always pays in this model
+        kind = mode.split("+")[0].rstrip("!")
+        # a long kernel and a tiny gradient: splitting queries always pays in this model;
+        # "!": a short kernel and a huge gradient, so that leaving ranks idle beats any
+        # collective
         cost = sdist.CostModel(entry_seconds=1.0, entry_grad_bytes=1.0)
+        if mode.endswith("!"):
+            cost = sdist.CostModel(entry_seconds=1e-6, entry_grad_bytes=1e12)
         p = sdist.plan(w.B, w.Q, world, cost=cost, scatter=scatter)
         assert p.kind == kind, (p.kind, kind)
         groups = sdist.make_groups(p)
@@ -173,7 +177,7 @@ def _rank_main(rank, world, port, B, mode, out_q):
 
 @pytest.mark.parametrize("world,B,mode", [(2, 2, "batch"), (2, 3, "batch"), (2, 1, "hybrid"),
                                           (2, 1, "hybrid+scatter"), (4, 2, "hybrid"),
-                                          (4, 2, "hybrid+scatter")])
+                                          (4, 2, "hybrid+scatter"), (4, 3, "batch!")])
 def test_ranks_match_unsharded(world, B, mode):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
