@@ -531,7 +531,8 @@ def run_planned_splits(lib, dist, dev, rank, world, w, dtype, replica_ms_per_ste
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         entry_s = float(tt.item()) * 1e-3
         del dv, o1, g1, ws1
-        cost = sdist.CostModel(entry_s, float(wl.K * wl.H * wl.D * esize))
+        cost = sdist.CostModel(entry_s, float(wl.K * wl.H * wl.D * esize),
+                               fixed_seconds=sdist.fixed_entry_seconds(wl.K, wl.H, wl.D, esize))
         plan = sdist.plan(wl.B, wl.Q, world, cost=cost)
         if force_kind == "hybrid" and plan.kind != "hybrid":
             plan = sdist.candidate_plans(wl.B, wl.Q, world)[1]

@@ -56,19 +56,39 @@ def query_range(Q: int, world: int, rank: int) -> Tuple[int, int]:
 @dataclass(frozen=True)
 class CostModel:
     """What ``plan`` needs to compare plans: seconds one GPU takes for forward + backward of
-    ONE batch entry, bytes of one entry's grad_value, and the collective's bus bandwidth
-    (bytes/s; 550e9 is an 8-GPU NCCL all-reduce of ~190 MB measured on B200 NVLink) and
-    latency."""
+    ONE batch entry, bytes of one entry's grad_value, how much of the entry's time does not
+    shrink when its queries are split (zero-fill and 16-bit conversion of grad_value, launch
+    gaps), and the collective's cost: bus bandwidth (bytes/s) plus a latency per ring step
+    (2(n-1) steps for an all-reduce over n ranks, n-1 for a reduce-scatter). The defaults are
+    NCCL all-reduces of 30.6 MB measured on 2, 4 and 8 B200s over NVLink (88 / 129 / 166 us);
+    messages of ~190 MB reach 550-600 GB/s."""
     entry_seconds: float
     entry_grad_bytes: float
-    bus_bytes_per_s: float = 550e9
-    latency_s: float = 25e-6
+    bus_bytes_per_s: float = 420e9
+    latency_s: float = 3e-6
+    fixed_seconds: float = 0.0
 
     def reduce_seconds(self, nbytes: float, ranks: int, scatter: bool = False) -> float:
         if ranks <= 1:
             return 0.0
-        factor = (1.0 if scatter else 2.0) * (ranks - 1) / ranks
-        return self.latency_s + factor * nbytes / self.bus_bytes_per_s
+        passes = 1.0 if scatter else 2.0
+        return (passes * (ranks - 1) * self.latency_s +
+                passes * (ranks - 1) / ranks * nbytes / self.bus_bytes_per_s)
+
+    def split_seconds(self, share: float) -> float:
+        """One entry's time on a rank that works `share` of its queries."""
+        fixed = min(self.fixed_seconds, self.entry_seconds)
+        return fixed + share * (self.entry_seconds - fixed)
+
+
+def fixed_entry_seconds(K: int, H: int, D: int, elem_size: int, hbm_bytes_per_s: float = 6.4e12,
+                        launch_gaps_s: float = 15e-6) -> float:
+    """The part of one entry's forward + backward that a split of its queries does not
+    shrink: the zero-fill of grad_value (for 16-bit tensors of its fp32 accumulation copy,
+    plus the conversion pass: 4 + 4 + 2 bytes per element) at HBM speed, and the gaps between
+    the call's launches."""
+    per_elem = 4 if elem_size == 4 else 10
+    return per_elem * K * H * D / hbm_bytes_per_s + launch_gaps_s
 
 
 def estimate_cost(K: int, H: int, D: int, L: int, Q: int, P: int, elem_size: int,
@@ -78,6 +98,7 @@ def estimate_cost(K: int, H: int, D: int, L: int, Q: int, P: int, elem_size: int
     one GPU (default: what they measure at the BEVFormer shape)."""
     v, s, o = K * H * D, Q * H * L * P, Q * H * D
     step_bytes = elem_size * (3 * v + 9 * s + 2 * o)
+    kw.setdefault("fixed_seconds", fixed_entry_seconds(K, H, D, elem_size))
     return CostModel(step_bytes / achieved_bytes_per_s, float(elem_size * v), **kw)
 
 
@@ -145,11 +166,11 @@ def predict_seconds(p: ShardPlan, B: int, Q: int, cost: CostModel) -> float:
     if p.kind == "hybrid":
         g = len(p.groups[0])
         share = max(qh - ql for ql, qh in p.query_ranges) / Q
-        return share * cost.entry_seconds + cost.reduce_seconds(cost.entry_grad_bytes, g,
-                                                                p.scatter)
+        return cost.split_seconds(share) + cost.reduce_seconds(cost.entry_grad_bytes, g,
+                                                               p.scatter)
     share = max(hi - lo for lo, hi in p.ranges) / Q
-    return B * share * cost.entry_seconds + cost.reduce_seconds(B * cost.entry_grad_bytes,
-                                                                p.world, p.scatter)
+    return B * cost.split_seconds(share) + cost.reduce_seconds(B * cost.entry_grad_bytes,
+                                                               p.world, p.scatter)
 
 
 def candidate_plans(B: int, Q: int, world: int, scatter: bool = False) -> List[ShardPlan]:
