@@ -869,6 +869,17 @@ def run_sibling(args):
                               "algorithmic_bytes": fwd_bytes + bwd_bytes}},
         "gpu_launches": int(lib.msda_sm100_launch_count() - launches0),
     }
+    if args.op == "gka":
+        # row-rate roofline, as for the headline operator: every sample is exactly one row
+        # (clamped pixel), gathered in the forward, gathered and reduced in the backward
+        ceil = measured_row_ceilings(lib, capi, dev, D, 4)
+        rows = B * Q * H * L * P
+        line["roofline"]["rows"] = {
+            "rows_per_launch": rows, "measured": ceil,
+            "forward": {"achieved_rows_per_s": rows / (fwd_ms * 1e-3),
+                        "frac": rows / (fwd_ms * 1e-3) / ceil["gather_rows_per_s"]},
+            "backward": {"achieved_rows_per_s": rows / (bwd_ms * 1e-3),
+                         "frac": rows / (bwd_ms * 1e-3) / ceil["red_rows_per_s"]}}
     if not args.no_cpu_baseline:
         msda_oracle.set_threads(os.cpu_count() or 1)
         t0 = time.perf_counter()
